@@ -1,0 +1,445 @@
+#!/usr/bin/env python
+"""Benchmark of the fused-RoPE 2D sliding-window attention path (forward + backward).
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload target|cfg2..cfg5] [--impl ours|reference]
+
+One "step" is one pass of the hot path over one batch of synthetic input: the fused
+RoPE-2D forward kernel, then the delta, dQ and dK/dV kernels.  Every rank works
+on its own (batch, head) slices; there is no collective on the data path (weak
+scaling: the per-GPU batch is fixed).  Rank 0 prints ONE JSON line.
+
+  value     whole-job windowed TFLOP/s with the inputs already resident in HBM
+  e2e       the same through the public Python surface with pinned HOST buffers:
+            q, k, v, dO copied host->device and o, dq, dk, dv copied back every step
+  roofline  the dominant kernel (largest share of a step) against the measured
+            bf16 tensor peak, from CUDA events around its launches in the timed region
+  cpu_baseline  the CPU oracle (the reference's dense-mask + SDPA form) on a bounded
+            sample of the same workload, on this box's host cores
+
+FLOP convention: forward 2*N*w^2*(d_qk+d_v) per (batch, head), backward 2.5x that;
+border truncation ignored (also printed: the exact in-grid pair count).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "2D-SWA fwd+bwd TFLOP/s (windowed FLOPs, whole job)"
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        d["_source"] = "measured"
+        return d
+    d = dict(FALLBACK_PEAKS)
+    d["_source"] = "fallback"
+    return d
+
+
+def workload_dims(name):
+    from dl_templates_b200.workloads import CONFIGS
+    cfg = dict(CONFIGS[name])
+    cfg["name"] = name
+    return cfg
+
+
+def exact_pairs(G, half):
+    """Number of in-grid (query, key) pairs of one head: sum over queries of the truncated window."""
+    per_axis = sum(min(G - 1, i + half) - max(0, i - half) + 1 for i in range(G))
+    return per_axis * per_axis
+
+
+# --------------------------------------------------------------------------------------------
+# clocks sampler
+# --------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=self.out, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.out.close()
+        sm, mx, reasons = [], [], set()
+        with open(self.path) as f:
+            for line in f:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    sm.append(float(parts[1]))
+                    mx.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                     parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        os.unlink(self.path)
+        # samples under load: the upper half of the observed SM clocks' time line is what ran the kernels
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------------
+# CPU arm: the oracle's SDPA form (the reference's own CPU path) on a bounded sample
+# --------------------------------------------------------------------------------------------
+def cpu_sample_step(case, cfg, n_slices):
+    """Forward + autograd backward of `n_slices` (batch, head) slices on the host."""
+    from oracle import swa_oracle as orc
+    q, k, v, do = (case[x][:, :n_slices].float().requires_grad_(x != "do") for x in ("q", "k", "v", "do"))
+    qr = orc.rope2d_ref(q, case["idx"], case["row_cs"], case["col_cs"])
+    kr = orc.rope2d_ref(k, case["idx"], case["row_cs"], case["col_cs"])
+    o = orc.tiled_swa_ref_sdpa(qr, kr, v, *case["win"], case["sm_scale"])
+    if cfg["bwd"]:
+        o.backward(do)
+    return o
+
+
+def cpu_case(cfg, n_slices):
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from swa_cases import make_case     # seeded CPU inputs shared with the parity tests (imports the oracle)
+    return make_case(cfg, B=1, H=n_slices)
+
+
+def cpu_slices_for(cfg):
+    """(batch, head) slices per CPU step: dense attention is O(N^2) per slice."""
+    N = cfg["grid"] ** 2
+    return 1 if N >= 8192 else (4 if N >= 4096 else 8)
+
+
+def run_cpu_reference(cfg, steps, warmup):
+    from dl_templates_b200.workloads import windowed_flops
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    n_slices = cpu_slices_for(cfg)
+    case = cpu_case(cfg, n_slices)
+    half = (cfg["w"] - 1) // 2
+    fwd, bwd = windowed_flops(n_slices, cfg["grid"] ** 2, 1, half, half, cfg["d_qk"], cfg["d_v"])
+    flops = fwd + (bwd if cfg["bwd"] else 0.0)
+    for _ in range(warmup):
+        cpu_sample_step(case, cfg, n_slices)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_sample_step(case, cfg, n_slices)
+    dt = (time.perf_counter() - t0) / max(1, steps)
+    return flops / dt / 1e12, dt * 1e3, cores, n_slices
+
+
+# --------------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------------
+def device_case(cfg, bh_local, device, seed):
+    """Rank-local synthetic inputs [1, bh_local, N, d] drawn on the device."""
+    import dl_templates_b200 as swa
+    G = cfg["grid"]
+    N = G * G
+    g = torch.Generator(device=device).manual_seed(seed)
+    mk = lambda d: torch.randn((1, bh_local, N, d), generator=g, device=device, dtype=torch.float32).to(cfg["dtype"])
+    q, k, v, do = mk(cfg["d_qk"]), mk(cfg["d_qk"]), mk(cfg["d_v"]), mk(cfg["d_v"])
+    R = cfg["rope_dims"] // 4
+    idx = swa.FusedInplaceRotaryPositionEncoding2D.encode_idx(G, G)
+    if cfg["drop"] > 0:
+        gc = torch.Generator().manual_seed(1000)
+        idx[torch.bernoulli(torch.full((N,), cfg["drop"]), generator=gc).bool()] = -1
+    tab = swa.make_cs_table(R, G, 10000.0)
+    half = (cfg["w"] - 1) // 2
+    return dict(q=q, k=k, v=v, do=do, rope=(idx.to(device), tab.to(device), tab.clone().to(device)),
+                win=(1, G, G, half, half), sm_scale=cfg["d_qk"] ** -0.5)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="target")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--bh-per-gpu", type=int, default=0, help="(batch*head) slices per GPU; 0 = the workload's B*H")
+    ap.add_argument("--kernels", default="auto", choices=["auto", "simt", "tc"], help="kernel family to force")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--verify", action="store_true", help="gather outputs over NCCL and compare rank slices")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    cfg = workload_dims(args.workload)
+    half = (cfg["w"] - 1) // 2
+    dtype_name = {torch.float32: "f32", torch.float16: "f16", torch.bfloat16: "bf16"}[cfg["dtype"]]
+
+    # ---------------------------------------------------------------- reference (CPU) arm
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        steps, warmup = max(1, min(args.steps, 10)), max(1, min(args.warmup, 2))
+        tf, ms, cores, n_slices = run_cpu_reference(cfg, steps, warmup)
+        sample = (f"{n_slices} (batch,head) slice(s) of {args.workload} per step, dense [N,N] mask + SDPA + autograd, "
+                  f"fp32, {steps} steps")
+        print(json.dumps({
+            "impl": "reference", "metric": METRIC, "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus,
+            "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(cfg, args, n_slices, world),
+            "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0,
+        }))
+        return 0
+
+    # ---------------------------------------------------------------- our arm
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (sm_100a); there is no CPU fallback")
+    import dl_templates_b200 as swa
+    from dl_templates_b200 import _lib
+    from dl_templates_b200.workloads import windowed_flops
+
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    import torch.distributed as dist
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    bh_local = args.bh_per_gpu or cfg["B"] * cfg["H"]
+    c = device_case(cfg, bh_local, device, seed=rank)
+    q, k, v, do, rope, win, sm = c["q"], c["k"], c["v"], c["do"], c["rope"], c["win"], c["sm_scale"]
+    impl = args.kernels
+    fwd_f, bwd_f = windowed_flops(bh_local, cfg["grid"] ** 2, 1, half, half, cfg["d_qk"], cfg["d_v"])
+    step_flops = fwd_f + (bwd_f if cfg["bwd"] else 0.0)
+    stream = torch.cuda.current_stream(device)
+
+    names = ["fwd", "delta", "dq", "dkdv"] if cfg["bwd"] else ["fwd"]
+    kernel_ms = {n: [] for n in names}
+
+    def step(record=None):
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)] if record is not None else None
+        if ev:
+            ev[0].record(stream)
+        o, lse = swa.swa_forward(q, k, v, rope, *win, sm, impl=impl)
+        if ev:
+            ev[1].record(stream)
+        if cfg["bwd"]:
+            out = swa_backward_timed(swa, _lib, q, k, v, o, lse, do, rope, win, sm, impl, ev, stream)
+        else:
+            out = (o,)
+        if record is not None:
+            record.append(ev)
+        return out
+
+    def barrier():
+        torch.cuda.synchronize(device)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    swa.check_status()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = _lib.launch_count()
+    rec = []
+    barrier()
+    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_start.record(stream)
+    for _ in range(args.steps):
+        step(rec)
+    t_end.record(stream)
+    barrier()
+    launches = _lib.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    swa.check_status()
+    ms_total = t_start.elapsed_time(t_end)
+    for ev in rec:
+        for i, n in enumerate(names):
+            kernel_ms[n].append(ev[i].elapsed_time(ev[i + 1]))
+    t = torch.tensor([ms_total], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = t.item() / args.steps
+    value = step_flops * world / (ms_step * 1e-3) / 1e12
+
+    # ---------------------------------------------------------------- e2e with host buffers
+    e2e = None
+    if not args.no_e2e:
+        host_in = [x.cpu().pin_memory() for x in (q, k, v, do)]
+        dev_in = [torch.empty_like(x) for x in (q, k, v, do)]
+        n_out = 4 if cfg["bwd"] else 1
+        host_out = [torch.empty_like(x, device="cpu").pin_memory() for x in ((v, q, k, v) if cfg["bwd"] else (v,))]
+
+        def e2e_step():
+            for h, d in zip(host_in, dev_in):
+                d.copy_(h, non_blocking=True)
+            qq, kk, vv, dd = dev_in
+            o, lse = swa.swa_forward(qq, kk, vv, rope, *win, sm, impl=impl)
+            outs = (o,) + (tuple(swa.swa_backward(qq, kk, vv, o, lse, dd, rope, *win, sm, impl=impl))
+                           if cfg["bwd"] else ())
+            for h, d in zip(host_out, outs):
+                h.copy_(d, non_blocking=True)
+
+        e2e_steps = max(2, min(args.steps, 10))
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(e2e_steps):
+            e2e_step()
+        e1.record(stream)
+        barrier()
+        te = torch.tensor([e0.elapsed_time(e1)], device=device, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        ms_e2e = te.item() / e2e_steps
+        e2e = {"value": step_flops * world / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": sum(x.numel() * x.element_size() for x in host_in),
+               "d2h_bytes_per_step": sum(x.numel() * x.element_size() for x in host_out[:n_out]),
+               "ms_per_step": ms_e2e, "steps": e2e_steps}
+        del host_in, dev_in, host_out
+
+    # ---------------------------------------------------------------- optional verification gather
+    verified = None
+    if args.verify and world > 1:
+        from dl_templates_b200.sharding import gather_bh
+        o = step()[0]
+        full = gather_bh(o.float().sum(dim=(2, 3), keepdim=True), bh_local * world)
+        verified = bool(torch.isfinite(full).all().item())
+
+    if world > 1:
+        dist.barrier()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
+
+    # ---------------------------------------------------------------- roofline of the dominant kernel
+    peaks = load_peaks()
+    med = {n: statistics.median(vv_) for n, vv_ in kernel_ms.items()}
+    dom = max(med, key=med.get)
+    # algorithmic FLOPs per launch: the forward's 2 matmuls are F; the backward's 2.5F counts 5
+    # matmuls (S, dP, dV, dQ, dK) once each although the two kernels execute 7; the dQ kernel is
+    # credited with 2 of them (F), the dK/dV kernel with 3 (1.5F).
+    alg = {"fwd": fwd_f, "dq": 1.0 * fwd_f, "dkdv": 1.5 * fwd_f, "delta": 0.0}
+    if dom == "delta":
+        dom = max((n for n in med if n != "delta"), key=med.get)
+    achieved = alg[dom] / (med[dom] * 1e-3) / 1e12
+    peak = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "traffic_per_launch.json")
+    if os.path.exists(tpath):
+        with open(tpath) as f:
+            tj = json.load(f)
+        ent = tj.get(f"{args.workload}:{dom}")
+        if ent:
+            traffic = ent["bytes_per_bh"] * bh_local
+    roofline = {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                "frac": achieved / peak, "traffic": traffic, "peak_source": peaks["_source"] + " (sustained bf16)",
+                "kernel_ms": med,
+                "kernel_share": {n: med[n] / sum(med.values()) for n in med},
+                "kernel_family": {n: swa.selected_impl(q, v, rope, *win, sm, which=w_, impl=impl)
+                                  for n, w_ in (("fwd", 0), ("dq", 1), ("dkdv", 2))}}
+
+    cpu_baseline = None
+    if world == 1 and not args.no_cpu_baseline:
+        tf, ms, cores, n_slices = run_cpu_reference(cfg, steps=3, warmup=1)
+        cpu_baseline = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                        "sample": f"{n_slices} (batch,head) slice(s) of {args.workload} per step, dense [N,N] mask + "
+                                  f"SDPA + autograd, fp32, 3 steps, {ms:.0f} ms/step"}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": dtype_name, "data": "synthetic",
+        "config": workload_config(cfg, args, bh_local, world),
+        "frac_of_bf16_peak": value / world / peaks["bf16_tflops"],
+        "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": int(launches),
+        "clocks": clocks,
+    }
+    if verified is not None:
+        line["verified_gather"] = verified
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def swa_backward_timed(swa, _lib, q, k, v, o, lse, do, rope, win, sm, impl, ev, stream):
+    """swa_backward with an event after each of its three launches (same calls, same order)."""
+    if ev is None:
+        return (o,) + tuple(swa.swa_backward(q, k, v, o, lse, do, rope, *win, sm, impl=impl))
+    import ctypes as C
+    from dl_templates_b200 import tiled_swa as ts
+    B, H, N, _ = q.shape
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    delta = torch.empty((B, H, N), dtype=torch.float32, device=q.device)
+    g = ts._geom(q, v, *win, sm, impl)
+    r = _lib.make_rope(*rope) if rope is not None else None
+    tq, tk, tv, to, tdo, tdq, tdk, tdv = (_lib.tensor4(t) for t in (q, k, v, o, do, dq, dk, dv))
+    st, status = _lib.stream_ptr(q.device), ts._status(q.device).data_ptr()
+    _lib.check(_lib.lib.swa_bwd_delta(C.byref(g), C.byref(to), C.byref(tdo), delta.data_ptr(), st), "delta")
+    ev[2].record(stream)
+    _lib.check(_lib.lib.swa_bwd_dq(C.byref(g), ts._ref(r), C.byref(tq), C.byref(tk), C.byref(tv), C.byref(tdo),
+                                   lse.data_ptr(), delta.data_ptr(), C.byref(tdq), status, st), "dq")
+    ev[3].record(stream)
+    _lib.check(_lib.lib.swa_bwd_dkdv(C.byref(g), ts._ref(r), C.byref(tq), C.byref(tk), C.byref(tv), C.byref(tdo),
+                                     lse.data_ptr(), delta.data_ptr(), C.byref(tdk), C.byref(tdv), status, st), "dkdv")
+    ev[4].record(stream)
+    return o, dq, dk, dv
+
+
+def workload_config(cfg, args, bh_local, world):
+    half = (cfg["w"] - 1) // 2
+    G = cfg["grid"]
+    return {"workload": f"{cfg['name']}: {G}x{G} grid, {cfg['w']}x{cfg['w']} window, d_qk={cfg['d_qk']}, "
+                        f"d_v={cfg['d_v']}, fused RoPE-2D on {cfg['rope_dims']} dims, "
+                        f"{'fwd+bwd' if cfg['bwd'] else 'fwd only'}",
+            "bh_per_gpu": bh_local, "tokens_per_head": G * G, "window": cfg["w"],
+            "parallelism": f"batch*head sharded over {world} GPU(s), no collective",
+            "l2": "inputs larger than L2 (no flush)" if bh_local * G * G * cfg["d_qk"] * 2 > 126e6 else
+                  "inputs smaller than L2 (warm)",
+            "exact_pairs_per_head": exact_pairs(G, half), "counted_pairs_per_head": G * G * cfg["w"] ** 2}
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,104 @@
+// HBM-bound streaming kernels: the softmax-delta preprocess (delta = rowsum(o*do))
+// and the stand-alone in-place RoPE-2D.  Both move each byte once with 16-byte
+// accesses when the layout allows, and fall back to element accesses otherwise.
+#pragma once
+
+#include "common.cuh"
+
+namespace swa {
+
+// ---- delta ------------------------------------------------------------------------------------
+// Vector path (16-bit types, d_v % 8 == 0, unit last stride, 16-byte aligned rows):
+// a group of d_v/8 consecutive threads owns one token, each thread reads 8 elements
+// of o and of do, the group reduces with shuffles.  Groups never straddle a warp
+// because d_v/8 is a power of two <= 32 on this path.
+template <typename T>
+__global__ void __launch_bounds__(256) delta_vec_kernel(View4 o, View4 d_o, float* __restrict__ delta, int H,
+                                                        int64_t N, int dv, int64_t total_rows) {
+  const int tpr = dv >> 3;  // threads per row
+  const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t row = gid / tpr;
+  const int part = (int)(gid - row * tpr);
+  float acc = 0.f;
+  if (row < total_rows) {
+    const int64_t bh = row / N, n = row - bh * N;
+    const int64_t bi = bh / H, hi = bh - bi * H;
+    const uint4 a = *reinterpret_cast<const uint4*>((const T*)o.ptr + bi * o.s0 + hi * o.s1 + n * o.s2 + part * 8);
+    const uint4 b =
+        *reinterpret_cast<const uint4*>((const T*)d_o.ptr + bi * d_o.s0 + hi * d_o.s1 + n * d_o.s2 + part * 8);
+    const T* pa = reinterpret_cast<const T*>(&a);
+    const T* pb = reinterpret_cast<const T*>(&b);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc += to_f(pa[i]) * to_f(pb[i]);
+  }
+  for (int off = tpr >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (row < total_rows && part == 0) delta[row] = acc;
+}
+
+// Element path: one warp per token, any dtype / stride / head dim.
+template <typename T>
+__global__ void __launch_bounds__(256) delta_generic_kernel(View4 o, View4 d_o, float* __restrict__ delta, int H,
+                                                            int64_t N, int dv, int64_t total_rows) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= total_rows) return;
+  const int64_t bh = row / N, n = row - bh * N;
+  const int64_t bi = bh / H, hi = bh - bi * H;
+  const T* po = (const T*)o.ptr + bi * o.s0 + hi * o.s1 + n * o.s2;
+  const T* pd = (const T*)d_o.ptr + bi * d_o.s0 + hi * d_o.s1 + n * d_o.s2;
+  float acc = 0.f;
+  for (int d = lane; d < dv; d += 32) acc += to_f(po[d * o.s3]) * to_f(pd[d * d_o.s3]);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) delta[row] = acc;
+}
+
+// ---- stand-alone RoPE-2D, in place -----------------------------------------------------------
+// x [batch, N, C] with element strides (xs0, xs1, xs2).  One thread rotates VEC
+// consecutive pairs (i .. i+VEC) of one half (row or column) of one token of one
+// batch entry; tokens whose half has a negative index are skipped without
+// touching memory.  blockIdx.y is the batch entry.
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256) rope2d_kernel(T* __restrict__ x, int64_t batch, int64_t N, int64_t xs0,
+                                                     int64_t xs1, int64_t xs2, RopeDev rp, float sign) {
+  const int per_tok = 2 * (rp.R / VEC);  // work items per token: halves x chunks
+  const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t tok = gid / per_tok;
+  const int item = (int)(gid - tok * per_tok);
+  const int64_t bi = blockIdx.y;
+  if (tok >= N || bi >= batch) return;
+  int irow, icol;
+  decode_idx(rp.idx[tok], rp.max_h, rp.max_w, irow, icol);
+  const int half = item / (rp.R / VEC);  // 0 row, 1 col
+  const int i0 = (item - half * (rp.R / VEC)) * VEC;
+  const int pos = half ? icol : irow;
+  if (pos < 0) return;
+  const float* tab = (half ? rp.col_cs : rp.row_cs) + ((int64_t)pos * rp.R + i0) * 2;
+  T* p0 = x + bi * xs0 + tok * xs1 + (int64_t)(2 * half * rp.R + i0) * xs2;
+  T* p1 = p0 + (int64_t)rp.R * xs2;
+  if constexpr (VEC == 1) {
+    const float c = tab[0], s = tab[1] * sign;
+    const float a = to_f(*p0), b = to_f(*p1);
+    *p0 = from_f<T>(a * c - b * s);
+    *p1 = from_f<T>(a * s + b * c);
+  } else {
+    // VEC * sizeof(T) == 16 bytes, unit element stride, 16-byte aligned (checked on the host)
+    uint4 va = *reinterpret_cast<const uint4*>(p0), vb = *reinterpret_cast<const uint4*>(p1);
+    T* ea = reinterpret_cast<T*>(&va);
+    T* eb = reinterpret_cast<T*>(&vb);
+    float cs[2 * VEC];
+#pragma unroll
+    for (int j = 0; j < 2 * VEC; j += 4) *reinterpret_cast<float4*>(cs + j) = *reinterpret_cast<const float4*>(tab + j);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      const float c = cs[2 * j], s = cs[2 * j + 1] * sign;
+      const float a = to_f(ea[j]), b = to_f(eb[j]);
+      ea[j] = from_f<T>(a * c - b * s);
+      eb[j] = from_f<T>(a * s + b * c);
+    }
+    *reinterpret_cast<uint4*>(p0) = va;
+    *reinterpret_cast<uint4*>(p1) = vb;
+  }
+}
+
+}  // namespace swa

@@ -1,0 +1,255 @@
+// C ABI (include/swa2d.h): argument validation, kernel-family selection, launches.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+#include "stream_kernels.cuh"
+#include "swa_simt.cuh"
+#include "swa_tc.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+std::atomic<int64_t> g_launches{0};
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+enum : int {
+  E_NULL = -1, E_DTYPE = -2, E_SHAPE = -3, E_ROPE = -4, E_IMPL = -5, E_LAUNCH = -6, E_STRIDE = -7
+};
+
+int check_geom(const swa_geom_t* g) {
+  if (!g) return fail(E_NULL, "geometry is NULL");
+  if (g->dtype < SWA_F32 || g->dtype > SWA_BF16) return fail(E_DTYPE, "unknown dtype %d", g->dtype);
+  if (g->B <= 0 || g->H <= 0 || g->b_size <= 0 || g->t_height <= 0 || g->t_width <= 0)
+    return fail(E_SHAPE, "B, H, b_size, t_height, t_width must be positive");
+  if (g->row_size < 0 || g->col_size < 0) return fail(E_SHAPE, "window half-sizes must be >= 0");
+  if (g->d_qk <= 0 || g->d_v <= 0 || g->d_qk > 32 * swa::kMaxT || g->d_v > 32 * swa::kMaxT)
+    return fail(E_SHAPE, "head dims must be in [1, %d]", 32 * swa::kMaxT);
+  if ((int64_t)g->t_height * g->t_width * g->b_size > (int64_t)INT32_MAX)
+    return fail(E_SHAPE, "too many tokens per head");
+  if ((int64_t)g->B * g->H > 65535) return fail(E_SHAPE, "B*H exceeds 65535");
+  if (g->impl < SWA_IMPL_AUTO || g->impl > SWA_IMPL_TC) return fail(E_IMPL, "unknown impl %d", g->impl);
+  return 0;
+}
+
+int check_rope(const swa_geom_t* g, const swa_rope_t* r) {
+  if (!r || !r->idx) return 0;
+  if (!r->row_cs || !r->col_cs) return fail(E_ROPE, "rope tables are NULL");
+  if (r->n_rdim <= 0 || 4 * r->n_rdim > g->d_qk)
+    return fail(E_ROPE, "4*n_rdim (%d) must be in [4, d_qk=%d]", 4 * r->n_rdim, g->d_qk);
+  if (r->max_h <= 0 || r->max_w <= 0) return fail(E_ROPE, "rope table lengths must be positive");
+  return 0;
+}
+
+int check_tensor(const swa_tensor_t* t, const char* name) {
+  if (!t || !t->ptr) return fail(E_NULL, "%s is NULL", name);
+  return 0;
+}
+
+int launch_ok(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(E_LAUNCH, "%s launch failed: %s", what, cudaGetErrorString(e));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return 0;
+}
+
+// Runs `body` with T bound to the element type of the call.
+#define SWA_DISPATCH_DTYPE(dtype, ...)                                  \
+  do {                                                                  \
+    switch (dtype) {                                                    \
+      case SWA_F32: { using T = float; __VA_ARGS__; break; }            \
+      case SWA_F16: { using T = __half; __VA_ARGS__; break; }           \
+      default: { using T = __nv_bfloat16; __VA_ARGS__; break; }         \
+    }                                                                   \
+  } while (0)
+
+// Resolve AUTO / reject TC requests the tensor-core kernels cannot serve.
+int resolve_impl(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* const* tensors, int n_tensors,
+                 int which) {
+  const char* why = swa::tc::unsupported_reason(g, rope, tensors, n_tensors, which);
+  if (g->impl == SWA_IMPL_SIMT) return SWA_IMPL_SIMT;
+  if (why == nullptr) return SWA_IMPL_TC;
+  if (g->impl == SWA_IMPL_TC) return fail(E_IMPL, "tensor-core path unavailable: %s", why);
+  return SWA_IMPL_SIMT;
+}
+
+}  // namespace
+
+extern "C" {
+
+int swa_version(void) { return 1; }
+const char* swa_last_error(void) { return g_err; }
+int64_t swa_launch_count(void) { return g_launches.load(); }
+
+int swa_select_impl(const swa_geom_t* g, const swa_rope_t* rope, int32_t which) {
+  if (int e = check_geom(g)) return e;
+  if (int e = check_rope(g, rope)) return e;
+  return resolve_impl(g, rope, nullptr, 0, which);
+}
+
+int swa_fwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
+            const swa_tensor_t* v, const swa_tensor_t* o, float* lse, int32_t* status, void* stream) {
+  if (int e = check_geom(g)) return e;
+  if (int e = check_rope(g, rope)) return e;
+  if (int e = check_tensor(q, "q")) return e;
+  if (int e = check_tensor(k, "k")) return e;
+  if (int e = check_tensor(v, "v")) return e;
+  if (int e = check_tensor(o, "o")) return e;
+  if (!lse) return fail(E_NULL, "lse is NULL");
+  const swa_tensor_t* ts[] = {q, k, v, o};
+  const int impl = resolve_impl(g, rope, ts, 4, 0);
+  if (impl < 0) return impl;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (impl == SWA_IMPL_TC) {
+    int e = swa::tc::launch_fwd(g, rope, q, k, v, o, lse, status, st);
+    if (e) return fail(E_LAUNCH, "tcgen05 forward: %s", swa::tc::last_error());
+    return launch_ok("tcgen05 forward");
+  }
+  const swa::Geom gg = swa::make_geom(g);
+  const swa::RopeDev rp = swa::make_rope(rope);
+  const int N = g->t_height * g->t_width * g->b_size;
+  dim3 grid((N + 7) / 8, g->B * g->H), block(256);
+  SWA_DISPATCH_DTYPE(g->dtype, swa::simt_fwd_kernel<T><<<grid, block, 0, st>>>(
+                                   gg, rp, swa::make_view(q), swa::make_view(k), swa::make_view(v),
+                                   swa::make_view(o), lse));
+  return launch_ok("simt forward");
+}
+
+int swa_bwd_delta(const swa_geom_t* g, const swa_tensor_t* o, const swa_tensor_t* d_o, float* delta, void* stream) {
+  if (int e = check_geom(g)) return e;
+  if (int e = check_tensor(o, "o")) return e;
+  if (int e = check_tensor(d_o, "do")) return e;
+  if (!delta) return fail(E_NULL, "delta is NULL");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t N = (int64_t)g->t_height * g->t_width * g->b_size;
+  const int64_t rows = N * g->B * g->H;
+  const int dv = g->d_v;
+  const int esz = g->dtype == SWA_F32 ? 4 : 2;
+  auto vec_ok = [&](const swa_tensor_t* t) {
+    return t->stride[3] == 1 && ((uintptr_t)t->ptr % 16) == 0 && (t->stride[0] * esz) % 16 == 0 &&
+           (t->stride[1] * esz) % 16 == 0 && (t->stride[2] * esz) % 16 == 0;
+  };
+  const bool pow2 = (dv & (dv - 1)) == 0;
+  if (esz == 2 && pow2 && dv >= 8 && dv <= 256 && vec_ok(o) && vec_ok(d_o)) {
+    const int64_t threads = rows * (dv / 8);
+    const unsigned blocks = (unsigned)((threads + 255) / 256);
+    if (g->dtype == SWA_F16)
+      swa::delta_vec_kernel<__half><<<blocks, 256, 0, st>>>(swa::make_view(o), swa::make_view(d_o), delta, g->H, N,
+                                                            dv, rows);
+    else
+      swa::delta_vec_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(swa::make_view(o), swa::make_view(d_o), delta,
+                                                                   g->H, N, dv, rows);
+    return launch_ok("delta");
+  }
+  const unsigned blocks = (unsigned)((rows + 7) / 8);
+  SWA_DISPATCH_DTYPE(g->dtype, swa::delta_generic_kernel<T><<<blocks, 256, 0, st>>>(
+                                   swa::make_view(o), swa::make_view(d_o), delta, g->H, N, dv, rows));
+  return launch_ok("delta");
+}
+
+int swa_bwd_dq(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
+               const swa_tensor_t* v, const swa_tensor_t* d_o, const float* lse, const float* delta,
+               const swa_tensor_t* dq, int32_t* status, void* stream) {
+  if (int e = check_geom(g)) return e;
+  if (int e = check_rope(g, rope)) return e;
+  if (int e = check_tensor(q, "q")) return e;
+  if (int e = check_tensor(k, "k")) return e;
+  if (int e = check_tensor(v, "v")) return e;
+  if (int e = check_tensor(d_o, "do")) return e;
+  if (int e = check_tensor(dq, "dq")) return e;
+  if (!lse || !delta) return fail(E_NULL, "lse/delta is NULL");
+  const swa_tensor_t* ts[] = {q, k, v, d_o, dq};
+  const int impl = resolve_impl(g, rope, ts, 5, 1);
+  if (impl < 0) return impl;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (impl == SWA_IMPL_TC) {
+    int e = swa::tc::launch_dq(g, rope, q, k, v, d_o, lse, delta, dq, status, st);
+    if (e) return fail(E_LAUNCH, "tcgen05 dq: %s", swa::tc::last_error());
+    return launch_ok("tcgen05 dq");
+  }
+  const swa::Geom gg = swa::make_geom(g);
+  const swa::RopeDev rp = swa::make_rope(rope);
+  const int N = g->t_height * g->t_width * g->b_size;
+  dim3 grid((N + 7) / 8, g->B * g->H), block(256);
+  SWA_DISPATCH_DTYPE(g->dtype, swa::simt_dq_kernel<T><<<grid, block, 0, st>>>(
+                                   gg, rp, swa::make_view(q), swa::make_view(k), swa::make_view(v),
+                                   swa::make_view(d_o), lse, delta, swa::make_view(dq)));
+  return launch_ok("simt dq");
+}
+
+int swa_bwd_dkdv(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
+                 const swa_tensor_t* v, const swa_tensor_t* d_o, const float* lse, const float* delta,
+                 const swa_tensor_t* dk, const swa_tensor_t* dv, int32_t* status, void* stream) {
+  if (int e = check_geom(g)) return e;
+  if (int e = check_rope(g, rope)) return e;
+  if (int e = check_tensor(q, "q")) return e;
+  if (int e = check_tensor(k, "k")) return e;
+  if (int e = check_tensor(v, "v")) return e;
+  if (int e = check_tensor(d_o, "do")) return e;
+  if (int e = check_tensor(dk, "dk")) return e;
+  if (int e = check_tensor(dv, "dv")) return e;
+  if (!lse || !delta) return fail(E_NULL, "lse/delta is NULL");
+  const swa_tensor_t* ts[] = {q, k, v, d_o, dk, dv};
+  const int impl = resolve_impl(g, rope, ts, 6, 2);
+  if (impl < 0) return impl;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (impl == SWA_IMPL_TC) {
+    int e = swa::tc::launch_dkdv(g, rope, q, k, v, d_o, lse, delta, dk, dv, status, st);
+    if (e) return fail(E_LAUNCH, "tcgen05 dkdv: %s", swa::tc::last_error());
+    return launch_ok("tcgen05 dkdv");
+  }
+  const swa::Geom gg = swa::make_geom(g);
+  const swa::RopeDev rp = swa::make_rope(rope);
+  const int N = g->t_height * g->t_width * g->b_size;
+  dim3 grid((N + 7) / 8, g->B * g->H), block(256);
+  SWA_DISPATCH_DTYPE(g->dtype, swa::simt_dkdv_kernel<T><<<grid, block, 0, st>>>(
+                                   gg, rp, swa::make_view(q), swa::make_view(k), swa::make_view(v),
+                                   swa::make_view(d_o), lse, delta, swa::make_view(dk), swa::make_view(dv)));
+  return launch_ok("simt dkdv");
+}
+
+int rope2d_apply(int32_t dtype, void* x, int64_t batch, int64_t n_tokens, int32_t n_dim, const int64_t* xs,
+                 const swa_rope_t* rope, int32_t inverse, void* stream) {
+  if (dtype < SWA_F32 || dtype > SWA_BF16) return fail(E_DTYPE, "unknown dtype %d", dtype);
+  if (!x || !xs) return fail(E_NULL, "x / strides are NULL");
+  if (!rope || !rope->idx || !rope->row_cs || !rope->col_cs) return fail(E_ROPE, "rope index / tables are NULL");
+  if (rope->n_rdim <= 0 || 4 * rope->n_rdim > n_dim)
+    return fail(E_ROPE, "4*n_rdim (%d) must be in [4, n_dim=%d]", 4 * rope->n_rdim, n_dim);
+  if (rope->max_h <= 0 || rope->max_w <= 0) return fail(E_ROPE, "rope table lengths must be positive");
+  if (batch <= 0 || n_tokens <= 0) return fail(E_SHAPE, "batch and n_tokens must be positive");
+  if (batch > 65535) return fail(E_SHAPE, "batch exceeds 65535");
+  cudaStream_t st = (cudaStream_t)stream;
+  const swa::RopeDev rp = swa::make_rope(rope);
+  const float sign = inverse ? -1.f : 1.f;
+  const int esz = dtype == SWA_F32 ? 4 : 2;
+  const int vec = 16 / esz;
+  const bool vec_ok = xs[2] == 1 && rp.R % vec == 0 && ((uintptr_t)x % 16) == 0 && (xs[0] * esz) % 16 == 0 &&
+                      (xs[1] * esz) % 16 == 0 && ((uintptr_t)rp.row_cs % 16) == 0 && ((uintptr_t)rp.col_cs % 16) == 0;
+  const int per_tok = 2 * (vec_ok ? rp.R / vec : rp.R);
+  const int64_t items = n_tokens * per_tok;
+  dim3 grid((unsigned)((items + 255) / 256), (unsigned)batch), block(256);
+  if (vec_ok) {
+    if (dtype == SWA_F32)
+      swa::rope2d_kernel<float, 4><<<grid, block, 0, st>>>((float*)x, batch, n_tokens, xs[0], xs[1], xs[2], rp, sign);
+    else if (dtype == SWA_F16)
+      swa::rope2d_kernel<__half, 8><<<grid, block, 0, st>>>((__half*)x, batch, n_tokens, xs[0], xs[1], xs[2], rp, sign);
+    else
+      swa::rope2d_kernel<__nv_bfloat16, 8><<<grid, block, 0, st>>>((__nv_bfloat16*)x, batch, n_tokens, xs[0], xs[1],
+                                                                   xs[2], rp, sign);
+  } else {
+    SWA_DISPATCH_DTYPE(dtype, swa::rope2d_kernel<T, 1><<<grid, block, 0, st>>>((T*)x, batch, n_tokens, xs[0], xs[1],
+                                                                              xs[2], rp, sign));
+  }
+  return launch_ok("rope2d");
+}
+
+}  // extern "C"

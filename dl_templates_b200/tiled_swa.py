@@ -1,0 +1,184 @@
+"""Tiled 2D sliding-window attention: the call surface of the reference's
+``src/tiled_swa.py`` on top of the sm_100a C-ABI library.
+
+Same names and argument order as the reference:
+
+  ``TiledSwa.apply(q, k, v, b_size, t_height, t_width, row_size, col_size, sm_scale)``   (src/tiled_swa.py:604)
+  ``tiled_swa_fwd(q, k, v, b_size, t_height, t_width, row_size, col_size, sm_scale=1.0)`` (src/tiled_swa.py:564)
+
+plus the composed entry the reference does not have, which rotates q and k on
+chip instead of in two extra passes over HBM:
+
+  ``TiledSwaRope2D.apply(q, k, v, idx, row_cs_buffer, col_cs_buffer, b_size, t_height,
+  t_width, row_size, col_size, sm_scale)``
+
+Layout: ``q, k [B,H,N,d_qk]``, ``v, o [B,H,N,d_v]``, ``N = t_height*t_width*b_size``,
+token ``n = (tile_row*t_width + tile_col)*b_size + s``; a query attends every token
+of every tile within ``row_size`` rows and ``col_size`` columns of its own tile,
+truncated at the grid border (src/tiled_swa.py:76-79,212-214,704-710).
+
+Departures from reference quirks (none changes the mathematics): outputs take the
+dtype and device of ``q`` (the reference hard-codes fp16 on the default device,
+src/tiled_swa.py:608-609); ``dq`` comes back in ``q.dtype`` (reference: fp32,
+src/tiled_swa.py:656); backward works for every ``b_size`` (reference raises
+below 16, src/tiled_swa.py:660-661); the saved softmax statistic is fp32.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+_status_words = {}
+
+
+def _status(device: torch.device) -> torch.Tensor:
+    """Per-device int32[4] word the tensor-core kernels write to when one of their
+    bounded waits gives up; stays zero in normal operation."""
+    key = (device.type, device.index)
+    if key not in _status_words:
+        _status_words[key] = torch.zeros(4, dtype=torch.int32, device=device)
+    return _status_words[key]
+
+
+def check_status(device=None) -> None:
+    """Synchronise and raise if any kernel reported a timed-out wait."""
+    for key, word in _status_words.items():
+        vals = word.cpu().tolist()
+        if vals[0] != 0:
+            word.zero_()
+            raise RuntimeError(f"swa2d kernel reported a bounded-wait timeout on {key}: status={vals}")
+
+
+def _check_inputs(q, k, v, b_size, t_height, t_width):
+    if not (q.is_cuda and k.is_cuda and v.is_cuda):
+        raise RuntimeError("dl_templates_b200 runs on CUDA tensors only (sm_100a); there is no CPU path")
+    if q.dim() != 4 or k.shape != q.shape or v.shape[:3] != q.shape[:3]:
+        raise ValueError("expected q,k [B,H,N,d_qk] and v [B,H,N,d_v]")
+    if q.dtype != k.dtype or q.dtype != v.dtype:
+        raise TypeError("q, k, v must share a dtype")
+    assert q.shape[2] == t_height * t_width * b_size, "seqlen should match image size"
+
+
+def _geom(q, v, b_size, t_height, t_width, row_size, col_size, sm_scale, impl):
+    B, H, N, d_qk = q.shape
+    return _lib.make_geom(q.dtype, B, H, b_size, t_height, t_width, row_size, col_size, d_qk, v.shape[-1], sm_scale,
+                          impl)
+
+
+def _ref(x):
+    return C.byref(x) if x is not None else None
+
+
+def swa_forward(q, k, v, rope, b_size, t_height, t_width, row_size, col_size, sm_scale, impl="auto"):
+    """Launch the forward kernel; returns ``(o, lse)`` with ``lse`` fp32 ``[B,H,N]`` in
+    the base-2 domain.  ``rope`` is ``None`` or ``(idx, row_cs, col_cs)``."""
+    _check_inputs(q, k, v, b_size, t_height, t_width)
+    B, H, N, _ = q.shape
+    with torch.cuda.device(q.device):
+        o = torch.empty((B, H, N, v.shape[-1]), dtype=q.dtype, device=q.device)
+        lse = torch.empty((B, H, N), dtype=torch.float32, device=q.device)
+        g = _geom(q, v, b_size, t_height, t_width, row_size, col_size, sm_scale, impl)
+        r = _lib.make_rope(*rope) if rope is not None else None
+        tq, tk, tv, to = (_lib.tensor4(t) for t in (q, k, v, o))
+        code = _lib.lib.swa_fwd(C.byref(g), _ref(r), C.byref(tq), C.byref(tk), C.byref(tv), C.byref(to),
+                                lse.data_ptr(), _status(q.device).data_ptr(), _lib.stream_ptr(q.device))
+    _lib.check(code, "swa_fwd")
+    if os.environ.get("SWA_DEBUG_SYNC"):
+        check_status()
+    return o, lse
+
+
+def swa_backward(q, k, v, o, lse, do, rope, b_size, t_height, t_width, row_size, col_size, sm_scale, impl="auto"):
+    """Launch delta, dQ and dK/dV kernels; returns ``(dq, dk, dv)`` in the input dtype
+    (gradients of the un-rotated q and k when ``rope`` is given)."""
+    B, H, N, _ = q.shape
+    with torch.cuda.device(q.device):
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        delta = torch.empty((B, H, N), dtype=torch.float32, device=q.device)
+        g = _geom(q, v, b_size, t_height, t_width, row_size, col_size, sm_scale, impl)
+        r = _lib.make_rope(*rope) if rope is not None else None
+        tq, tk, tv, to, tdo, tdq, tdk, tdv = (_lib.tensor4(t) for t in (q, k, v, o, do, dq, dk, dv))
+        st, status = _lib.stream_ptr(q.device), _status(q.device).data_ptr()
+        _lib.check(_lib.lib.swa_bwd_delta(C.byref(g), C.byref(to), C.byref(tdo), delta.data_ptr(), st),
+                   "swa_bwd_delta")
+        _lib.check(_lib.lib.swa_bwd_dq(C.byref(g), _ref(r), C.byref(tq), C.byref(tk), C.byref(tv), C.byref(tdo),
+                                       lse.data_ptr(), delta.data_ptr(), C.byref(tdq), status, st), "swa_bwd_dq")
+        _lib.check(_lib.lib.swa_bwd_dkdv(C.byref(g), _ref(r), C.byref(tq), C.byref(tk), C.byref(tv), C.byref(tdo),
+                                         lse.data_ptr(), delta.data_ptr(), C.byref(tdk), C.byref(tdv), status, st),
+                   "swa_bwd_dkdv")
+    if os.environ.get("SWA_DEBUG_SYNC"):
+        check_status()
+    return dq, dk, dv
+
+
+def selected_impl(q, v, rope, b_size, t_height, t_width, row_size, col_size, sm_scale=1.0, which=0, impl="auto"):
+    """'tc' or 'simt': the kernel family a call with these shapes would run."""
+    g = _geom(q, v, b_size, t_height, t_width, row_size, col_size, sm_scale, impl)
+    r = _lib.make_rope(*rope) if rope is not None else None
+    code = _lib.lib.swa_select_impl(C.byref(g), _ref(r), which)
+    if code < 0:
+        _lib.check(code, "swa_select_impl")
+    return {_lib.IMPL_SIMT: "simt", _lib.IMPL_TC: "tc"}[code]
+
+
+def tiled_swa_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, b_size: int, t_height: int, t_width: int,
+                  row_size: int, col_size: int, sm_scale: float = 1.0) -> torch.Tensor:
+    """Forward only, no autograd graph (src/tiled_swa.py:564-600)."""
+    return swa_forward(q, k, v, None, b_size, t_height, t_width, row_size, col_size, sm_scale)[0]
+
+
+class TiledSwa(torch.autograd.Function):
+    """``TiledSwa.apply(q, k, v, b_size, t_height, t_width, row_size, col_size, sm_scale)``
+    -- src/tiled_swa.py:602-689."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, b_size: int, t_height: int, t_width: int, row_size: int, col_size: int,
+                sm_scale: float):
+        o, lse = swa_forward(q, k, v, None, b_size, t_height, t_width, row_size, col_size, sm_scale)
+        ctx.save_for_backward(q, k, v, lse, o)
+        ctx.win = (b_size, t_height, t_width, row_size, col_size, sm_scale)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, lse, o = ctx.saved_tensors
+        dq, dk, dv = swa_backward(q, k, v, o, lse, do, None, *ctx.win)
+        return dq, dk, dv, None, None, None, None, None, None
+
+
+class TiledSwaRope2D(torch.autograd.Function):
+    """RoPE-2D on q and k fused into the attention kernels.
+
+    Equivalent to ``TiledSwa.apply(rope(q, idx), rope(k, idx), v, ...)`` with
+    ``rope`` = ``RotaryPE2D`` (src/fused_rope2d.py:124-168), but q and k are read
+    un-rotated, rotated on chip, and left unmodified; ``dq``/``dk`` are gradients
+    of the un-rotated tensors.  ``idx`` may be ``None`` (no rotation).
+    """
+
+    @staticmethod
+    def forward(ctx, q, k, v, idx: Optional[torch.Tensor], row_cs_buffer, col_cs_buffer, b_size: int,
+                t_height: int, t_width: int, row_size: int, col_size: int, sm_scale: float):
+        rope = None if idx is None else (idx, row_cs_buffer, col_cs_buffer)
+        if rope is not None:
+            assert idx.shape[0] == q.shape[2]
+            assert row_cs_buffer.shape[1] == col_cs_buffer.shape[1]
+        o, lse = swa_forward(q, k, v, rope, b_size, t_height, t_width, row_size, col_size, sm_scale)
+        if rope is None:
+            ctx.save_for_backward(q, k, v, lse, o)
+        else:
+            ctx.save_for_backward(q, k, v, lse, o, idx, row_cs_buffer, col_cs_buffer)
+        ctx.win = (b_size, t_height, t_width, row_size, col_size, sm_scale)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        saved = ctx.saved_tensors
+        q, k, v, lse, o = saved[:5]
+        rope = tuple(saved[5:8]) if len(saved) == 8 else None
+        dq, dk, dv = swa_backward(q, k, v, o, lse, do, rope, *ctx.win)
+        return (dq, dk, dv) + (None,) * 9

@@ -1,0 +1,119 @@
+/*
+ * swa2d.h -- C ABI of the B200 (sm_100a) tiled 2D sliding-window attention library.
+ *
+ * The library is the device side of the call surface of the reference project's
+ * src/tiled_swa.py and src/fused_rope2d.py.  Each entry point below replaces one
+ * Triton launch site of the reference; the Python classes of the same names
+ * (TiledSwa, RotaryPE2D, ...) in dl_templates_b200/ bind these with ctypes.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer of the current CUDA device; the caller
+ *     owns all memory, the library allocates no device memory;
+ *   - tensors are described by a pointer and four ELEMENT strides, shape
+ *     [B, H, N, d] with N = t_height * t_width * b_size and token
+ *     n = (tile_row * t_width + tile_col) * b_size + s   (src/tiled_swa.py:104,216);
+ *   - work is enqueued on `stream` and the call returns without synchronising;
+ *   - return value 0 = enqueued; negative = argument rejected before any launch
+ *     (swa_last_error() returns the message for the calling thread);
+ *   - `status` is an optional device int32[4] word the tensor-core kernels write
+ *     to when one of their bounded waits gives up (0 = ok); may be NULL;
+ *   - lse is the base-2 logsumexp of (sm_scale * log2(e) * q.k) over the window,
+ *     fp32 [B,H,N] contiguous (the reference keeps the same quantity in fp16,
+ *     src/tiled_swa.py:35,129).
+ */
+#ifndef SWA2D_H_
+#define SWA2D_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum { SWA_F32 = 0, SWA_F16 = 1, SWA_BF16 = 2 } swa_dtype_t;
+
+/* which implementation a call may use */
+typedef enum {
+  SWA_IMPL_AUTO = 0,  /* tensor-core kernels when the shape qualifies, else the SIMT kernels */
+  SWA_IMPL_SIMT = 1,  /* fp32-accumulate CUDA-core kernels (every dtype, every shape)        */
+  SWA_IMPL_TC   = 2   /* tcgen05 kernels only; shapes they do not cover are rejected          */
+} swa_impl_t;
+
+typedef struct {
+  void*   ptr;
+  int64_t stride[4]; /* element strides of [B, H, N, d] */
+} swa_tensor_t;
+
+/* Geometry shared by all attention entry points (argument order of
+ * TiledSwa.forward, src/tiled_swa.py:604). */
+typedef struct {
+  int32_t dtype;      /* swa_dtype_t of q, k, v, o, do, dq, dk, dv */
+  int32_t B, H;
+  int32_t b_size;     /* tokens per grid cell ("tile")                       */
+  int32_t t_height, t_width;
+  int32_t row_size, col_size; /* window half-extent in tiles; truncated at the border */
+  int32_t d_qk, d_v;
+  float   sm_scale;
+  int32_t impl;       /* swa_impl_t */
+} swa_geom_t;
+
+/* Optional fused RoPE-2D (src/fused_rope2d.py:204-225 semantics).  idx == NULL
+ * disables it.  idx[n] = (row << 16) | col, each half an int16, a negative half
+ * leaves that half of the token un-rotated.  Tables are fp32 [max, n_rdim, 2]
+ * (cos, sin) contiguous.  Only the first 4*n_rdim dims of q/k are rotated. */
+typedef struct {
+  const int32_t* idx;     /* [N] */
+  const float*   row_cs;  /* [max_h, n_rdim, 2] */
+  const float*   col_cs;  /* [max_w, n_rdim, 2] */
+  int32_t n_rdim, max_h, max_w;
+} swa_rope_t;
+
+/* Forward: o = softmax(sm_scale * rope(q) rope(k)^T + window mask) v, and lse.
+ * Replaces the tiled_swa_fwd_kernel / tiled_swa_fwd_large_kernel launches of
+ * TiledSwa.forward (src/tiled_swa.py:611-637); with rope != NULL also the two
+ * rope2d_fwd_kernel launches on q and k that precede it (src/fused_rope2d.py:138). */
+int swa_fwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
+            const swa_tensor_t* v, const swa_tensor_t* o, float* lse, int32_t* status, void* stream);
+
+/* delta[b,h,n] = sum_d o*do (fp32).  Replaces tiled_swa_bwd_preprocess_kernel
+ * (src/tiled_swa.py:253-282, launch at :666). */
+int swa_bwd_delta(const swa_geom_t* g, const swa_tensor_t* o, const swa_tensor_t* d_o, float* delta, void* stream);
+
+/* dq (gradient of the UN-rotated q when rope != NULL).  Replaces phase 2 of
+ * tiled_swa_bwd_large_kernel_decoupled_q (src/tiled_swa.py:520-562) plus the
+ * rope2d_bwd_kernel launch on dq (src/fused_rope2d.py:163). */
+int swa_bwd_dq(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
+               const swa_tensor_t* v, const swa_tensor_t* d_o, const float* lse, const float* delta,
+               const swa_tensor_t* dq, int32_t* status, void* stream);
+
+/* dk (of the UN-rotated k) and dv.  Replaces phase 1 of
+ * tiled_swa_bwd_large_kernel_decoupled_q (src/tiled_swa.py:475-518) plus the
+ * rope2d_bwd_kernel launch on dk. */
+int swa_bwd_dkdv(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
+                 const swa_tensor_t* v, const swa_tensor_t* d_o, const float* lse, const float* delta,
+                 const swa_tensor_t* dk, const swa_tensor_t* dv, int32_t* status, void* stream);
+
+/* Stand-alone in-place RoPE-2D on x [batch, N, C] (element strides xs[3]).
+ * inverse = 0 replaces rope2d_fwd_kernel (src/fused_rope2d.py:24-72), inverse = 1
+ * replaces rope2d_bwd_kernel (src/fused_rope2d.py:74-122).  A negative index half
+ * means identity for that half, as rope2d_ref defines it (src/fused_rope2d.py:215-219). */
+int rope2d_apply(int32_t dtype, void* x, int64_t batch, int64_t n_tokens, int32_t n_dim, const int64_t* xs,
+                 const swa_rope_t* rope, int32_t inverse, void* stream);
+
+/* Which kernel family swa_fwd / swa_bwd_dq / swa_bwd_dkdv would run for this
+ * geometry: SWA_IMPL_SIMT or SWA_IMPL_TC (negative = rejected). `which`: 0 fwd, 1 dq, 2 dkdv. */
+int swa_select_impl(const swa_geom_t* g, const swa_rope_t* rope, int32_t which);
+
+/* Number of kernel launches this library has enqueued from the calling process. */
+int64_t swa_launch_count(void);
+
+/* Message of the last rejected call on this thread ("" if none). */
+const char* swa_last_error(void);
+
+/* ABI version of this header. */
+int swa_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SWA2D_H_ */

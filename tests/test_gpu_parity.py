@@ -1,0 +1,180 @@
+"""GPU parity: the CUDA path (through the Python surface over the C ABI) against
+the CPU oracle and the stored reference outputs.
+
+Ground truth for bf16/fp16 is the oracle evaluated in fp32 on the rounded inputs.
+Tolerances: max-abs 2e-2 and mean-rel 5e-3 for bf16/fp16, 1e-4 for fp32.
+"""
+import pytest
+import torch
+
+from conftest import SWA_GOLDEN_CASES, load_golden
+from oracle import swa_oracle as orc
+from swa_cases import CONFIGS, make_case, tolerances
+
+import dl_templates_b200 as swa
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def run_gpu(q, k, v, do, rope, win, sm_scale, impl="auto"):
+    """Forward (+ backward when ``do`` is given) through the ABI; returns CPU tensors."""
+    qd, kd, vd = (t.to(DEV) for t in (q, k, v))
+    rd = None if rope is None else tuple(t.to(DEV) for t in rope)
+    o, lse = swa.swa_forward(qd, kd, vd, rd, *win, sm_scale, impl=impl)
+    outs = [o]
+    if do is not None:
+        outs += list(swa.swa_backward(qd, kd, vd, o, lse, do.to(DEV), rd, *win, sm_scale, impl=impl))
+    swa.check_status()
+    return [t.float().cpu() for t in outs], lse.cpu()
+
+
+def assert_close(got, want, dtype, names=("o", "dq", "dk", "dv"), what=""):
+    ma, mr = tolerances(dtype)
+    for g, w, n in zip(got, want, names):
+        assert torch.isfinite(g).all(), f"{what} {n}: non-finite values"
+        a, r = orc.max_abs(g, w), orc.mean_rel(g, w)
+        assert a < ma and r < mr, f"{what} {n}: max_abs={a:.3e} (<{ma}) mean_rel={r:.3e} (<{mr})"
+
+
+@pytest.mark.parametrize("impl", ["auto", "simt"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("name", SWA_GOLDEN_CASES)
+def test_golden_cases(name, dtype, impl):
+    g = load_golden(name)
+    m = g["meta"]
+    win = (m["b_size"], m["t_height"], m["t_width"], m["row_size"], m["col_size"])
+    q, k, v, do = (g[x].to(dtype) for x in ("q", "k", "v", "do"))
+    rope = (g["idx"], g["row_cs"], g["col_cs"]) if "idx" in g else None
+    got, _ = run_gpu(q, k, v, do, rope, win, g["sm_scale"], impl)
+    if dtype == torch.float32:
+        want = [g["o"], g["dq"], g["dk"], g["dv"]]      # the reference's own stored outputs
+    else:
+        want = orc.fused_ref(q.float(), k.float(), v.float(), do.float(), *(rope or (None, None, None)), *win,
+                             g["sm_scale"])
+    assert_close(got, want, dtype, what=f"{name}/{impl}")
+
+
+def _config_check(cfg_name, B, H, impl="auto", windowed=False):
+    cfg = CONFIGS[cfg_name]
+    c = make_case(cfg, B=B, H=H)
+    rope = (c["idx"], c["row_cs"], c["col_cs"])
+    do = c["do"] if cfg["bwd"] else None
+    got, lse = run_gpu(c["q"], c["k"], c["v"], do, rope, c["win"], c["sm_scale"], impl)
+    f = lambda t: None if t is None else t.float()
+    want = orc.fused_ref(f(c["q"]), f(c["k"]), f(c["v"]), f(do), *rope, *c["win"], c["sm_scale"], windowed=windowed)
+    if do is None:
+        want = [want]
+    assert_close(got, want, cfg["dtype"], what=f"{cfg_name}/{impl}")
+    return got
+
+
+def test_config1_fp32_full():
+    _config_check("cfg1", None, None)
+
+
+def test_config2_bf16_forward_full():
+    _config_check("cfg2", None, None)
+
+
+def test_config3_fp16_dropped_idx():
+    # 8 of the 96 (batch, head) slices: the dense oracle is O(N^2) per slice
+    _config_check("cfg3", 2, 4)
+
+
+def test_config4_mixed_dims_slices():
+    _config_check("cfg4", 1, 2, windowed=True)
+
+
+def test_target_config_slices():
+    _config_check("target", 1, 2, windowed=True)
+
+
+def test_lse_matches_oracle():
+    c = make_case(CONFIGS["cfg1"])
+    rope = (c["idx"], c["row_cs"], c["col_cs"])
+    _, lse = run_gpu(c["q"], c["k"], c["v"], None, rope, c["win"], c["sm_scale"])
+    qr = orc.rope2d_ref(c["q"], c["idx"], c["row_cs"], c["col_cs"])
+    kr = orc.rope2d_ref(c["k"], c["idx"], c["row_cs"], c["col_cs"])
+    _, want = orc.tiled_swa_ref(qr, kr, c["v"], *c["win"], c["sm_scale"], return_lse=True)
+    assert orc.max_abs(lse * 0.6931471805599453, want) < 1e-4
+
+
+def test_autograd_surface_matches_reference_order():
+    """TiledSwa.apply / TiledSwaRope2D.apply / RotaryPE2D.apply compose as in the reference."""
+    g = load_golden("g5x7_r2c1_partial_rope_drop")
+    m = g["meta"]
+    win = (m["b_size"], m["t_height"], m["t_width"], m["row_size"], m["col_size"])
+    idx, rcs, ccs = (g[x].to(DEV) for x in ("idx", "row_cs", "col_cs"))
+    want = [g["o"], g["dq"], g["dk"], g["dv"]]
+    # (a) fused entry
+    q, k, v = (g[x].to(DEV).requires_grad_(True) for x in ("q", "k", "v"))
+    o = swa.TiledSwaRope2D.apply(q, k, v, idx, rcs, ccs, *win, g["sm_scale"])
+    o.backward(g["do"].to(DEV))
+    assert_close([t.detach().cpu() for t in (o, q.grad, k.grad, v.grad)], want, torch.float32, what="fused")
+    # (b) the reference's own composition: in-place RoPE on q and k, then TiledSwa
+    q, k, v = (g[x].to(DEV).requires_grad_(True) for x in ("q", "k", "v"))
+    B, H, N, D = q.shape
+    qr = swa.RotaryPE2D.apply(q.clone().reshape(B * H, N, D), idx, rcs, ccs).reshape(B, H, N, D)
+    kr = swa.RotaryPE2D.apply(k.clone().reshape(B * H, N, D), idx, rcs, ccs).reshape(B, H, N, D)
+    o = swa.TiledSwa.apply(qr, kr, v, *win, g["sm_scale"])
+    o.backward(g["do"].to(DEV))
+    assert_close([t.detach().cpu() for t in (o, q.grad, k.grad, v.grad)], want, torch.float32, what="composed")
+    swa.check_status()
+
+
+def test_strided_inputs():
+    """q, k, v as strided views of one packed projection output [B, N, 3, H, d]."""
+    torch.manual_seed(0)
+    B, H, G, d = 2, 3, 12, 64
+    N = G * G
+    packed = torch.randn(B, N, 3, H, d).to(torch.bfloat16)
+    q, k, v = (packed[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+    assert not q.is_contiguous()
+    do = torch.randn(B, H, N, d).to(torch.bfloat16)
+    win = (1, G, G, 2, 2)
+    pd = packed.to(DEV)
+    qd, kd, vd = (pd[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+    o, lse = swa.swa_forward(qd, kd, vd, None, *win, 0.125)
+    dq, dk, dv = swa.swa_backward(qd, kd, vd, o, lse, do.to(DEV), None, *win, 0.125)
+    swa.check_status()
+    want = orc.fused_ref(q.float(), k.float(), v.float(), do.float(), None, None, None, *win, 0.125)
+    assert_close([t.float().cpu() for t in (o, dq, dk, dv)], want, torch.bfloat16, what="strided")
+
+
+def test_bitwise_determinism():
+    c = make_case(CONFIGS["cfg2"], B=1, H=2)
+    rope = (c["idx"], c["row_cs"], c["col_cs"])
+    a, _ = run_gpu(c["q"], c["k"], c["v"], c["do"], rope, c["win"], c["sm_scale"])
+    b, _ = run_gpu(c["q"], c["k"], c["v"], c["do"], rope, c["win"], c["sm_scale"])
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
+
+
+def test_rows_of_p_sum_to_one_and_linearity_in_v():
+    """Size-independent properties on a full-size grid: with v = 1 the output is 1;
+    the output is linear in v."""
+    cfg = CONFIGS["target"]
+    c = make_case(cfg, B=1, H=4)
+    rope = tuple(t.to(DEV) for t in (c["idx"], c["row_cs"], c["col_cs"]))
+    q, k, v = (c[x].to(DEV) for x in ("q", "k", "v"))
+    ones = torch.ones_like(v)
+    o1, _ = swa.swa_forward(q, k, ones, rope, *c["win"], c["sm_scale"])
+    assert (o1.float() - 1).abs().max().item() < 1e-2
+    v2 = torch.roll(v, 1, dims=2)
+    oa, _ = swa.swa_forward(q, k, v, rope, *c["win"], c["sm_scale"])
+    ob, _ = swa.swa_forward(q, k, v2, rope, *c["win"], c["sm_scale"])
+    oc, _ = swa.swa_forward(q, k, (2 * v.float() + v2.float()).to(v.dtype), rope, *c["win"], c["sm_scale"])
+    swa.check_status()
+    assert (oc.float() - (2 * oa.float() + ob.float())).abs().max().item() < 6e-2
+
+
+def test_batch_head_slices_are_independent():
+    """A sharded run must equal the unsharded one bitwise: computing slices [2:4) alone
+    gives the same bits as those slices of the full call."""
+    c = make_case(CONFIGS["cfg2"], B=1, H=4)
+    rope = (c["idx"], c["row_cs"], c["col_cs"])
+    full, _ = run_gpu(c["q"], c["k"], c["v"], c["do"], rope, c["win"], c["sm_scale"])
+    part, _ = run_gpu(c["q"][:, 2:4], c["k"][:, 2:4], c["v"][:, 2:4], c["do"][:, 2:4], rope, c["win"], c["sm_scale"])
+    for x, y in zip(full, part):
+        assert torch.equal(x[:, 2:4], y)
