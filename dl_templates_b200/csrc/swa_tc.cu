@@ -1,9 +1,224 @@
-// placeholder until the tcgen05 kernels land
+// Host side of the tcgen05 kernels: shape qualification, tile planning, TMA tensor
+// maps and launches.
+#include <cudaTypedefs.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <type_traits>
+
 #include "swa_tc.cuh"
-namespace swa { namespace tc {
-const char* unsupported_reason(const swa_geom_t*, const swa_rope_t*, const swa_tensor_t* const*, int, int) { return "tensor-core kernels not built"; }
-const char* last_error() { return ""; }
-int launch_fwd(const swa_geom_t*, const swa_rope_t*, const swa_tensor_t*, const swa_tensor_t*, const swa_tensor_t*, const swa_tensor_t*, float*, int32_t*, cudaStream_t) { return -1; }
-int launch_dq(const swa_geom_t*, const swa_rope_t*, const swa_tensor_t*, const swa_tensor_t*, const swa_tensor_t*, const swa_tensor_t*, const float*, const float*, const swa_tensor_t*, int32_t*, cudaStream_t) { return -1; }
-int launch_dkdv(const swa_geom_t*, const swa_rope_t*, const swa_tensor_t*, const swa_tensor_t*, const swa_tensor_t*, const swa_tensor_t*, const float*, const float*, const swa_tensor_t*, const swa_tensor_t*, int32_t*, cudaStream_t) { return -1; }
-}}
+#include "swa_tc_fwd.cuh"
+
+namespace swa {
+namespace tc {
+
+namespace {
+
+thread_local char g_tc_err[256] = "";
+constexpr uint32_t kSmemLimit = 227 * 1024;
+
+PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+  });
+  return fn;
+}
+
+// 5-D map over a [B, H, N, d] tensor seen as (d, token column, grid row, head, batch); box =
+// (64 elements, box_cols, box_rows, 1, 1), 128-byte swizzle, zero fill outside the tensor.
+bool make_map(CUtensorMap* m, const swa_tensor_t* t, const swa_geom_t* g, int d, int box_cols, int box_rows) {
+  auto fn = encode_fn();
+  if (!fn) {
+    snprintf(g_tc_err, sizeof(g_tc_err), "cuTensorMapEncodeTiled entry point not available");
+    return false;
+  }
+  const uint64_t Wtok = (uint64_t)g->t_width * g->b_size;
+  cuuint64_t dims[5] = {(cuuint64_t)d, Wtok, (cuuint64_t)g->t_height, (cuuint64_t)g->H, (cuuint64_t)g->B};
+  cuuint64_t strides[4] = {(cuuint64_t)t->stride[2] * 2, (cuuint64_t)t->stride[2] * 2 * Wtok,
+                           (cuuint64_t)t->stride[1] * 2, (cuuint64_t)t->stride[0] * 2};
+  // a dimension of extent 1 may carry any stride; give it a legal one
+  for (int i = 0; i < 4; ++i)
+    if (dims[i + 1] == 1 && (strides[i] == 0 || strides[i] % 16)) strides[i] = 16;
+  cuuint32_t box[5] = {64u, (cuuint32_t)box_cols, (cuuint32_t)box_rows, 1u, 1u};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  const CUtensorMapDataType dt = g->dtype == SWA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = fn(m, dt, 5, t->ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_tc_err, sizeof(g_tc_err), "cuTensorMapEncodeTiled failed (%d)", (int)r);
+    return false;
+  }
+  return true;
+}
+
+int env_int(const char* name, int dflt) {
+  const char* v = getenv(name);
+  return v ? atoi(v) : dflt;
+}
+
+// Widest halo, in token columns, over all resident-tile columns.
+int halo_width(const swa_geom_t* g, int TW) {
+  const int Wtok = g->t_width * g->b_size, b = g->b_size;
+  int best = 0;
+  for (int x0 = 0; x0 < Wtok; x0 += TW) {
+    const int lo = (x0 / b - g->col_size) * b;
+    const int hi = ((x0 + TW - 1) / b + g->col_size + 1) * b;
+    best = hi - lo > best ? hi - lo : best;
+  }
+  return best;
+}
+
+// Choose the resident tile and streamed-block shape.  `fixed_bytes` = shared memory that
+// does not scale with the pipeline depth; `stage_bytes_per_row` = bytes one streamed
+// token row (all its operands) takes; `pbuf_bytes(N)` handled by the caller through
+// `p_operands` (number of 16-bit [128 x N] operand buffers written by the softmax warps).
+bool make_plan(const swa_geom_t* g, int which, Plan* out) {
+  Plan pl;
+  pl.TH = env_int("SWA_TC_TH", 8);
+  pl.TW = 128 / pl.TH;
+  const int hw = halo_width(g, pl.TW);
+  if (hw > 64) return false;
+  const int halo_rows = pl.TH + 2 * g->row_size;
+  const int qch = g->d_qk / 64, vch = g->d_v / 64;
+  // per-row bytes of one pipeline stage and fixed bytes, per kernel
+  //   fwd : stage = K + V            fixed = Q              p-operands = 1 (P)
+  //   dq  : stage = K + V            fixed = Q + dO         p-operands = 1 (dS)
+  //   dkdv: stage = Q + dO (+lse,delta)  fixed = K + V      p-operands = 2 (P^T, dS^T)
+  const uint32_t fixed = (which == 0 ? qch : qch + vch) * 16384u;
+  const uint32_t row_bytes = (qch + vch) * 128u;
+  const int p_ops = which == 2 ? 2 : 1;
+  const int nmax = env_int("SWA_TC_NMAX", 128);
+  long best_cost = -1;
+  for (int KW = hw; KW <= 64; ++KW)
+    for (int KR = 1; KR <= 16; ++KR) {
+      const int N = KW * KR;
+      if (N > nmax || N % 16) continue;
+      const int pch = (N + 63) / 64;
+      const uint32_t stage = (uint32_t)N * row_bytes + (which == 2 ? (uint32_t)N * 8u : 0u);
+      const uint32_t pbuf = (uint32_t)p_ops * pch * 16384u;
+      const uint32_t need = fixed + 2 * stage + pbuf + 2048u;
+      if (need > kSmemLimit) continue;
+      const long nblk = (halo_rows + KR - 1) / KR;
+      const long cost = nblk * N * 16 + nblk * 400;  // executed columns + a per-block overhead
+      if (best_cost < 0 || cost < best_cost) {
+        best_cost = cost;
+        pl.KR = KR; pl.KW = KW; pl.N = N;
+      }
+    }
+  if (best_cost < 0) return false;
+  if (int v = env_int("SWA_TC_KR", 0)) {
+    pl.KR = v;
+    pl.KW = env_int("SWA_TC_KW", pl.KW);
+    pl.N = pl.KR * pl.KW;
+  }
+  const int pch = (pl.N + 63) / 64;
+  const uint32_t stage = (uint32_t)pl.N * row_bytes + (which == 2 ? (uint32_t)pl.N * 8u : 0u);
+  const uint32_t pbuf1 = (uint32_t)p_ops * pch * 16384u;
+  const int Wtok = g->t_width * g->b_size;
+  pl.n_tiles_x = (Wtok + pl.TW - 1) / pl.TW;
+  pl.n_tiles_y = (g->t_height + pl.TH - 1) / pl.TH;
+  const int max_blocks = (halo_rows + pl.KR - 1) / pl.KR;
+  pl.pbufs = (which == 0 && fixed + 2 * stage + 2 * pbuf1 + 2048u <= kSmemLimit) ? 2 : 1;
+  pl.pbufs = env_int("SWA_TC_PBUFS", pl.pbufs);
+  pl.stages = 2;
+  while (pl.stages < kMaxStages && pl.stages < max_blocks &&
+         fixed + (pl.stages + 1) * stage + pl.pbufs * pbuf1 + 2048u <= kSmemLimit)
+    ++pl.stages;
+  pl.stages = env_int("SWA_TC_STAGES", pl.stages);
+  pl.smem_bytes = fixed + pl.stages * stage + pl.pbufs * pbuf1 + 2048u;
+  *out = pl;
+  return pl.smem_bytes <= kSmemLimit;
+}
+
+KParams make_params(const swa_geom_t* g, const swa_rope_t* rope, const Plan& pl, int32_t* status) {
+  KParams p;
+  p.t_h = g->t_height;
+  p.Wtok = g->t_width * g->b_size;
+  p.b = g->b_size;
+  p.wr = g->row_size;
+  p.wc = g->col_size;
+  p.H = g->H;
+  p.qch = g->d_qk / 64;
+  p.vch = g->d_v / 64;
+  p.sm_scale = g->sm_scale;
+  p.scale_log2 = g->sm_scale * kLog2e;
+  p.pl = pl;
+  p.rope = make_rope(rope);
+  p.status = status;
+  return p;
+}
+
+bool tensor_ok(const swa_tensor_t* t) {
+  return t->stride[3] == 1 && ((uintptr_t)t->ptr % 16) == 0 && t->stride[0] % 8 == 0 && t->stride[1] % 8 == 0 &&
+         t->stride[2] % 8 == 0 && t->stride[2] > 0;
+}
+
+}  // namespace
+
+const char* last_error() { return g_tc_err; }
+
+const char* unsupported_reason(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* const* tensors,
+                               int n_tensors, int which) {
+  if (getenv("SWA_TC_DISABLE")) return "disabled by SWA_TC_DISABLE";
+  if (which != 0) return "backward tensor-core kernels not built";
+  if (g->dtype != SWA_F16 && g->dtype != SWA_BF16) return "fp32 runs on the SIMT kernels";
+  if ((g->d_qk != 64 && g->d_qk != 128) || (g->d_v != 64 && g->d_v != 128)) return "head dims must be 64 or 128";
+  if (!(g->sm_scale > 0.f)) return "sm_scale must be positive";
+  if (rope && rope->idx && rope->n_rdim % 8) return "n_rdim must be a multiple of 8";
+  if ((int64_t)g->t_height * g->t_width * g->b_size > (1 << 30)) return "grid too large";
+  Plan pl;
+  if (!make_plan(g, which, &pl)) return "no tile plan fits (window too wide for one streamed block)";
+  for (int i = 0; i < n_tensors; ++i)
+    if (!tensor_ok(tensors[i])) return "tensors need unit last stride and 16-byte aligned rows";
+  return nullptr;
+}
+
+int launch_fwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
+               const swa_tensor_t* v, const swa_tensor_t* o, float* lse, int32_t* status, cudaStream_t st) {
+  Plan pl;
+  if (!make_plan(g, 0, &pl)) {
+    snprintf(g_tc_err, sizeof(g_tc_err), "no tile plan");
+    return -1;
+  }
+  CUtensorMap tq, tk, tv;
+  if (!make_map(&tq, q, g, g->d_qk, pl.TW, pl.TH) || !make_map(&tk, k, g, g->d_qk, pl.KW, pl.KR) ||
+      !make_map(&tv, v, g, g->d_v, pl.KW, pl.KR))
+    return -1;
+  const KParams p = make_params(g, rope, pl, status);
+  dim3 grid(pl.n_tiles_x * pl.n_tiles_y, g->B * g->H), block(kFwdThreads);
+  auto kern = g->dtype == SWA_BF16 ? fwd_kernel<true> : fwd_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem_bytes);
+  if (e != cudaSuccess) {
+    snprintf(g_tc_err, sizeof(g_tc_err), "cudaFuncSetAttribute(%u bytes): %s", pl.smem_bytes, cudaGetErrorString(e));
+    return -1;
+  }
+  if (getenv("SWA_TC_VERBOSE"))
+    fprintf(stderr, "[swa2d] fwd plan: tile %dx%d, block %dx%d (N=%d), stages %d, pbufs %d, smem %u, grid %ux%u\n", pl.TH,
+            pl.TW, pl.KR, pl.KW, pl.N, pl.stages, pl.pbufs, pl.smem_bytes, grid.x, grid.y);
+  kern<<<grid, block, pl.smem_bytes, st>>>(tq, tk, tv, p, make_view(o), lse);
+  return 0;
+}
+
+int launch_dq(const swa_geom_t*, const swa_rope_t*, const swa_tensor_t*, const swa_tensor_t*, const swa_tensor_t*,
+              const swa_tensor_t*, const float*, const float*, const swa_tensor_t*, int32_t*, cudaStream_t) {
+  snprintf(g_tc_err, sizeof(g_tc_err), "not built");
+  return -1;
+}
+
+int launch_dkdv(const swa_geom_t*, const swa_rope_t*, const swa_tensor_t*, const swa_tensor_t*, const swa_tensor_t*,
+                const swa_tensor_t*, const float*, const float*, const swa_tensor_t*, const swa_tensor_t*, int32_t*,
+                cudaStream_t) {
+  snprintf(g_tc_err, sizeof(g_tc_err), "not built");
+  return -1;
+}
+
+}  // namespace tc
+}  // namespace swa
