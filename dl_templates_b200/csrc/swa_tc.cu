@@ -9,6 +9,7 @@
 #include <type_traits>
 
 #include "swa_tc.cuh"
+#include "swa_tc_bwd.cuh"
 #include "swa_tc_fwd.cuh"
 
 namespace swa {
@@ -18,6 +19,7 @@ namespace {
 
 thread_local char g_tc_err[256] = "";
 constexpr uint32_t kSmemLimit = 227 * 1024;
+constexpr uint32_t kSmemSlack = 4096;  // 1 KiB alignment + lse/delta staging + barriers
 
 PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
   static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
@@ -95,16 +97,17 @@ bool make_plan(const swa_geom_t* g, int which, Plan* out) {
   const uint32_t fixed = (which == 0 ? qch : qch + vch) * 16384u;
   const uint32_t row_bytes = (qch + vch) * 128u;
   const int p_ops = which == 2 ? 2 : 1;
-  const int nmax = env_int("SWA_TC_NMAX", 128);
+  // the backward kernels double-buffer S and dP in TMEM next to two accumulators: 64 columns per buffer
+  const int nmax = env_int("SWA_TC_NMAX", which == 0 ? 128 : 64);
   long best_cost = -1;
   for (int KW = hw; KW <= 64; ++KW)
     for (int KR = 1; KR <= 16; ++KR) {
       const int N = KW * KR;
       if (N > nmax || N % 16) continue;
       const int pch = (N + 63) / 64;
-      const uint32_t stage = (uint32_t)N * row_bytes + (which == 2 ? (uint32_t)N * 8u : 0u);
+      const uint32_t stage = (uint32_t)N * row_bytes;
       const uint32_t pbuf = (uint32_t)p_ops * pch * 16384u;
-      const uint32_t need = fixed + 2 * stage + pbuf + 2048u;
+      const uint32_t need = fixed + 2 * stage + pbuf + kSmemSlack;
       if (need > kSmemLimit) continue;
       const long nblk = (halo_rows + KR - 1) / KR;
       const long cost = nblk * N * 16 + nblk * 400;  // executed columns + a per-block overhead
@@ -120,20 +123,20 @@ bool make_plan(const swa_geom_t* g, int which, Plan* out) {
     pl.N = pl.KR * pl.KW;
   }
   const int pch = (pl.N + 63) / 64;
-  const uint32_t stage = (uint32_t)pl.N * row_bytes + (which == 2 ? (uint32_t)pl.N * 8u : 0u);
+  const uint32_t stage = (uint32_t)pl.N * row_bytes;
   const uint32_t pbuf1 = (uint32_t)p_ops * pch * 16384u;
   const int Wtok = g->t_width * g->b_size;
   pl.n_tiles_x = (Wtok + pl.TW - 1) / pl.TW;
   pl.n_tiles_y = (g->t_height + pl.TH - 1) / pl.TH;
   const int max_blocks = (halo_rows + pl.KR - 1) / pl.KR;
-  pl.pbufs = (which == 0 && fixed + 2 * stage + 2 * pbuf1 + 2048u <= kSmemLimit) ? 2 : 1;
+  pl.pbufs = (fixed + 2 * stage + 2 * pbuf1 + kSmemSlack <= kSmemLimit) ? 2 : 1;
   pl.pbufs = env_int("SWA_TC_PBUFS", pl.pbufs);
   pl.stages = 2;
   while (pl.stages < kMaxStages && pl.stages < max_blocks &&
-         fixed + (pl.stages + 1) * stage + pl.pbufs * pbuf1 + 2048u <= kSmemLimit)
+         fixed + (pl.stages + 1) * stage + pl.pbufs * pbuf1 + kSmemSlack <= kSmemLimit)
     ++pl.stages;
   pl.stages = env_int("SWA_TC_STAGES", pl.stages);
-  pl.smem_bytes = fixed + pl.stages * stage + pl.pbufs * pbuf1 + 2048u;
+  pl.smem_bytes = fixed + pl.stages * stage + pl.pbufs * pbuf1 + kSmemSlack;
   *out = pl;
   return pl.smem_bytes <= kSmemLimit;
 }
@@ -168,7 +171,6 @@ const char* last_error() { return g_tc_err; }
 const char* unsupported_reason(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* const* tensors,
                                int n_tensors, int which) {
   if (getenv("SWA_TC_DISABLE")) return "disabled by SWA_TC_DISABLE";
-  if (which != 0) return "backward tensor-core kernels not built";
   if (g->dtype != SWA_F16 && g->dtype != SWA_BF16) return "fp32 runs on the SIMT kernels";
   if ((g->d_qk != 64 && g->d_qk != 128) || (g->d_v != 64 && g->d_v != 128)) return "head dims must be 64 or 128";
   if (!(g->sm_scale > 0.f)) return "sm_scale must be positive";
@@ -207,17 +209,49 @@ int launch_fwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* 
   return 0;
 }
 
-int launch_dq(const swa_geom_t*, const swa_rope_t*, const swa_tensor_t*, const swa_tensor_t*, const swa_tensor_t*,
-              const swa_tensor_t*, const float*, const float*, const swa_tensor_t*, int32_t*, cudaStream_t) {
-  snprintf(g_tc_err, sizeof(g_tc_err), "not built");
-  return -1;
+namespace {
+
+template <bool DKDV>
+int launch_bwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* xqk, const swa_tensor_t* xv,
+               const swa_tensor_t* yqk, const swa_tensor_t* yv, const float* lse, const float* delta,
+               const swa_tensor_t* out_qk, const swa_tensor_t* out_v, int32_t* status, cudaStream_t st) {
+  Plan pl;
+  if (!make_plan(g, DKDV ? 2 : 1, &pl)) {
+    snprintf(g_tc_err, sizeof(g_tc_err), "no tile plan");
+    return -1;
+  }
+  CUtensorMap mxqk, mxv, myqk, myv;
+  if (!make_map(&mxqk, xqk, g, g->d_qk, pl.TW, pl.TH) || !make_map(&mxv, xv, g, g->d_v, pl.TW, pl.TH) ||
+      !make_map(&myqk, yqk, g, g->d_qk, pl.KW, pl.KR) || !make_map(&myv, yv, g, g->d_v, pl.KW, pl.KR))
+    return -1;
+  const KParams p = make_params(g, rope, pl, status);
+  dim3 grid(pl.n_tiles_x * pl.n_tiles_y, g->B * g->H), block(kBwdThreads);
+  auto kern = g->dtype == SWA_BF16 ? bwd_kernel<true, DKDV> : bwd_kernel<false, DKDV>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem_bytes);
+  if (e != cudaSuccess) {
+    snprintf(g_tc_err, sizeof(g_tc_err), "cudaFuncSetAttribute(%u bytes): %s", pl.smem_bytes, cudaGetErrorString(e));
+    return -1;
+  }
+  if (getenv("SWA_TC_VERBOSE"))
+    fprintf(stderr, "[swa2d] %s plan: tile %dx%d, block %dx%d (N=%d), stages %d, pbufs %d, smem %u, grid %ux%u\n",
+            DKDV ? "dkdv" : "dq", pl.TH, pl.TW, pl.KR, pl.KW, pl.N, pl.stages, pl.pbufs, pl.smem_bytes, grid.x, grid.y);
+  kern<<<grid, block, pl.smem_bytes, st>>>(mxqk, mxv, myqk, myv, p, lse, delta, make_view(out_qk),
+                                          out_v ? make_view(out_v) : View4{nullptr, 0, 0, 0, 0});
+  return 0;
 }
 
-int launch_dkdv(const swa_geom_t*, const swa_rope_t*, const swa_tensor_t*, const swa_tensor_t*, const swa_tensor_t*,
-                const swa_tensor_t*, const float*, const float*, const swa_tensor_t*, const swa_tensor_t*, int32_t*,
-                cudaStream_t) {
-  snprintf(g_tc_err, sizeof(g_tc_err), "not built");
-  return -1;
+}  // namespace
+
+int launch_dq(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
+              const swa_tensor_t* v, const swa_tensor_t* d_o, const float* lse, const float* delta,
+              const swa_tensor_t* dq, int32_t* status, cudaStream_t st) {
+  return launch_bwd<false>(g, rope, q, d_o, k, v, lse, delta, dq, nullptr, status, st);
+}
+
+int launch_dkdv(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
+                const swa_tensor_t* v, const swa_tensor_t* d_o, const float* lse, const float* delta,
+                const swa_tensor_t* dk, const swa_tensor_t* dv, int32_t* status, cudaStream_t st) {
+  return launch_bwd<true>(g, rope, k, v, q, d_o, lse, delta, dk, dv, status, st);
 }
 
 }  // namespace tc
