@@ -180,9 +180,12 @@ def device_case(cfg, bh_local, device, seed):
     if cfg["drop"] > 0:
         gc = torch.Generator().manual_seed(1000)
         idx[torch.bernoulli(torch.full((N,), cfg["drop"]), generator=gc).bool()] = -1
-    tab = swa.make_cs_table(R, G, 10000.0)
     half = (cfg["w"] - 1) // 2
-    return dict(q=q, k=k, v=v, do=do, rope=(idx.to(device), tab.to(device), tab.clone().to(device)),
+    rope = None
+    if R > 0:
+        tab = swa.make_cs_table(R, G, 10000.0)
+        rope = (idx.to(device), tab.to(device), tab.clone().to(device))
+    return dict(q=q, k=k, v=v, do=do, rope=rope,
                 win=(1, G, G, half, half), sm_scale=cfg["d_qk"] ** -0.5)
 
 
@@ -195,6 +198,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--bh-per-gpu", type=int, default=0, help="(batch*head) slices per GPU; 0 = the workload's B*H")
     ap.add_argument("--kernels", default="auto", choices=["auto", "simt", "tc"], help="kernel family to force")
+    ap.add_argument("--rope-dims", type=int, default=-1, help="override the number of rotated q/k dims (0 = no RoPE)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--verify", action="store_true", help="gather outputs over NCCL and compare rank slices")
@@ -204,6 +208,8 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     cfg = workload_dims(args.workload)
+    if args.rope_dims >= 0:
+        cfg["rope_dims"] = args.rope_dims
     half = (cfg["w"] - 1) // 2
     dtype_name = {torch.float32: "f32", torch.float16: "f16", torch.bfloat16: "bf16"}[cfg["dtype"]]
 

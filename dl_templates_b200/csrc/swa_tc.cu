@@ -19,7 +19,7 @@ namespace {
 
 thread_local char g_tc_err[256] = "";
 constexpr uint32_t kSmemLimit = 227 * 1024;
-constexpr uint32_t kSmemSlack = 4096;  // 1 KiB alignment + lse/delta staging + barriers
+constexpr uint32_t kSmemSlack = 6144;  // 1 KiB alignment + lse/delta staging + barriers and exchange buffers
 
 PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
   static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
@@ -84,8 +84,8 @@ int halo_width(const swa_geom_t* g, int TW) {
 // `p_operands` (number of 16-bit [128 x N] operand buffers written by the softmax warps).
 bool make_plan(const swa_geom_t* g, int which, Plan* out) {
   Plan pl;
-  pl.TH = env_int("SWA_TC_TH", 8);
-  pl.TW = 128 / pl.TH;
+  pl.TH = 8;   // the window-mask columns are laid out for 8 tile rows x 16 tile columns
+  pl.TW = 16;
   const int hw = halo_width(g, pl.TW);
   if (hw > 64) return false;
   const int halo_rows = pl.TH + 2 * g->row_size;
@@ -94,8 +94,8 @@ bool make_plan(const swa_geom_t* g, int which, Plan* out) {
   //   fwd : stage = K + V            fixed = Q              p-operands = 1 (P)
   //   dq  : stage = K + V            fixed = Q + dO         p-operands = 1 (dS)
   //   dkdv: stage = Q + dO (+lse,delta)  fixed = K + V      p-operands = 2 (P^T, dS^T)
-  const uint32_t fixed = (which == 0 ? qch : qch + vch) * 16384u;
-  const uint32_t row_bytes = (qch + vch) * 128u;
+  const uint32_t fixed = (which == 0 ? qch : qch + vch) * 16384u + 128u * kXRowBytes;
+  const uint32_t row_bytes = (qch + vch) * 128u + kXRowBytes;
   const int p_ops = which == 2 ? 2 : 1;
   // the backward kernels double-buffer S and dP in TMEM next to two accumulators: 64 columns per buffer
   const int nmax = env_int("SWA_TC_NMAX", which == 0 ? 128 : 64);
@@ -141,6 +141,17 @@ bool make_plan(const swa_geom_t* g, int which, Plan* out) {
   return pl.smem_bytes <= kSmemLimit;
 }
 
+// Indicator value a and penalty b (powers of two, exact in fp16 and bf16) of the window mask that
+// rides on the score MMA: a*b*scale*log2(e) >= 4000, so exp2 of a masked score is exactly 0.
+bool mask_constants(float sm_scale, float* a, float* b) {
+  const float need = 4000.f / (sm_scale * kLog2e);
+  float bb = 16384.f, aa = 1.f;
+  while (aa * bb < need && aa < 16384.f) aa *= 2.f;
+  *a = aa;
+  *b = bb;
+  return aa * bb >= need;
+}
+
 KParams make_params(const swa_geom_t* g, const swa_rope_t* rope, const Plan& pl, int32_t* status) {
   KParams p;
   p.t_h = g->t_height;
@@ -153,9 +164,12 @@ KParams make_params(const swa_geom_t* g, const swa_rope_t* rope, const Plan& pl,
   p.vch = g->d_v / 64;
   p.sm_scale = g->sm_scale;
   p.scale_log2 = g->sm_scale * kLog2e;
+  mask_constants(g->sm_scale, &p.mask_a, &p.mask_b);
   p.pl = pl;
   p.rope = make_rope(rope);
   p.status = status;
+  // the Python layer hands a 4 KiB status buffer: words 0-3 status, bytes 16.. = 4 roles x 32 clock samples
+  p.trace = (status != nullptr && getenv("SWA_TC_TRACE")) ? reinterpret_cast<long long*>(status + 4) : nullptr;
   return p;
 }
 
@@ -174,6 +188,8 @@ const char* unsupported_reason(const swa_geom_t* g, const swa_rope_t* rope, cons
   if (g->dtype != SWA_F16 && g->dtype != SWA_BF16) return "fp32 runs on the SIMT kernels";
   if ((g->d_qk != 64 && g->d_qk != 128) || (g->d_v != 64 && g->d_v != 128)) return "head dims must be 64 or 128";
   if (!(g->sm_scale > 0.f)) return "sm_scale must be positive";
+  float ma, mb;
+  if (!mask_constants(g->sm_scale, &ma, &mb)) return "sm_scale too small for the MMA-side window mask";
   if (rope && rope->idx && rope->n_rdim % 8) return "n_rdim must be a multiple of 8";
   if ((int64_t)g->t_height * g->t_width * g->b_size > (1 << 30)) return "grid too large";
   Plan pl;

@@ -37,9 +37,11 @@ struct KParams {
   int t_h, Wtok, b, wr, wc, H;
   int qch, vch;        // d_qk/64, d_v/64
   float scale_log2, sm_scale;
+  float mask_a, mask_b;  // window mask through the MMA: indicator value and penalty magnitude (powers of two)
   Plan pl;
   RopeDev rope;
   int32_t* status;
+  long long* trace;    // optional per-role clock64() samples of one CTA (performance debugging), else null
 };
 
 // Position of a resident-tile CTA and the halo it streams.
@@ -119,44 +121,170 @@ __device__ __forceinline__ float2 unpack2(uint32_t u) {
   }
 }
 
+// ---- window mask as extra contraction columns ------------------------------------------------
+// The score MMA contracts over 32 extra columns.  The resident token at tile position (i, c)
+// carries mask_a in column i (its row in the tile, i < 8) and in column 8+c (its column in the
+// tile, c < 16); a streamed token carries -mask_b in column i when it is outside the row window
+// of tile row i (or outside the grid) and in column 8+c when it is outside the column window of
+// tile column c.  The product adds 0 to every allowed pair and at most -mask_a*mask_b to every
+// other pair, so exp2 of the scaled score underflows to exactly 0 there and the threads that
+// own the rows do no masking work at all.
+//
+// These "x tiles" are written by threads, not by TMA, in the unswizzled K-major core-matrix
+// layout: 16-byte unit u (0..3) of row r at (r/8)*512 + u*128 + (r%8)*16.
+constexpr uint32_t kXRowBytes = 64;
+constexpr uint32_t kXLbo = 128, kXSbo = 512, kXStepBytes = 256;
+
+__device__ __forceinline__ uint8_t* xtile_unit(uint8_t* tile, int row, int unit) {
+  return tile + (row >> 3) * 512 + unit * 128 + (row & 7) * 16;
+}
+
+template <bool BF16>
+__device__ __forceinline__ void write_indicator_row(uint8_t* tile, int row, const KParams& p) {
+  const int ti = row / p.pl.TW, tc = row - ti * p.pl.TW;
+  const float a = p.mask_a;
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    uint32_t w[4];
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+      const int d0 = u * 8 + 2 * h, d1 = d0 + 1;
+      const float v0 = (d0 < 8 ? d0 == ti : d0 - 8 == tc) ? a : 0.f;
+      const float v1 = (d1 < 8 ? d1 == ti : d1 - 8 == tc) ? a : 0.f;
+      w[h] = pack2<BF16>(v0, v1);
+    }
+    *reinterpret_cast<uint4*>(xtile_unit(tile, row, u)) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+// Penalty row of the streamed token at grid position (yr, yx) against the resident tile at (r0, x0).
+template <bool BF16>
+__device__ __forceinline__ void write_penalty_row(uint8_t* tile, int row, const KParams& p, int r0, int x0, int yr,
+                                                  int yx) {
+  const bool in = yr >= 0 && yr < p.t_h && yx >= 0 && yx < p.Wtok;
+  int row_lo = 1, row_hi = 0, col_lo = 1, col_hi = 0;  // empty ranges
+  if (in) {
+    const int yc = yx / p.b;
+    row_lo = yr - p.wr - r0;            // allowed tile rows, inclusive
+    row_hi = yr + p.wr - r0;
+    col_lo = (yc - p.wc) * p.b - x0;    // allowed tile columns, inclusive
+    col_hi = (yc + p.wc + 1) * p.b - x0 - 1;
+  }
+  const float nb = -p.mask_b;
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    uint32_t w[4];
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+      const int d0 = u * 8 + 2 * h, d1 = d0 + 1;
+      const bool ok0 = d0 < 8 ? (d0 >= row_lo && d0 <= row_hi) : (d0 - 8 >= col_lo && d0 - 8 <= col_hi);
+      const bool ok1 = d1 < 8 ? (d1 >= row_lo && d1 <= row_hi) : (d1 - 8 >= col_lo && d1 - 8 <= col_hi);
+      // columns 24..31 carry no indicator on the resident side, their value is irrelevant
+      w[h] = pack2<BF16>(ok0 ? 0.f : nb, ok1 ? 0.f : nb);
+    }
+    *reinterpret_cast<uint4*>(xtile_unit(tile, row, u)) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
 // Address of 16-byte unit `unit` (0..7) of row `row` in a swizzled 64-element-wide tile.
 __device__ __forceinline__ uint8_t* swz(uint8_t* tile, int row, int unit) {
   return tile + row * 128 + ((unit ^ (row & 7)) << 4);
 }
 
-// Rotate, in shared memory, row `row` of a q/k tile (chunks `chunk_stride` bytes
-// apart) by the RoPE-2D angles of token `token`.  n_rdim is a multiple of 8 here, so
-// the partner of a 16-byte unit is another whole unit of the same row.
-template <bool BF16>
-__device__ __forceinline__ void rotate_row_smem(uint8_t* tile, uint32_t chunk_stride, int row, int token,
-                                                const RopeDev& rp) {
-  int irow, icol;
-  decode_idx(rp.idx[token], rp.max_h, rp.max_w, irow, icol);
-#pragma unroll 1
-  for (int half = 0; half < 2; ++half) {
-    const int pos = half ? icol : irow;
-    if (pos < 0) continue;
-    const float* tab = (half ? rp.col_cs : rp.row_cs) + (int64_t)pos * rp.R * 2;
-#pragma unroll 1
-    for (int i0 = 0; i0 < rp.R; i0 += 8) {
-      const int d0 = 2 * half * rp.R + i0, d1 = d0 + rp.R;
-      uint8_t* a0 = swz(tile + (d0 >> 6) * chunk_stride, row, (d0 & 63) >> 3);
-      uint8_t* a1 = swz(tile + (d1 >> 6) * chunk_stride, row, (d1 & 63) >> 3);
-      uint4 va = *reinterpret_cast<uint4*>(a0), vb = *reinterpret_cast<uint4*>(a1);
-      uint32_t* pa = reinterpret_cast<uint32_t*>(&va);
-      uint32_t* pb = reinterpret_cast<uint32_t*>(&vb);
-      const float4* t4 = reinterpret_cast<const float4*>(tab + 2 * i0);
+// ---- fused RoPE-2D on a swizzled q/k tile in shared memory ---------------------------------
+// One thread rotates one row.  The cos/sin values of the row are fetched into registers ahead
+// of time (RopeCache) -- right after the thread has finished its previous row, i.e. while it
+// would otherwise wait for the next tile to arrive -- because the tables are served by L2 (with
+// ~200 KiB of shared memory per CTA there is hardly any L1 left) and a dependent chain of table
+// loads per row would make these warps the bottleneck of the whole pipeline.
+// n_rdim = 8*NI, so the partner of a 16-byte unit is another whole unit of the same row.
+struct RopeCache {
+  float4 cs[16];   // n_rdim 8/16: row half then column half; n_rdim 32: row half only
+  int irow, icol;  // decoded positions, negative = that half is not rotated
+};
+
+template <int NI>
+__device__ __forceinline__ void rope_fetch_n(RopeCache& c, const RopeDev& rp) {
+  constexpr int R = 8 * NI;
+  if (c.irow >= 0) {
+    const float4* t4 = reinterpret_cast<const float4*>(rp.row_cs + (int64_t)c.irow * R * 2);
 #pragma unroll
-      for (int h = 0; h < 4; ++h) {
-        const float4 cs = __ldg(t4 + h);  // (cos, sin) of pairs 2h and 2h+1
-        const float2 x0 = unpack2<BF16>(pa[h]), x1 = unpack2<BF16>(pb[h]);
-        pa[h] = pack2<BF16>(x0.x * cs.x - x1.x * cs.y, x0.y * cs.z - x1.y * cs.w);
-        pb[h] = pack2<BF16>(x0.x * cs.y + x1.x * cs.x, x0.y * cs.w + x1.y * cs.z);
-      }
-      *reinterpret_cast<uint4*>(a0) = va;
-      *reinterpret_cast<uint4*>(a1) = vb;
+    for (int i = 0; i < NI * 4; ++i) c.cs[i] = __ldg(t4 + i);
+  }
+  if (NI <= 2 && c.icol >= 0) {
+    const float4* t4 = reinterpret_cast<const float4*>(rp.col_cs + (int64_t)c.icol * R * 2);
+#pragma unroll
+    for (int i = 0; i < NI * 4; ++i) c.cs[(NI * 4 + i) & 15] = __ldg(t4 + i);
+  }
+}
+
+// Start fetching the cos/sin rows of the token with packed index `packed` (-1: nothing to do).
+__device__ __forceinline__ void rope_fetch(RopeCache& c, int32_t packed, const RopeDev& rp) {
+  decode_idx(packed, rp.max_h, rp.max_w, c.irow, c.icol);
+  switch (rp.R) {
+    case 8: rope_fetch_n<1>(c, rp); break;
+    case 16: rope_fetch_n<2>(c, rp); break;
+    case 32: rope_fetch_n<4>(c, rp); break;
+    default: c.irow = c.icol = -1; break;
+  }
+}
+
+// Rotate one half (0 = row pair, 1 = column pair) of the row with NI*4 float4 of (cos, sin).
+template <bool BF16, int NI>
+__device__ __forceinline__ void rope_rotate_half(uint8_t* tile, uint32_t chunk_stride, int row, int half,
+                                                 const float4* cs) {
+  constexpr int R = 8 * NI;
+#pragma unroll
+  for (int it = 0; it < NI; ++it) {
+    const int d0 = 2 * half * R + it * 8, d1 = d0 + R;
+    const uint32_t a0 = ptx::smem_u32(swz(tile + (d0 >> 6) * chunk_stride, row, (d0 & 63) >> 3));
+    const uint32_t a1 = ptx::smem_u32(swz(tile + (d1 >> 6) * chunk_stride, row, (d1 & 63) >> 3));
+    uint4 va = ptx::lds128(a0), vb = ptx::lds128(a1);
+    uint32_t* pa = reinterpret_cast<uint32_t*>(&va);
+    uint32_t* pb = reinterpret_cast<uint32_t*>(&vb);
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+      const float4 c = cs[it * 4 + h];  // (cos, sin) of pairs 2h and 2h+1
+      const float2 x0 = unpack2<BF16>(pa[h]), x1 = unpack2<BF16>(pb[h]);
+      pa[h] = pack2<BF16>(x0.x * c.x - x1.x * c.y, x0.y * c.z - x1.y * c.w);
+      pb[h] = pack2<BF16>(x0.x * c.y + x1.x * c.x, x0.y * c.w + x1.y * c.z);
+    }
+    ptx::sts128(a0, va.x, va.y, va.z, va.w);
+    ptx::sts128(a1, vb.x, vb.y, vb.z, vb.w);
+  }
+}
+
+template <bool BF16, int NI>
+__device__ __forceinline__ void rope_apply_n(uint8_t* tile, uint32_t chunk_stride, int row, RopeCache& c,
+                                             const RopeDev& rp) {
+  if (c.irow >= 0) rope_rotate_half<BF16, NI>(tile, chunk_stride, row, 0, &c.cs[0]);
+  if (c.icol >= 0) {
+    if constexpr (NI <= 2) {
+      rope_rotate_half<BF16, NI>(tile, chunk_stride, row, 1, &c.cs[NI * 4]);
+    } else {
+      const float4* t4 = reinterpret_cast<const float4*>(rp.col_cs + (int64_t)c.icol * (8 * NI) * 2);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) c.cs[i] = __ldg(t4 + i);
+      rope_rotate_half<BF16, NI>(tile, chunk_stride, row, 1, &c.cs[0]);
     }
   }
+}
+
+// Rotate row `row` of the tile with the values fetched by rope_fetch.
+template <bool BF16>
+__device__ __forceinline__ void rope_apply(uint8_t* tile, uint32_t chunk_stride, int row, RopeCache& c,
+                                           const RopeDev& rp) {
+  switch (rp.R) {
+    case 8: rope_apply_n<BF16, 1>(tile, chunk_stride, row, c, rp); break;
+    case 16: rope_apply_n<BF16, 2>(tile, chunk_stride, row, c, rp); break;
+    case 32: rope_apply_n<BF16, 4>(tile, chunk_stride, row, c, rp); break;
+    default: break;
+  }
+}
+
+// Performance tracing of one CTA: role `role` stores its k-th clock sample.
+__device__ __forceinline__ void trace_mark(const KParams& p, int role, int k) {
+  if (p.trace != nullptr && blockIdx.x == 37 && blockIdx.y == 1 && k < 32) p.trace[role * 32 + k] = clock64();
 }
 
 // Record a timed-out wait (first one wins) so the host can report it.

@@ -1,16 +1,20 @@
 // tcgen05 forward kernel: o = softmax(scale * rope(q) rope(k)^T + window mask) v, lse.
 //
-// One CTA per 128-query tile (TH rows x TW token columns) of one (batch, head).
-// Warp roles (320 threads):
-//   warp 0      TMA producer: the query tile once, then the K and V halo blocks
-//               through a `stages`-deep ring of shared-memory buffers
-//   warp 1      MMA issuer (one thread): S = Q K^T into one of two TMEM buffers,
-//               O += P V into a third; owns the TMEM allocation
-//   warps 2-5   softmax, one thread per query row (TMEM lane): tcgen05.ld of the S
-//               row, window mask, running max / sum, P written to shared memory as the
-//               A operand of the PV MMA, lazy rescale of O, final normalisation
-//   warps 6-9   fused RoPE-2D: rotate the Q tile and every K block in shared memory
-//               between TMA arrival and MMA issue (pass-through when RoPE is off)
+// One CTA per 128-query tile (8 rows x 16 token columns) of one (batch, head).
+// Warp roles (448 threads):
+//   warp 0       TMA producer: the query tile once, then the K and V halo blocks
+//                through a `stages`-deep ring of shared-memory buffers
+//   warp 1       MMA issuer (one thread): S = Q K^T (+ the window mask as 32 extra
+//                contraction columns) into one of two TMEM buffers, O += P V into a
+//                third; owns the TMEM allocation
+//   warps 2-9    softmax, TWO threads per query row (TMEM lane): warps w and w+4 share
+//                a lane quarter and each take every other 8-column unit of the row, so
+//                every scheduler has two softmax warps whose dependency stalls overlap;
+//                the pair exchanges its block maximum through shared memory.  tcgen05.ld
+//                of the S units, running max / sum, P written to shared memory as the A
+//                operand of the PV MMA, lazy rescale of O, final normalisation
+//   warps 10-13  fused RoPE-2D: rotate the Q tile and every K block in shared memory
+//                between TMA arrival and MMA issue, and write the window-mask tiles
 // S for block j+1 is computed by the tensor core while the softmax warps work on
 // block j.  All waits are bounded; a timed-out wait raises a CTA-wide abort flag,
 // every role leaves its loop, TMEM is freed and the status word records the event.
@@ -25,11 +29,14 @@ struct FwdBars {
   uint64_t q_full, q_ready, o_done;
   uint64_t kv_full[kMaxStages], k_ready[kMaxStages], kv_empty[kMaxStages];
   uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2];
+  float xchg[2][2][128];  // [block parity][column half][row]: block maxima of the two threads of a row
+  float lsum[2][128];     // [column half][row]: partial row sums, exchanged once at the end
   uint32_t tmem_base;
   int abort_flag;
 };
 
-constexpr int kFwdThreads = 320;
+constexpr int kFwdThreads = 448;
+constexpr int kFwdRopeThread0 = 320;
 constexpr uint32_t kFwdTmemCols = 512;
 constexpr uint32_t kTmemS = 0, kTmemO = 256;   // column offsets: S0 at 0, S1 at 128, O at 256
 constexpr float kRescaleThreshold = 8.f;       // lazy rescale when the running max grows by > 2^8
@@ -46,16 +53,20 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   const uint32_t blk_bytes = (uint32_t)N * 128u;               // one 64-wide chunk of a streamed block
   const uint32_t k_stage = blk_bytes * p.qch, v_stage = blk_bytes * p.vch;
   const int pch = (N + 63) >> 6;                                 // 64-key chunks of P
+  const uint32_t kx_stage = (uint32_t)N * kXRowBytes;           // window-mask penalty rows of a streamed block
   uint8_t* q_smem = smem;
-  uint8_t* k_smem = q_smem + p.qch * 16384;
+  uint8_t* qx_smem = q_smem + p.qch * 16384;                    // window-mask indicator rows of the query tile
+  uint8_t* k_smem = qx_smem + 128 * kXRowBytes;
   uint8_t* v_smem = k_smem + pl.stages * k_stage;
-  uint8_t* p_smem = v_smem + pl.stages * v_stage;
+  uint8_t* kx_smem = v_smem + pl.stages * v_stage;
+  uint8_t* p_smem = kx_smem + pl.stages * kx_stage;
   FwdBars* bars = reinterpret_cast<FwdBars*>(p_smem + pl.pbufs * pch * 16384);
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh = blockIdx.y, bi = bh / p.H, hi = bh - bi * p.H;
   const TilePos tp = tile_pos(p, blockIdx.x);
+  if (threadIdx.x == 64) trace_mark(p, 2, 29);
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
@@ -68,8 +79,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&bars->s_full[s], 1);
-      mbar_init(&bars->s_empty[s], 128);
-      mbar_init(&bars->p_full[s], 128);
+      mbar_init(&bars->s_empty[s], 256);
+      mbar_init(&bars->p_full[s], 256);
       mbar_init(&bars->p_empty[s], 1);
     }
     bars->abort_flag = 0;
@@ -85,16 +96,19 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   const uint32_t tmem = bars->tmem_base;
 
   if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    // ------------------------------------------------------------------ TMA producer (whole warp, one lane issues)
+    if (elect_one()) {
       prefetch_tmap(&tm_q);
       prefetch_tmap(&tm_k);
       prefetch_tmap(&tm_v);
       mbar_arrive_expect_tx(&bars->q_full, p.qch * 16384);
       for (int c = 0; c < p.qch; ++c) tma_load_5d(q_smem + c * 16384, &tm_q, &bars->q_full, c * 64, tp.x0, tp.r0, hi, bi);
-      for (int j = 0; j < tp.nblk; ++j) {
-        const int s = j % pl.stages;
-        if (j >= pl.stages && !mbar_wait(&bars->kv_empty[s], ((j / pl.stages) - 1) & 1, abort_flag)) break;
+    }
+    for (int j = 0; j < tp.nblk; ++j) {
+      const int s = j % pl.stages;
+      bool free_ = j < pl.stages || mbar_wait<64>(&bars->kv_empty[s], ((j / pl.stages) - 1) & 1, abort_flag);
+      if (!__all_sync(0xffffffffu, free_)) break;
+      if (elect_one()) {
         mbar_arrive_expect_tx(&bars->kv_full[s], k_stage + v_stage);
         const int row = tp.hr_first + j * pl.KR;
         for (int c = 0; c < p.qch; ++c)
@@ -102,79 +116,120 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         for (int c = 0; c < p.vch; ++c)
           tma_load_5d(v_smem + s * v_stage + c * blk_bytes, &tm_v, &bars->kv_full[s], c * 64, tp.hx0, row, hi, bi);
       }
+      __syncwarp();
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      const uint32_t fmt = BF16 ? 1u : 0u;
-      const uint32_t idesc_s = instr_desc(fmt, 128, N, 0, 0);
-      const uint32_t idesc_pv = instr_desc(fmt, 128, p.vch * 64, 0, 1);
-      const uint32_t q_addr = smem_u32(q_smem), k_addr = smem_u32(k_smem), v_addr = smem_u32(v_smem),
-                     p_addr = smem_u32(p_smem);
-      bool ok = mbar_wait(&bars->q_ready, 0, abort_flag);
-      auto issue_pv = [&](int i) -> bool {
-        const int pb = i % pl.pbufs, s = i % pl.stages;
-        if (!mbar_wait(&bars->p_full[pb], (i / pl.pbufs) & 1, abort_flag)) return false;
-        tc_fence_after();
-        for (int ks = 0; ks < (N >> 4); ++ks) {
-          const uint64_t a = smem_desc(p_addr + pb * pch * 16384 + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024);
-          const uint64_t b = smem_desc(v_addr + s * v_stage + ks * 2048, blk_bytes, 1024);
-          umma_ss(tmem + kTmemO, a, b, idesc_pv, (i > 0 || ks > 0) ? 1u : 0u);
-        }
+    // ------------------------------------------------------------------ MMA issuer (whole warp, one lane issues)
+    const uint32_t fmt = BF16 ? 1u : 0u;
+    const uint32_t idesc_s = instr_desc(fmt, 128, N, 0, 0);
+    const uint32_t idesc_pv = instr_desc(fmt, 128, p.vch * 64, 0, 1);
+    const uint32_t q_addr = smem_u32(q_smem), k_addr = smem_u32(k_smem), v_addr = smem_u32(v_smem),
+                   p_addr = smem_u32(p_smem), qx_addr = smem_u32(qx_smem), kx_addr = smem_u32(kx_smem);
+    const uint32_t hi_sw = smem_desc_hi(1024, true), hi_ns = smem_desc_hi(kXSbo, false);
+    bool ok = true;
+    auto wait_all = [&](uint64_t* bar, uint32_t parity) {
+      const bool r = ok && mbar_wait(bar, parity, abort_flag);
+      ok = __all_sync(0xffffffffu, r);
+    };
+    wait_all(&bars->q_ready, 0);
+    auto issue_pv = [&](int i) {
+      const int pb = i % pl.pbufs, s = i % pl.stages;
+      wait_all(&bars->p_full[pb], (i / pl.pbufs) & 1);
+      if (!ok) return;
+      tc_fence_after();
+      const uint32_t pa = p_addr + pb * pch * 16384, vb = v_addr + s * v_stage;
+      if (elect_one()) {
+        for (int ks = 0; ks < (N >> 4); ++ks)
+          umma_ss(tmem + kTmemO, smem_desc_from(pa + (ks >> 2) * 16384 + (ks & 3) * 32, 16, hi_sw),
+                  smem_desc_from(vb + ks * 2048, blk_bytes, hi_sw), idesc_pv, (i > 0 || ks > 0) ? 1u : 0u);
         umma_commit(&bars->kv_empty[s]);
         umma_commit(&bars->p_empty[pb]);
-        return true;
-      };
-      for (int j = 0; ok && j < tp.nblk; ++j) {
-        const int s = j % pl.stages, sb = j & 1;
-        if (!mbar_wait(&bars->k_ready[s], (j / pl.stages) & 1, abort_flag)) { ok = false; break; }
-        if (j >= 2 && !mbar_wait(&bars->s_empty[sb], ((j >> 1) - 1) & 1, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        for (int c = 0; c < p.qch; ++c)
-          for (int k = 0; k < 4; ++k) {
-            const uint64_t a = smem_desc(q_addr + c * 16384 + k * 32, 16, 1024);
-            const uint64_t b = smem_desc(k_addr + s * k_stage + c * blk_bytes + k * 32, 16, 1024);
-            umma_ss(tmem + kTmemS + sb * 128, a, b, idesc_s, (c | k) ? 1u : 0u);
-          }
-        umma_commit(&bars->s_full[sb]);
-        if (j >= 1 && !issue_pv(j - 1)) { ok = false; break; }
+        if (i == tp.nblk - 1) umma_commit(&bars->o_done);
       }
-      if (ok && issue_pv(tp.nblk - 1)) umma_commit(&bars->o_done);
+      __syncwarp();
+    };
+    for (int j = 0; ok && j < tp.nblk; ++j) {
+      const int s = j % pl.stages, sb = j & 1;
+      wait_all(&bars->k_ready[s], (j / pl.stages) & 1);
+      if (j >= 2) wait_all(&bars->s_empty[sb], ((j >> 1) - 1) & 1);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t kb = k_addr + s * k_stage, kxb = kx_addr + s * kx_stage, sd = tmem + kTmemS + sb * 128;
+      if (elect_one()) {
+        for (int c = 0; c < p.qch; ++c) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_ss(sd, smem_desc_from(q_addr + c * 16384 + k * 32, 16, hi_sw),
+                    smem_desc_from(kb + c * blk_bytes + k * 32, 16, hi_sw), idesc_s, (c | k) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < 2; ++k)  // + indicator x penalty: the window mask
+          umma_ss(sd, smem_desc_from(qx_addr + k * kXStepBytes, kXLbo, hi_ns),
+                  smem_desc_from(kxb + k * kXStepBytes, kXLbo, hi_ns), idesc_s, 1u);
+        umma_commit(&bars->s_full[sb]);
+        trace_mark(p, 1, 1 + 2 * j);
+      }
+      __syncwarp();
+      if (j >= 1) issue_pv(j - 1);
     }
-  } else if (warp < 6) {
-    // ------------------------------------------------------------------ softmax, one thread per query row
-    const int quarter = warp & 3;
+    if (ok) issue_pv(tp.nblk - 1);
+  } else if (warp < 10) {
+    // ------------------------------------------------------------------ softmax, two threads per query row
+    const int quarter = warp & 3;                 // TMEM lane quarter this warp may touch
+    const int half = (warp - 2) >> 2;             // which 8-column unit of every 16 columns is this thread's
     const int m = quarter * 32 + lane;
     const int qr = tp.r0 + m / pl.TW, qx = tp.x0 + m % pl.TW;
     const bool q_in = qr < p.t_h && qx < p.Wtok;
-    const uint64_t colmask = column_mask(p, tp.hx0, qx, q_in);
+    const float none_thresh = -0.5f * p.mask_a * p.mask_b;     // a block maximum below this: every entry masked
     const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
+    const uint32_t p_base = smem_u32(p_smem) + m * 128;
+    const uint32_t xchg_base = smem_u32(&bars->xchg[0][0][0]);
+    const int sw = m & 7;
     const float c2 = p.scale_log2;
+    const bool tr = (m == 0 && half == 0);
     float m_used = -INFINITY, l = 0.f;
+    // `ok` is kept warp-uniform, and a failed wait does not leave the loop: the two warps of a row
+    // pair meet at a named barrier every block, so both must run the same number of iterations.
     bool ok = true;
+    auto wait_all = [&](uint64_t* bar, uint32_t parity) {
+      const bool r = ok && mbar_wait(bar, parity, abort_flag);
+      ok = __all_sync(0xffffffffu, r);
+    };
     for (int j = 0; j < tp.nblk; ++j) {
       const int sb = j & 1, pb = j % pl.pbufs;
-      if (!mbar_wait(&bars->s_full[sb], (j >> 1) & 1, abort_flag)) { ok = false; break; }
-      tc_fence_after();
-      uint32_t sr[128];
-#pragma unroll
-      for (int c = 0; c < 8; ++c)
-        if (c * 16 < N) tmem_ld16(lane_base + kTmemS + sb * 128 + c * 16, &sr[c * 16]);
-      tmem_wait_ld();
-      tc_fence_before();
-      mbar_arrive(&bars->s_empty[sb]);
-
-      uint32_t vm[4];
-      block_mask(vm, p, colmask, tp.hr_first + j * pl.KR, qr, tp.hr_last);
+      if (tr && j == 2) trace_mark(p, 2, 21);
+      wait_all(&bars->s_full[sb], (j >> 1) & 1);
+      if (tr && j == 2) trace_mark(p, 2, 22);
+      uint32_t sr[64];                             // this thread's units: columns c*16 + half*8 .. +8
       float mx = -INFINITY;
+      if (ok) {
+        tc_fence_after();
+        if (tr) trace_mark(p, 2, 1 + 4 * j);
 #pragma unroll
-      for (int e = 0; e < 128; ++e)
-        if (e < N) {
-          float v = __uint_as_float(sr[e]);
-          v = ((vm[e >> 5] >> (e & 31)) & 1u) ? v : -INFINITY;
-          sr[e] = __float_as_uint(v);
-          mx = fmaxf(mx, v);
-        }
+        for (int c = 0; c < 8; ++c)
+          if (c * 16 < N) tmem_ld8(lane_base + kTmemS + sb * 128 + c * 16 + half * 8, &sr[c * 8]);
+        if (tr && j == 2) trace_mark(p, 2, 23);
+        tmem_wait_ld();
+        if (tr && j == 2) trace_mark(p, 2, 24);
+        tc_fence_before();
+        mbar_arrive(&bars->s_empty[sb]);
+        if (tr) trace_mark(p, 2, 2 + 4 * j);
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          if (c * 16 < N) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sr[c * 8 + i]));
+          }
+        mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      }
+      // combine with the thread that owns the other units of this row
+      if (tr && j == 2) trace_mark(p, 2, 25);
+      sts32(xchg_base + ((sb * 2 + half) * 128 + m) * 4, mx);
+      named_bar_sync(1 + quarter, 64);
+      if (tr && j == 2) trace_mark(p, 2, 26);
+      mx = fmaxf(mx, lds32(xchg_base + ((sb * 2 + (half ^ 1)) * 128 + m) * 4));
+      if (mx < none_thresh) mx = -INFINITY;
       // running max with lazy rescale: keep scaling by m_used until the true max exceeds it by 2^8
       bool need = false;
       float m_new = m_used;
@@ -186,90 +241,128 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       const float alpha = need ? exp2f((m_used - m_new) * c2) : 1.f;
       if (need) { m_used = m_new; l *= alpha; }
       const float mc = (m_used == -INFINITY) ? 0.f : m_used * c2;
+      if (tr) trace_mark(p, 2, 3 + 4 * j);
 
-      if (j >= pl.pbufs && !mbar_wait(&bars->p_empty[pb], ((j / pl.pbufs) - 1) & 1, abort_flag)) { ok = false; break; }
-      uint8_t* prow = p_smem + pb * pch * 16384;
-      float lsum = 0.f;
+      if (j >= pl.pbufs) wait_all(&bars->p_empty[pb], ((j / pl.pbufs) - 1) & 1);
+      if (ok) {
+        const uint32_t prow = p_base + pb * pch * 16384;
+        float ls4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int u = 0; u < 16; ++u)
-        if (u * 8 < N) {
-          uint32_t w[4];
+        for (int c = 0; c < 8; ++c)
+          if (c * 16 < N) {
+            uint32_t w[4];
 #pragma unroll
-          for (int h = 0; h < 4; ++h) {
-            const float p0 = exp2f(fmaf(__uint_as_float(sr[u * 8 + 2 * h]), c2, -mc));
-            const float p1 = exp2f(fmaf(__uint_as_float(sr[u * 8 + 2 * h + 1]), c2, -mc));
-            lsum += p0 + p1;
-            w[h] = pack2<BF16>(p0, p1);
+            for (int h = 0; h < 4; ++h) {
+              const float p0 = exp2f(fmaf(__uint_as_float(sr[c * 8 + 2 * h]), c2, -mc));
+              const float p1 = exp2f(fmaf(__uint_as_float(sr[c * 8 + 2 * h + 1]), c2, -mc));
+              ls4[h] += p0 + p1;
+              w[h] = pack2<BF16>(p0, p1);
+            }
+            const int u = 2 * c + half;              // 16-byte unit of the P row (8 keys)
+            sts128(prow + (u >> 3) * 16384 + (((u & 7) ^ sw) << 4), w[0], w[1], w[2], w[3]);
           }
-          *reinterpret_cast<uint4*>(swz(prow + (u >> 3) * 16384, m, u & 7)) = make_uint4(w[0], w[1], w[2], w[3]);
-        }
-      l += lsum;
-      fence_proxy_async_smem();
-      if (any_need && j > 0) {
-        // O must be at rest: wait for PV of block j-1, then scale this thread's row
-        const int pprev = (j - 1) % pl.pbufs;
-        if (!mbar_wait(&bars->p_empty[pprev], ((j - 1) / pl.pbufs) & 1, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        for (int c = 0; c < p.vch * 4; ++c) {
-          uint32_t orow[16];
-          tmem_ld16(lane_base + kTmemO + c * 16, orow);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 16; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
-          tmem_st16(lane_base + kTmemO + c * 16, orow);
-        }
-        tmem_wait_st();
-        tc_fence_before();
+        l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+        if (tr && j == 2) trace_mark(p, 2, 27);
+        fence_proxy_async_smem();
+        if (tr && j == 2) trace_mark(p, 2, 28);
       }
-      mbar_arrive(&bars->p_full[pb]);
+      if (any_need && j > 0) {
+        // O must be at rest: wait for PV of block j-1, then scale this thread's share of the row
+        const int pprev = (j - 1) % pl.pbufs;
+        wait_all(&bars->p_empty[pprev], ((j - 1) / pl.pbufs) & 1);
+        if (ok) {
+          tc_fence_after();
+          for (int c = half; c < p.vch * 4; c += 2) {
+            uint32_t orow[16];
+            tmem_ld16(lane_base + kTmemO + c * 16, orow);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
+            tmem_st16(lane_base + kTmemO + c * 16, orow);
+          }
+          tmem_wait_st();
+          tc_fence_before();
+        }
+      }
+      if (ok) mbar_arrive(&bars->p_full[pb]);
+      if (tr) trace_mark(p, 2, 4 + 4 * j);
     }
-    // epilogue: O / l and lse
-    if (ok && mbar_wait(&bars->o_done, 0, abort_flag)) {
+    // epilogue: O / l and lse; each thread of the pair stores one contiguous half of the row
+    wait_all(&bars->o_done, 0);
+    const uint32_t lsum_base = smem_u32(&bars->lsum[0][0]);
+    sts32(lsum_base + (half * 128 + m) * 4, l);
+    named_bar_sync(1 + quarter, 64);
+    l += lds32(lsum_base + ((half ^ 1) * 128 + m) * 4);
+    if (ok) {
       tc_fence_after();
+      if (tr) trace_mark(p, 2, 30);
       const float inv = 1.f / l;
       const int64_t tok = (int64_t)qr * p.Wtok + qx;
       using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
-      T* orow_g = (T*)o.ptr + bi * o.s0 + hi * o.s1 + tok * o.s2;
-      for (int c = 0; c < p.vch * 4; ++c) {
-        uint32_t orow[16];
-        tmem_ld16(lane_base + kTmemO + c * 16, orow);
+      const int ncol = p.vch * 32;                 // columns per thread: d_v / 2
+      T* orow_g = (T*)o.ptr + bi * o.s0 + hi * o.s1 + tok * o.s2 + half * ncol;
+      for (int c0 = 0; c0 < ncol; c0 += 32) {
+        uint32_t orow[32];
+        tmem_ld16(lane_base + kTmemO + half * ncol + c0, &orow[0]);
+        tmem_ld16(lane_base + kTmemO + half * ncol + c0 + 16, &orow[16]);
         tmem_wait_ld();
         if (q_in) {
-          uint32_t w[8];
+          uint4* dst = reinterpret_cast<uint4*>(orow_g + c0);
 #pragma unroll
-          for (int h = 0; h < 8; ++h)
-            w[h] = pack2<BF16>(__uint_as_float(orow[2 * h]) * inv, __uint_as_float(orow[2 * h + 1]) * inv);
-          uint4* dst = reinterpret_cast<uint4*>(orow_g + c * 16);
-          dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-          dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+          for (int u = 0; u < 4; ++u) {
+            uint32_t w[4];
+#pragma unroll
+            for (int h = 0; h < 4; ++h)
+              w[h] = pack2<BF16>(__uint_as_float(orow[u * 8 + 2 * h]) * inv, __uint_as_float(orow[u * 8 + 2 * h + 1]) * inv);
+            dst[u] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
         }
       }
-      if (q_in) lse[(int64_t)bh * p.t_h * p.Wtok + tok] = m_used * c2 + log2f(l);
+      if (q_in && half == 0) lse[(int64_t)bh * p.t_h * p.Wtok + tok] = m_used * c2 + log2f(l);
       tc_fence_before();
+      if (tr) trace_mark(p, 2, 31);
     }
   } else {
-    // ------------------------------------------------------------------ fused RoPE-2D on Q and K tiles
-    const int t = threadIdx.x - 192;
+    // ------------------------------------------------------------------ fused RoPE-2D on Q and K tiles, mask tiles
+    const int t = threadIdx.x - kFwdRopeThread0;
     const bool rope_on = p.rope.idx != nullptr;
-    if (mbar_wait(&bars->q_full, 0, abort_flag)) {
-      if (rope_on) {
-        const int qr = tp.r0 + t / pl.TW, qx = tp.x0 + t % pl.TW;
-        if (qr < p.t_h && qx < p.Wtok) rotate_row_smem<BF16>(q_smem, 16384, t, qr * p.Wtok + qx, p.rope);
-        fence_proxy_async_smem();
-      }
+    // packed index of this thread's row of the query tile and of its row of block 0, fetched before any wait
+    const int qr = tp.r0 + t / pl.TW, qx = tp.x0 + t % pl.TW;
+    const bool q_in = qr < p.t_h && qx < p.Wtok;
+    const int kjr = t / pl.KW, kx = tp.hx0 + t % pl.KW;           // this thread's row inside every streamed block
+    const bool kx_in = t < N && kx >= 0 && kx < p.Wtok;
+    int32_t k_idx = -1;
+    RopeCache rc;
+    rc.irow = rc.icol = -1;
+    if (rope_on) {
+      if (q_in) rope_fetch(rc, __ldg(p.rope.idx + qr * p.Wtok + qx), p.rope);
+      const int kr0 = tp.hr_first + kjr;
+      if (kx_in && kr0 < p.t_h) k_idx = __ldg(p.rope.idx + kr0 * p.Wtok + kx);
+    }
+    write_indicator_row<BF16>(qx_smem, t, p);
+    if (mbar_wait<100>(&bars->q_full, 0, abort_flag)) {
+      if (t == 0) trace_mark(p, 3, 1);
+      if (rope_on && q_in) rope_apply<BF16>(q_smem, 16384, t, rc, p.rope);
+      fence_proxy_async_smem();
       mbar_arrive(&bars->q_ready);
+      if (t == 0) trace_mark(p, 3, 2);
+      rope_fetch(rc, k_idx, p.rope);               // cos/sin of this thread's row of block 0
       for (int j = 0; j < tp.nblk; ++j) {
         const int s = j % pl.stages;
-        if (!mbar_wait(&bars->kv_full[s], (j / pl.stages) & 1, abort_flag)) break;
-        if (rope_on) {
-          if (t < N) {
-            const int kr = tp.hr_first + j * pl.KR + t / pl.KW, kx = tp.hx0 + t % pl.KW;
-            if (kr < p.t_h && kx >= 0 && kx < p.Wtok)
-              rotate_row_smem<BF16>(k_smem + s * k_stage, blk_bytes, t, kr * p.Wtok + kx, p.rope);
-          }
-          fence_proxy_async_smem();
-        }
+        const int kr = tp.hr_first + j * pl.KR + kjr;
+        // index of the same row of the next block: in flight while this block is rotated
+        int32_t k_idx_next = -1;
+        if (rope_on && kx_in && j + 1 < tp.nblk && kr + pl.KR < p.t_h) k_idx_next = __ldg(p.rope.idx + (kr + pl.KR) * p.Wtok + kx);
+        // the stage (K, V and penalty rows) is free once its refill has landed: the producer refills
+        // only after every MMA of the stage's previous block has completed
+        if (!mbar_wait<100>(&bars->kv_full[s], (j / pl.stages) & 1, abort_flag)) break;
+        if (t == 0) trace_mark(p, 3, 3 + 2 * j);
+        if (t < N) write_penalty_row<BF16>(kx_smem + s * kx_stage, t, p, tp.r0, tp.x0, kr, kx);
+        if (rope_on && kx_in && kr < p.t_h) rope_apply<BF16>(k_smem + s * k_stage, blk_bytes, t, rc, p.rope);
+        fence_proxy_async_smem();
         mbar_arrive(&bars->k_ready[s]);
+        if (t == 0) trace_mark(p, 3, 4 + 2 * j);
+        rope_fetch(rc, k_idx_next, p.rope);        // lands while this thread waits for the next block
       }
     }
   }

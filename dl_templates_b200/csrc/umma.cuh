@@ -13,6 +13,41 @@ namespace ptx {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
+// ---- explicit shared-space 16-byte accesses (a generic pointer would compile to generic ld/st) ---
+__device__ __forceinline__ void sts128(uint32_t saddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(saddr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t saddr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(saddr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void sts32(uint32_t saddr, float v) {
+  asm volatile("st.shared.f32 [%0], %1;" ::"r"(saddr), "f"(v) : "memory");
+}
+__device__ __forceinline__ float lds32(uint32_t saddr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(saddr) : "memory");
+  return v;
+}
+// named barrier among `count` threads (count a multiple of 32); id 0 is __syncthreads
+__device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
+// One lane of a converged warp.  Roles that issue TMA / MMA instructions keep the whole warp in
+// the (warp-uniform) control flow and let only the elected lane execute the instruction, so that
+// descriptor and address arithmetic stays on the uniform datapath.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "elect.sync _|P, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // ---- mbarrier ----------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
@@ -35,18 +70,38 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-constexpr uint32_t kWaitFastPolls = 1u << 12;  // polls before backing off
-constexpr uint32_t kWaitMaxPolls = 1u << 22;   // then ~100 ns sleeps: gives up after roughly half a second
+// try_wait that lets the hardware park the thread for up to `hint_ns` before it reports failure.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+
+constexpr uint32_t kWaitMaxPolls = 1u << 22;  // polls (spinning) resp. sleeps before a wait gives up: about half a second
 
 // Wait for the phase with the given parity to complete.  Returns false when the
 // CTA-wide abort flag is (or becomes) set or the poll budget runs out; in the
 // latter case it sets the flag so that every other role of the CTA leaves too.
+//
+// PARK_NS == 0: spin on try_wait (warps on the critical path).  PARK_NS > 0: each poll lets the
+// hardware park the thread for up to PARK_NS nanoseconds and wake it when the phase completes, so
+// a waiting warp takes (almost) no issue slots from the working warps of its sub-partition.
+template <uint32_t PARK_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
   for (uint32_t it = 0; it < kWaitMaxPolls; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (it > kWaitFastPolls) {
-      if (*abort_flag) return false;
-      __nanosleep(100);
+    if constexpr (PARK_NS == 0) {
+      if (mbar_try_wait(bar, parity)) return true;
+      if ((it & 1023u) == 1023u && *abort_flag) return false;
+    } else {
+      if (mbar_try_wait_hint(bar, parity, PARK_NS)) return true;
+      if ((it & 15u) == 15u && *abort_flag) return false;
     }
   }
   *abort_flag = 1;
@@ -98,6 +153,24 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
          ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
 }
 
+// The upper 32 bits of a descriptor do not depend on the start address: build them once and
+// combine them with a 16-byte-granular address when an MMA is issued.
+__device__ __forceinline__ uint32_t smem_desc_hi(uint32_t sbo_bytes, bool swizzle128) {
+  return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (swizzle128 ? (2u << 29) : 0u);
+}
+__device__ __forceinline__ uint64_t smem_desc_from(uint32_t saddr, uint32_t lbo_bytes, uint32_t hi) {
+  const uint32_t lo = ((saddr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+  return ((uint64_t)hi << 32) | lo;
+}
+
+// Same descriptor format without swizzling ("interleaved" core matrices), K-major: a core matrix
+// is 8 rows x 16 bytes stored contiguously (128 B); the second 16-byte column of a K=16 step lies
+// `lbo` bytes after the first, the next 8 rows `sbo` bytes further.
+__device__ __forceinline__ uint64_t smem_desc_noswizzle(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+         ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46);
+}
+
 // Instruction descriptor for kind::f16 with fp32 accumulation.
 //   fmt: 0 = fp16 operands, 1 = bf16 operands; a_mn / b_mn: 1 = that operand is MN-major.
 __host__ __device__ __forceinline__ uint32_t instr_desc(uint32_t fmt, uint32_t M, uint32_t N, uint32_t a_mn, uint32_t b_mn) {
@@ -127,6 +200,12 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t* r) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
 }
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
   asm volatile(

@@ -41,14 +41,14 @@ def _status(device: torch.device) -> torch.Tensor:
     bounded waits gives up; stays zero in normal operation."""
     key = (device.type, device.index)
     if key not in _status_words:
-        _status_words[key] = torch.zeros(4, dtype=torch.int32, device=device)
+        _status_words[key] = torch.zeros(1024, dtype=torch.int32, device=device)
     return _status_words[key]
 
 
 def check_status(device=None) -> None:
     """Synchronise and raise if any kernel reported a timed-out wait."""
     for key, word in _status_words.items():
-        vals = word.cpu().tolist()
+        vals = word[:4].cpu().tolist()
         if vals[0] != 0:
             word.zero_()
             raise RuntimeError(f"swa2d kernel reported a bounded-wait timeout on {key}: status={vals}")
