@@ -35,6 +35,14 @@ import torch
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+# DRAM bytes (read + write) per launch and per (batch, head) slice, from one `ncu --set full` capture at
+# B*H = 64 (profiles/ncu_full_target_bh64_all_kernels.md); traffic grows in proportion to B*H.
+TRAFFIC_BYTES_PER_BH = {
+    "target:fwd": (402.9e6 + 121.4e6) / 64,
+    "target:dq": (545.5e6 + 120.6e6) / 64,
+    "target:dkdv": (546.0e6 + 240.9e6) / 64,
+}
+
 METRIC = "2D-SWA fwd+bwd TFLOP/s (windowed FLOPs, whole job)"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -371,14 +379,8 @@ def main():
         dom = max((n for n in med if n != "delta"), key=med.get)
     achieved = alg[dom] / (med[dom] * 1e-3) / 1e12
     peak = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
-    traffic = None
-    tpath = os.path.join(ROOT, "profiles", "traffic_per_launch.json")
-    if os.path.exists(tpath):
-        with open(tpath) as f:
-            tj = json.load(f)
-        ent = tj.get(f"{args.workload}:{dom}")
-        if ent:
-            traffic = ent["bytes_per_bh"] * bh_local
+    per_bh = TRAFFIC_BYTES_PER_BH.get(f"{args.workload}:{dom}") if args.rope_dims < 0 else None
+    traffic = per_bh * bh_local if per_bh else None
     roofline = {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                 "frac": achieved / peak, "traffic": traffic, "peak_source": peaks["_source"] + " (sustained bf16)",
                 "kernel_ms": med,

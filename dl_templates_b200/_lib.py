@@ -41,7 +41,7 @@ EXPORTS = ("swa_fwd", "swa_bwd_delta", "swa_bwd_dq", "swa_bwd_dkdv", "rope2d_app
 def _load() -> C.CDLL:
     if not os.path.exists(LIB_PATH):
         raise RuntimeError(
-            f"{LIB_PATH} is missing: build it with `python -m dl_templates_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python dl_templates_b200/build.py` "
             "(nvcc, sm_100a). This package has no fallback implementation.")
     lib = C.CDLL(LIB_PATH)
     P = C.POINTER

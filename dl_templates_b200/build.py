@@ -1,6 +1,6 @@
 """Build recipe for the C-ABI shared library (``libswa2d.so``) next to this file.
 
-``python -m dl_templates_b200.build`` compiles every ``.cu`` under ``csrc/`` for
+``python dl_templates_b200/build.py`` compiles every ``.cu`` under ``csrc/`` for
 sm_100a with nvcc (cross-compiles without a GPU) and links one shared object that
 depends only on the CUDA runtime -- no libtorch, no libcuda link (the driver entry
 point for tensor-map encoding is fetched at run time).
