@@ -14,6 +14,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libswa2d.so")
 
 SWA_F32, SWA_F16, SWA_BF16 = 0, 1, 2
+NOALLOC_MAX_ROWS = 1 << 21          # SWA_NOALLOC_MAX_ROWS of include/swa2d.h
 IMPL_AUTO, IMPL_SIMT, IMPL_TC = 0, 1, 2
 _IMPL_BY_NAME = {"auto": IMPL_AUTO, "simt": IMPL_SIMT, "tc": IMPL_TC}
 _DTYPES = {torch.float32: SWA_F32, torch.float16: SWA_F16, torch.bfloat16: SWA_BF16}
@@ -34,7 +35,7 @@ class Rope(C.Structure):
                 ("n_rdim", C.c_int32), ("max_h", C.c_int32), ("max_w", C.c_int32)]
 
 
-EXPORTS = ("swa_fwd", "swa_bwd_delta", "swa_bwd_dq", "swa_bwd_dkdv", "rope2d_apply", "swa_select_impl",
+EXPORTS = ("swa_fwd", "swa_bwd_delta", "swa_bwd_dq", "swa_bwd_dkdv", "swa_bwd_noalloc", "rope2d_apply", "swa_select_impl",
            "swa_launch_count", "swa_last_error", "swa_version")
 
 
@@ -52,11 +53,13 @@ def _load() -> C.CDLL:
                                C.c_void_p, P(Tensor4), C.c_void_p, C.c_void_p]
     lib.swa_bwd_dkdv.argtypes = [P(Geom), P(Rope), P(Tensor4), P(Tensor4), P(Tensor4), P(Tensor4), C.c_void_p,
                                  C.c_void_p, P(Tensor4), P(Tensor4), C.c_void_p, C.c_void_p]
+    lib.swa_bwd_noalloc.argtypes = [P(Geom), P(Rope), P(Tensor4), P(Tensor4), P(Tensor4), P(Tensor4), P(Tensor4),
+                                    C.c_void_p, P(Tensor4), P(Tensor4), P(Tensor4), C.c_void_p, C.c_void_p]
     lib.rope2d_apply.argtypes = [C.c_int32, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, P(C.c_int64), P(Rope),
                                  C.c_int32, C.c_void_p]
     lib.swa_select_impl.argtypes = [P(Geom), P(Rope), C.c_int32]
-    for name in ("swa_fwd", "swa_bwd_delta", "swa_bwd_dq", "swa_bwd_dkdv", "rope2d_apply", "swa_select_impl",
-                 "swa_version"):
+    for name in ("swa_fwd", "swa_bwd_delta", "swa_bwd_dq", "swa_bwd_dkdv", "swa_bwd_noalloc", "rope2d_apply",
+                 "swa_select_impl", "swa_version"):
         getattr(lib, name).restype = C.c_int
     lib.swa_launch_count.restype = C.c_int64
     lib.swa_last_error.restype = C.c_char_p

@@ -3,6 +3,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "common.cuh"
 #include "stream_kernels.cuh"
@@ -215,6 +216,51 @@ int swa_bwd_dkdv(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t
                                    gg, rp, swa::make_view(q), swa::make_view(k), swa::make_view(v),
                                    swa::make_view(d_o), lse, delta, swa::make_view(dk), swa::make_view(dv)));
   return launch_ok("simt dkdv");
+}
+
+// ---- backward without allocation ------------------------------------------------------------
+// Scratch for the softmax delta of swa_bwd_noalloc.  In host code this name is only a handle of
+// the symbol, not a device address: the address is looked up once per device below.
+static __device__ __align__(256) float g_noalloc_delta[SWA_NOALLOC_MAX_ROWS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_noalloc_mu;
+float* g_noalloc_ptr[kMaxDevices] = {};
+
+// Device address of g_noalloc_delta on the current device (set-up on first use, no allocation).
+int noalloc_scratch(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(E_LAUNCH, "cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(E_SHAPE, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_noalloc_mu);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_delta);
+    if (e != cudaSuccess || p == nullptr)
+      return fail(E_LAUNCH, "cudaGetSymbolAddress(delta scratch) on device %d: %s", dev, cudaGetErrorString(e));
+    g_noalloc_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_noalloc_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+int swa_bwd_noalloc(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
+                    const swa_tensor_t* v, const swa_tensor_t* o, const swa_tensor_t* d_o, const float* lse,
+                    const swa_tensor_t* dq, const swa_tensor_t* dk, const swa_tensor_t* dv, int32_t* status,
+                    void* stream) {
+  if (int e = check_geom(g)) return e;
+  const int64_t rows = (int64_t)g->B * g->H * g->t_height * g->t_width * g->b_size;
+  if (rows > (int64_t)SWA_NOALLOC_MAX_ROWS)
+    return fail(E_SHAPE, "swa_bwd_noalloc: B*H*N = %lld exceeds the built-in scratch of %d rows; use swa_bwd_delta/"
+                "swa_bwd_dq/swa_bwd_dkdv with a caller-provided delta buffer", (long long)rows, SWA_NOALLOC_MAX_ROWS);
+  float* delta = nullptr;
+  if (int e = noalloc_scratch(&delta)) return e;
+  if (int e = swa_bwd_delta(g, o, d_o, delta, stream)) return e;
+  if (int e = swa_bwd_dq(g, rope, q, k, v, d_o, lse, delta, dq, status, stream)) return e;
+  return swa_bwd_dkdv(g, rope, q, k, v, d_o, lse, delta, dk, dv, status, stream);
 }
 
 int rope2d_apply(int32_t dtype, void* x, int64_t batch, int64_t n_tokens, int32_t n_dim, const int64_t* xs,

@@ -116,6 +116,27 @@ def swa_backward(q, k, v, o, lse, do, rope, b_size, t_height, t_width, row_size,
     return dq, dk, dv
 
 
+def swa_backward_noalloc(q, k, v, o, lse, do, rope, b_size, t_height, t_width, row_size, col_size, sm_scale, dq, dk,
+                         dv, impl="auto"):
+    """Backward pass into caller-provided ``dq, dk, dv`` through ``swa_bwd_noalloc``: the library
+    neither allocates nor frees anything, the softmax-delta scratch lives in a fixed array
+    inside the library (limit: ``B*H*N <= _lib.NOALLOC_MAX_ROWS``).  Meant for callers that own
+    no allocator (everything, outputs included, comes from memory they reserved up front).
+    Calls on one device share that array, so do not let two of them overlap on the GPU; the
+    first call on a device does a one-time address lookup and should come before any stream
+    capture.  Returns ``(dq, dk, dv)``."""
+    B, H, N, _ = q.shape
+    g = _geom(q, v, b_size, t_height, t_width, row_size, col_size, sm_scale, impl)
+    r = _lib.make_rope(*rope) if rope is not None else None
+    tq, tk, tv, to, tdo, tdq, tdk, tdv = (_lib.tensor4(t) for t in (q, k, v, o, do, dq, dk, dv))
+    with torch.cuda.device(q.device):
+        code = _lib.lib.swa_bwd_noalloc(C.byref(g), _ref(r), C.byref(tq), C.byref(tk), C.byref(tv), C.byref(to),
+                                        C.byref(tdo), lse.data_ptr(), C.byref(tdq), C.byref(tdk), C.byref(tdv),
+                                        _status(q.device).data_ptr(), _lib.stream_ptr(q.device))
+    _lib.check(code, "swa_bwd_noalloc")
+    return dq, dk, dv
+
+
 def selected_impl(q, v, rope, b_size, t_height, t_width, row_size, col_size, sm_scale=1.0, which=0, impl="auto"):
     """'tc' or 'simt': the kernel family a call with these shapes would run."""
     g = _geom(q, v, b_size, t_height, t_width, row_size, col_size, sm_scale, impl)

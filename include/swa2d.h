@@ -100,6 +100,29 @@ int swa_bwd_dkdv(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t
 int rope2d_apply(int32_t dtype, void* x, int64_t batch, int64_t n_tokens, int32_t n_dim, const int64_t* xs,
                  const swa_rope_t* rope, int32_t inverse, void* stream);
 
+/* Whole backward pass (delta, then dq, then dk/dv) for callers that must not allocate.
+ * This entry point has no counterpart in the reference; it exists for hosts that cannot call
+ * cudaMalloc around the op: a plugin running inside a runtime that has already handed all device
+ * memory to its own arena, a serving loop that may not take the device-wide synchronisation an
+ * allocation implies, or a caller that simply owns no allocator handle.  The backward pass
+ * needs one scratch vector, delta[B*H*N] in fp32; the other entry points take it from the
+ * caller, this one keeps it in a fixed array inside the library image, so
+ *   - B*H*N may not exceed SWA_NOALLOC_MAX_ROWS (the call is rejected with an error otherwise);
+ *   - every GPU that loads the library holds that array (SWA_NOALLOC_MAX_ROWS * 4 bytes) until
+ *     the process exits, whether or not this entry point is ever used;
+ *   - all calls on a device share the array: two calls whose kernels may overlap on the GPU
+ *     (different streams, no dependency between them) race on it -- serialise them.  Nothing
+ *     in it has to start at zero: each call overwrites the rows it then reads;
+ *   - the first call on a device looks up the array's device address (no allocation); make that
+ *     first call before starting any stream capture on that device.
+ * The caller passes every input and every output (dq, dk, dv); nothing is allocated or freed.
+ * Results are identical to swa_bwd_delta + swa_bwd_dq + swa_bwd_dkdv on the same arguments. */
+#define SWA_NOALLOC_MAX_ROWS (1 << 21)
+int swa_bwd_noalloc(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
+                    const swa_tensor_t* v, const swa_tensor_t* o, const swa_tensor_t* d_o, const float* lse,
+                    const swa_tensor_t* dq, const swa_tensor_t* dk, const swa_tensor_t* dv, int32_t* status,
+                    void* stream);
+
 /* Which kernel family swa_fwd / swa_bwd_dq / swa_bwd_dkdv would run for this
  * geometry: SWA_IMPL_SIMT or SWA_IMPL_TC (negative = rejected). `which`: 0 fwd, 1 dq, 2 dkdv. */
 int swa_select_impl(const swa_geom_t* g, const swa_rope_t* rope, int32_t which);
