@@ -19,7 +19,7 @@ namespace {
 
 thread_local char g_tc_err[256] = "";
 constexpr uint32_t kSmemLimit = 227 * 1024;
-constexpr uint32_t kSmemSlack = 6144;  // 1 KiB alignment + lse/delta staging + barriers and exchange buffers
+constexpr uint32_t kSmemSlack = 14336;  // 1 KiB alignment + lse/delta staging + barriers, exchange buffers, penalty tables
 
 PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
   static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
@@ -97,8 +97,8 @@ bool make_plan(const swa_geom_t* g, int which, Plan* out) {
   const uint32_t fixed = (which == 0 ? qch : qch + vch) * 16384u + 128u * kXRowBytes;
   const uint32_t row_bytes = (qch + vch) * 128u + kXRowBytes;
   const int p_ops = which == 2 ? 2 : 1;
-  // the backward kernels double-buffer S and dP in TMEM next to two accumulators: 64 columns per buffer
-  const int nmax = env_int("SWA_TC_NMAX", which == 0 ? 128 : 64);
+  // blocks of up to 128 streamed tokens (the backward kernels double-buffer S and dP in TMEM up to 64)
+  const int nmax = env_int("SWA_TC_NMAX", 128);
   long best_cost = -1;
   for (int KW = hw; KW <= 64; ++KW)
     for (int KR = 1; KR <= 16; ++KR) {
@@ -191,6 +191,7 @@ const char* unsupported_reason(const swa_geom_t* g, const swa_rope_t* rope, cons
   float ma, mb;
   if (!mask_constants(g->sm_scale, &ma, &mb)) return "sm_scale too small for the MMA-side window mask";
   if (rope && rope->idx && rope->n_rdim % 8) return "n_rdim must be a multiple of 8";
+  if (g->row_size > 64) return "row window too tall for the penalty tables";
   if ((int64_t)g->t_height * g->t_width * g->b_size > (1 << 30)) return "grid too large";
   Plan pl;
   if (!make_plan(g, which, &pl)) return "no tile plan fits (window too wide for one streamed block)";

@@ -5,7 +5,7 @@
 //   DKDV = true   (dK/dV kernel) resident tile X = (K, V) of 128 keys,
 //                                streamed blocks Y = (Q, dO) of the halo queries
 //
-// Per streamed block (N <= 64 tokens), with T = the resident token (one TMEM lane):
+// Per streamed block (N <= 128 tokens), with T = the resident token (one TMEM lane):
 //   S  = Xqk Yqk^T  (+ the window mask as 32 extra contraction columns)
 //   dP = Xv  Yv^T
 //   P  = exp2(scale*log2e * S - lse[query])      (exactly 0 outside the window)
@@ -22,8 +22,8 @@
 // keep the whole warp in uniform control flow and let one elected lane issue),
 // warps 2-9 compute: TWO threads per resident token -- warps w and w+4 share a TMEM
 // lane quarter and take the lower / upper half of each block's columns -- then the
-// epilogue; warps 10-13 RoPE rotation of the tiles, the window-mask tiles and staging
-// of lse/delta.  S and dP are double-buffered in TMEM so the tensor core works on
+// epilogue; warps 10-13 RoPE rotation of the tiles (two threads per row of a streamed block:
+// row-angle and column-angle pairs), the window-mask tiles and staging of lse/delta.  S and dP are double-buffered in TMEM so the tensor core works on
 // block j+1 while the compute warps work on j.
 // TMEM columns: S[2] at 0/64, dP[2] at 128/192, acc_qk at 256, acc_v at 384.
 #pragma once
@@ -39,6 +39,7 @@ struct BwdBars {
   uint64_t x_full, x_ready, acc_done;
   uint64_t y_full[kMaxStages], y_ready[kMaxStages], y_empty[kMaxStages];
   uint64_t sd_full[2], sd_empty[2], op_full[2], op_empty[2];
+  PenaltyTables pen;  // window-mask penalty parts of this CTA's halo rows / columns
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -127,6 +128,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ C
   const uint32_t blk_bytes = (uint32_t)N * 128u;
   const uint32_t yqk_stage = blk_bytes * p.qch, yv_stage = blk_bytes * p.vch;
   constexpr int kOps = DKDV ? 2 : 1;                       // 16-bit operand tiles written per block: dS (and P)
+  const int pch = (N + 63) >> 6;                           // 64-column chunks of such a tile
+  const int nsb = N <= 64 ? 2 : 1;                         // S / dP buffers in TMEM
   const uint32_t yx_stage = (uint32_t)N * kXRowBytes;      // window-mask penalty rows of a streamed block
   uint8_t* xqk_smem = smem;
   uint8_t* xv_smem = xqk_smem + p.qch * 16384;
@@ -134,9 +137,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ C
   uint8_t* yqk_smem = xx_smem + 128 * kXRowBytes;
   uint8_t* yv_smem = yqk_smem + pl.stages * yqk_stage;
   uint8_t* yx_smem = yv_smem + pl.stages * yv_stage;
-  uint8_t* op_smem = yx_smem + pl.stages * yx_stage;       // [pbufs][kOps][128 x 64] : dS then P
-  float* vec_smem = reinterpret_cast<float*>(op_smem + pl.pbufs * kOps * 16384);  // [stages][2][64]: lse, delta
-  BwdBars* bars = reinterpret_cast<BwdBars*>(reinterpret_cast<uint8_t*>(vec_smem) + kMaxStages * 2 * 64 * 4);
+  uint8_t* op_smem = yx_smem + pl.stages * yx_stage;       // [pbufs][kOps][pch][128 x 64] : dS then P
+  float* vec_smem = reinterpret_cast<float*>(op_smem + pl.pbufs * kOps * pch * 16384);  // [stages][2][128]: lse, delta
+  BwdBars* bars = reinterpret_cast<BwdBars*>(reinterpret_cast<uint8_t*>(vec_smem) + kMaxStages * 2 * 128 * 4);
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5;
@@ -144,6 +147,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ C
   const int bh = blockIdx.y, bi = bh / p.H, hi = bh - bi * p.H;
   const TilePos tp = tile_pos(p, blockIdx.x);
   const int64_t vec_base = (int64_t)bh * p.t_h * p.Wtok;
+  if (threadIdx.x == 64) trace_mark(p, 0, 31);
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->x_full, 1);
@@ -224,26 +228,27 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ C
       wait_spin(&bars->op_full[pb], (i / pl.pbufs) & 1);
       if (!ok) return;
       tc_fence_after();
-      const uint32_t ds_addr = ops + (pb * kOps) * 16384, yqk_s = yqk + s * yqk_stage, yv_s = yv + s * yv_stage;
+      const uint32_t ds_addr = ops + (pb * kOps) * pch * 16384, yqk_s = yqk + s * yqk_stage, yv_s = yv + s * yv_stage;
       if (elect_one()) {
         for (int ks = 0; ks < (N >> 4); ++ks)
-          umma_ss(tmem + kTmAccQK, smem_desc_from(ds_addr + ks * 32, 16, hi_sw),
+          umma_ss(tmem + kTmAccQK, smem_desc_from(ds_addr + (ks >> 2) * 16384 + (ks & 3) * 32, 16, hi_sw),
                   smem_desc_from(yqk_s + ks * 2048, blk_bytes, hi_sw), idesc_aqk, (i > 0 || ks > 0) ? 1u : 0u);
         if constexpr (DKDV) {
           for (int ks = 0; ks < (N >> 4); ++ks)
-            umma_ss(tmem + kTmAccV, smem_desc_from(ds_addr + 16384 + ks * 32, 16, hi_sw),
+            umma_ss(tmem + kTmAccV, smem_desc_from(ds_addr + (pch + (ks >> 2)) * 16384 + (ks & 3) * 32, 16, hi_sw),
                     smem_desc_from(yv_s + ks * 2048, blk_bytes, hi_sw), idesc_av, (i > 0 || ks > 0) ? 1u : 0u);
         }
         umma_commit(&bars->y_empty[s]);
         umma_commit(&bars->op_empty[pb]);
         if (i == tp.nblk - 1) umma_commit(&bars->acc_done);
+        trace_mark(p, 1, 2 * i + 1);
       }
       __syncwarp();
     };
     for (int j = 0; ok && j < tp.nblk; ++j) {
-      const int s = j % pl.stages, sb = j & 1;
+      const int s = j % pl.stages, sb = j % nsb;
       wait_spin(&bars->y_ready[s], (j / pl.stages) & 1);
-      if (j >= 2) wait_spin(&bars->sd_empty[sb], ((j >> 1) - 1) & 1);
+      if (j >= nsb) wait_spin(&bars->sd_empty[sb], ((j / nsb) - 1) & 1);
       if (!ok) break;
       tc_fence_after();
       const uint32_t yqk_s = yqk + s * yqk_stage, yv_s = yv + s * yv_stage, yx_s = yx + s * yx_stage;
@@ -265,6 +270,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ C
                     smem_desc_from(yv_s + c * blk_bytes + k * 32, 16, hi_sw), idesc_s, (c | k) ? 1u : 0u);
         }
         umma_commit(&bars->sd_full[sb]);
+        trace_mark(p, 1, 2 * j);
       }
       __syncwarp();
       if (j >= 1) issue_acc(j - 1);
@@ -280,7 +286,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ C
     const int64_t tok = (int64_t)tr * p.Wtok + tx;
     const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
     const float c2 = p.scale_log2;
-    const int nh = N >> 1;                        // columns per thread, a multiple of 8, <= 32
+    const int nh = N >> 1;                        // columns per thread, a multiple of 8, <= 64
     const int col0 = half * nh;
     const int sw = m & 7;
     float my_lse = INFINITY, my_delta = 0.f;
@@ -291,14 +297,15 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ C
     const uint32_t op_base = smem_u32(op_smem) + m * 128;
     const uint32_t vec_addr = smem_u32(vec_smem);
     for (int j = 0; j < tp.nblk && ok; ++j) {
-      const int sb = j & 1, pb = j % pl.pbufs, s = j % pl.stages;
-      wait_spin(&bars->sd_full[sb], (j >> 1) & 1);
+      const int sb = j % nsb, pb = j % pl.pbufs, s = j % pl.stages;
+      wait_spin(&bars->sd_full[sb], (j / nsb) & 1);
       if (DKDV) wait_spin(&bars->y_ready[s], (j / pl.stages) & 1);   // lse/delta of the block are staged
       if (j >= pl.pbufs) wait_spin(&bars->op_empty[pb], ((j / pl.pbufs) - 1) & 1);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t ds_row = op_base + (pb * kOps) * 16384;
-      const uint32_t lse_s = vec_addr + (s * 128) * 4, dl_s = lse_s + 64 * 4;
+      if (m == 0 && half == 0) trace_mark(p, 2, 2 * j);
+      const uint32_t ds_row = op_base + (pb * kOps) * pch * 16384;
+      const uint32_t lse_s = vec_addr + (s * 256) * 4, dl_s = lse_s + 128 * 4;
       // columns [col0 + off, col0 + off + CNT) of the block
       auto process = [&](int off, auto cnt_tag) {
         constexpr int CNT = decltype(cnt_tag)::value;
@@ -342,23 +349,24 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ C
             wp[h] = pack2<BF16>(pv[0], pv[1]);
           }
           const int unit = ((col0 + off) >> 3) + u;
-          const uint32_t a = ds_row + ((unit ^ sw) << 4);
+          const uint32_t a = ds_row + (unit >> 3) * 16384 + (((unit & 7) ^ sw) << 4);
           sts128(a, wds[0], wds[1], wds[2], wds[3]);
-          if constexpr (DKDV) sts128(a + 16384, wp[0], wp[1], wp[2], wp[3]);
+          if constexpr (DKDV) sts128(a + pch * 16384, wp[0], wp[1], wp[2], wp[3]);
         }
       };
-      if (nh >= 16) process(0, std::integral_constant<int, 16>{});
-      if (nh >= 32) process(16, std::integral_constant<int, 16>{});
+      for (int off = 0; off + 16 <= nh; off += 16) process(off, std::integral_constant<int, 16>{});
       if (nh & 8) process(nh - 8, std::integral_constant<int, 8>{});
       tc_fence_before();
       mbar_arrive(&bars->sd_empty[sb]);
       fence_proxy_async_smem();
       mbar_arrive(&bars->op_full[pb]);
+      if (m == 0 && half == 0) trace_mark(p, 2, 2 * j + 1);
     }
     // epilogue: the two threads of a row each store half of the accumulator row(s)
     wait_spin(&bars->acc_done, 0);
     if (ok) {
       tc_fence_after();
+      if (m == 0 && half == 0) trace_mark(p, 2, 30);
       using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
       const bool rot = p.rope.idx != nullptr && t_in;
       int irow = -1, icol = -1;
@@ -370,57 +378,71 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ C
         store_acc_row<BF16>(lane_base + kTmAccV, p.vch, half, 1.f, false, -1, -1, p.rope, v_row, t_in);
       }
       tc_fence_before();
+      if (m == 0 && half == 0) trace_mark(p, 2, 31);
     }
   } else {
     // ------------------------------------------------------------------ RoPE on the q/k tiles, mask tiles, lse/delta staging
     const int t = threadIdx.x - kBwdRopeThread0;
     const bool rope_on = p.rope.idx != nullptr;
-    const int xr = tp.r0 + t / pl.TW, xx_ = tp.x0 + t % pl.TW;
+    const RopeParts xp = rope_parts(t, 128), yp = rope_parts(t, N);   // share of the resident tile / of a streamed block
+    const int xr = tp.r0 + xp.row / pl.TW, xx_ = tp.x0 + xp.row % pl.TW;
     const bool x_in = xr < p.t_h && xx_ < p.Wtok;
-    const int yjr = t / pl.KW, yx_ = tp.hx0 + t % pl.KW;           // this thread's row inside every streamed block
-    const bool yx_in = t < N && yx_ >= 0 && yx_ < p.Wtok;
+    const int yjr = yp.row / pl.KW, yx_ = tp.hx0 + yp.row % pl.KW;    // this thread's row inside every streamed block
+    const bool yx_in = yp.active && yx_ >= 0 && yx_ < p.Wtok;
     int32_t y_idx = -1;
-    RopeCache rc;
-    rc.irow = rc.icol = -1;
+    RopeRow rc;
+    rc.pos[0] = rc.pos[1] = -1;
     if (rope_on) {
-      if (x_in) rope_fetch(rc, __ldg(p.rope.idx + xr * p.Wtok + xx_), p.rope);
+      if (x_in) rope_fetch(rc, __ldg(p.rope.idx + xr * p.Wtok + xx_), xp, p.rope);
       const int yr0 = tp.hr_first + yjr;
       if (yx_in && yr0 < p.t_h) y_idx = __ldg(p.rope.idx + yr0 * p.Wtok + yx_);
     }
-    write_indicator_row<BF16>(xx_smem, t, p);
+    write_indicator_row<BF16>(xx_smem, xp.row, xp.lo, xp.hi, p);
+    build_penalty_tables<BF16>(&bars->pen, t, p, tp);
+    named_bar_sync(5, 128);                          // the tables are complete before any of these warps reads them
     wait_park(&bars->x_full, 0);
     if (ok) {
-      if (rope_on && x_in) rope_apply<BF16>(xqk_smem, 16384, t, rc, p.rope);
+      if (rope_on && x_in) rope_apply<BF16>(xqk_smem, 16384, rc, xp, p.rope);
       fence_proxy_async_smem();
       mbar_arrive(&bars->x_ready);
-      rope_fetch(rc, y_idx, p.rope);               // cos/sin of this thread's row of block 0
+      rope_fetch(rc, y_idx, yp, p.rope);           // cos/sin of this thread's row of block 0
       for (int j = 0; j < tp.nblk; ++j) {
         const int s = j % pl.stages;
         const int yr = tp.hr_first + j * pl.KR + yjr;
         const bool in = yx_in && yr < p.t_h;
         int32_t y_idx_next = -1;
         if (rope_on && yx_in && j + 1 < tp.nblk && yr + pl.KR < p.t_h) y_idx_next = __ldg(p.rope.idx + (yr + pl.KR) * p.Wtok + yx_);
+        // lse and delta of the block's queries: thread t stages both values of block row t
         float lse_v = INFINITY, delta_v = 0.f;
-        if (DKDV && in) {
-          lse_v = __ldg(lse + vec_base + (int64_t)yr * p.Wtok + yx_);
-          delta_v = __ldg(delta + vec_base + (int64_t)yr * p.Wtok + yx_);
+        if constexpr (DKDV) {
+          if (t < N) {
+            const int vr = tp.hr_first + j * pl.KR + t / pl.KW, vx = tp.hx0 + t % pl.KW;
+            if (vr < p.t_h && vx >= 0 && vx < p.Wtok) {
+              lse_v = __ldg(lse + vec_base + (int64_t)vr * p.Wtok + vx);
+              delta_v = __ldg(delta + vec_base + (int64_t)vr * p.Wtok + vx);
+            }
+          }
         }
         // the stage (tiles, penalty rows, lse/delta slots) is free once its refill has landed: the
         // producer refills only after every MMA of the stage's previous block has completed, which in
         // turn is after the compute warps finished reading that block's lse/delta
         wait_park(&bars->y_full[s], (j / pl.stages) & 1);
         if (!ok) break;
-        if (t < N) {
-          write_penalty_row<BF16>(yx_smem + s * yx_stage, t, p, tp.r0, tp.x0, yr, yx_);
-          if (rope_on && in) rope_apply<BF16>(yqk_smem + s * yqk_stage, blk_bytes, t, rc, p.rope);
-          if constexpr (DKDV) {
-            vec_smem[s * 128 + t] = lse_v;
-            vec_smem[s * 128 + 64 + t] = delta_v;
+        if (t == 0) trace_mark(p, 3, 2 * j);
+        if (yp.active) {
+          write_penalty_row(yx_smem + s * yx_stage, yp.row, yp.lo, yp.hi, &bars->pen, j * pl.KR + yjr, yp.row % pl.KW);
+          if (rope_on && in) rope_apply<BF16>(yqk_smem + s * yqk_stage, blk_bytes, rc, yp, p.rope);
+        }
+        if constexpr (DKDV) {
+          if (t < N) {
+            vec_smem[s * 256 + t] = lse_v;
+            vec_smem[s * 256 + 128 + t] = delta_v;
           }
         }
         fence_proxy_async_smem();
         mbar_arrive(&bars->y_ready[s]);
-        rope_fetch(rc, y_idx_next, p.rope);        // lands while this thread waits for the next block
+        if (t == 0) trace_mark(p, 3, 2 * j + 1);
+        rope_fetch(rc, y_idx_next, yp, p.rope);    // lands while this thread waits for the next block
       }
     }
   }

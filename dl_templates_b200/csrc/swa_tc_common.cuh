@@ -139,12 +139,14 @@ __device__ __forceinline__ uint8_t* xtile_unit(uint8_t* tile, int row, int unit)
   return tile + (row >> 3) * 512 + unit * 128 + (row & 7) * 16;
 }
 
+// Units [2*part_lo, 2*part_hi + 2) of the row (a row may be shared by two threads).
 template <bool BF16>
-__device__ __forceinline__ void write_indicator_row(uint8_t* tile, int row, const KParams& p) {
+__device__ __forceinline__ void write_indicator_row(uint8_t* tile, int row, int part_lo, int part_hi, const KParams& p) {
   const int ti = row / p.pl.TW, tc = row - ti * p.pl.TW;
   const float a = p.mask_a;
 #pragma unroll
   for (int u = 0; u < 4; ++u) {
+    if ((u >> 1) < part_lo || (u >> 1) > part_hi) continue;
     uint32_t w[4];
 #pragma unroll
     for (int h = 0; h < 4; ++h) {
@@ -157,32 +159,59 @@ __device__ __forceinline__ void write_indicator_row(uint8_t* tile, int row, cons
   }
 }
 
-// Penalty row of the streamed token at grid position (yr, yx) against the resident tile at (r0, x0).
+// The penalty row of a streamed token is [row part (8 values) | column part (16 values) | 8 zeros]:
+// the row part depends only on the token's halo row, the column part only on its halo column.  Both
+// are tabulated once per CTA; per block a thread only copies 16-byte units.
+constexpr int kPenRows = 160;   // >= 8 + 2*wr + KR halo rows (wr <= 64)
+struct PenaltyTables {
+  uint4 row[kPenRows];          // [halo row - hr_first]
+  uint4 col[64][2];             // [halo column - hx0]
+};
+
 template <bool BF16>
-__device__ __forceinline__ void write_penalty_row(uint8_t* tile, int row, const KParams& p, int r0, int x0, int yr,
-                                                  int yx) {
-  const bool in = yr >= 0 && yr < p.t_h && yx >= 0 && yx < p.Wtok;
-  int row_lo = 1, row_hi = 0, col_lo = 1, col_hi = 0;  // empty ranges
-  if (in) {
-    const int yc = yx / p.b;
-    row_lo = yr - p.wr - r0;            // allowed tile rows, inclusive
-    row_hi = yr + p.wr - r0;
-    col_lo = (yc - p.wc) * p.b - x0;    // allowed tile columns, inclusive
-    col_hi = (yc + p.wc + 1) * p.b - x0 - 1;
-  }
+__device__ __forceinline__ uint4 penalty_unit(int lo, int hi, float nb) {  // 8 tile positions, allowed range [lo, hi]
+  uint32_t w[4];
+#pragma unroll
+  for (int h = 0; h < 4; ++h)
+    w[h] = pack2<BF16>((2 * h >= lo && 2 * h <= hi) ? 0.f : nb, (2 * h + 1 >= lo && 2 * h + 1 <= hi) ? 0.f : nb);
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// Called by the 128 threads that write the mask tiles, once per CTA.
+template <bool BF16>
+__device__ __forceinline__ void build_penalty_tables(PenaltyTables* tab, int t, const KParams& p, const TilePos& tp) {
   const float nb = -p.mask_b;
-#pragma unroll
-  for (int u = 0; u < 4; ++u) {
-    uint32_t w[4];
-#pragma unroll
-    for (int h = 0; h < 4; ++h) {
-      const int d0 = u * 8 + 2 * h, d1 = d0 + 1;
-      const bool ok0 = d0 < 8 ? (d0 >= row_lo && d0 <= row_hi) : (d0 - 8 >= col_lo && d0 - 8 <= col_hi);
-      const bool ok1 = d1 < 8 ? (d1 >= row_lo && d1 <= row_hi) : (d1 - 8 >= col_lo && d1 - 8 <= col_hi);
-      // columns 24..31 carry no indicator on the resident side, their value is irrelevant
-      w[h] = pack2<BF16>(ok0 ? 0.f : nb, ok1 ? 0.f : nb);
+  for (int hr = t; hr < kPenRows; hr += 128) {
+    const int yr = tp.hr_first + hr;
+    const bool in = yr <= tp.hr_last;                       // hr_first >= 0 and hr_last < t_h by construction
+    const int lo = in ? yr - p.wr - tp.r0 : 1, hi = in ? yr + p.wr - tp.r0 : 0;
+    tab->row[hr] = penalty_unit<BF16>(lo, hi, nb);
+  }
+  if (t < 64) {
+    const int yx = tp.hx0 + t;
+    const bool in = yx >= 0 && yx < p.Wtok;
+    int lo = 1, hi = 0;
+    if (in) {
+      const int yc = yx / p.b;
+      lo = (yc - p.wc) * p.b - tp.x0;                       // allowed tile columns, inclusive
+      hi = (yc + p.wc + 1) * p.b - tp.x0 - 1;
     }
-    *reinterpret_cast<uint4*>(xtile_unit(tile, row, u)) = make_uint4(w[0], w[1], w[2], w[3]);
+    tab->col[t][0] = penalty_unit<BF16>(lo, hi, nb);
+    tab->col[t][1] = penalty_unit<BF16>(lo - 8, hi - 8, nb);
+  }
+}
+
+// Penalty row of the streamed token at halo row index `hr` / halo column `jc` into row `row` of an x tile;
+// part 0 = units 0-1, part 1 = units 2-3 (a row may be shared by two threads).
+__device__ __forceinline__ void write_penalty_row(uint8_t* tile, int row, int part_lo, int part_hi,
+                                                  const PenaltyTables* tab, int hr, int jc) {
+  if (part_lo == 0) {
+    *reinterpret_cast<uint4*>(xtile_unit(tile, row, 0)) = tab->row[hr];
+    *reinterpret_cast<uint4*>(xtile_unit(tile, row, 1)) = tab->col[jc][0];
+  }
+  if (part_hi == 1) {
+    *reinterpret_cast<uint4*>(xtile_unit(tile, row, 2)) = tab->col[jc][1];
+    *reinterpret_cast<uint4*>(xtile_unit(tile, row, 3)) = make_uint4(0u, 0u, 0u, 0u);
   }
 }
 
@@ -192,92 +221,125 @@ __device__ __forceinline__ uint8_t* swz(uint8_t* tile, int row, int unit) {
 }
 
 // ---- fused RoPE-2D on a swizzled q/k tile in shared memory ---------------------------------
-// One thread rotates one row.  The cos/sin values of the row are fetched into registers ahead
-// of time (RopeCache) -- right after the thread has finished its previous row, i.e. while it
-// would otherwise wait for the next tile to arrive -- because the tables are served by L2 (with
-// ~200 KiB of shared memory per CTA there is hardly any L1 left) and a dependent chain of table
-// loads per row would make these warps the bottleneck of the whole pipeline.
-// n_rdim = 8*NI, so the partner of a 16-byte unit is another whole unit of the same row.
-struct RopeCache {
-  float4 cs[16];   // n_rdim 8/16: row half then column half; n_rdim 32: row half only
-  int irow, icol;  // decoded positions, negative = that half is not rotated
+// 128 threads rotate one tile of `rows` rows.  When 2*rows <= 128 two threads share a row (one
+// rotates the row-angle pairs, dims [0,R) with [R,2R), the other the column-angle pairs, dims
+// [2R,3R) with [3R,4R)); otherwise one thread does both halves of its row.  The cos/sin values
+// a thread needs are fetched into registers ahead of time (RopeRow) -- right after it has
+// finished its previous row, i.e. while it would otherwise wait for the next tile to arrive --
+// because the tables are served by L2 (with ~200 KiB of shared memory per CTA there is hardly
+// any L1 left) and a dependent chain of table loads per row would make these warps the
+// bottleneck of the whole pipeline.  n_rdim = 8*NI, so the partner of a 16-byte unit is another
+// whole unit of the same row.
+struct RopeRow {
+  float4 cs[16];   // (cos, sin) pairs: [first half handled][second half handled, if it fits]
+  int pos[2];      // table rows of the row-angle / column-angle half; negative = not rotated
 };
 
+// Which halves a thread handles: [lo, hi].
+struct RopeParts {
+  int row, lo, hi;
+  bool active;
+};
+
+__device__ __forceinline__ RopeParts rope_parts(int t, int rows) {
+  RopeParts r;
+  if (2 * rows <= 128) {
+    r.active = t < 2 * rows;
+    r.lo = r.hi = t >= rows ? 1 : 0;
+    r.row = t - r.lo * rows;
+  } else {
+    r.active = t < rows;
+    r.lo = 0;
+    r.hi = 1;
+    r.row = t;
+  }
+  return r;
+}
+
 template <int NI>
-__device__ __forceinline__ void rope_fetch_n(RopeCache& c, const RopeDev& rp) {
+__device__ __forceinline__ void rope_fetch_n(RopeRow& c, const RopeParts& pt, const RopeDev& rp) {
   constexpr int R = 8 * NI;
-  if (c.irow >= 0) {
-    const float4* t4 = reinterpret_cast<const float4*>(rp.row_cs + (int64_t)c.irow * R * 2);
+  const int first = pt.lo;
+  const int pos_first = first ? c.pos[1] : c.pos[0];
+  if (pos_first >= 0) {
+    const float4* t4 = reinterpret_cast<const float4*>((first ? rp.col_cs : rp.row_cs) + (int64_t)pos_first * R * 2);
 #pragma unroll
     for (int i = 0; i < NI * 4; ++i) c.cs[i] = __ldg(t4 + i);
   }
-  if (NI <= 2 && c.icol >= 0) {
-    const float4* t4 = reinterpret_cast<const float4*>(rp.col_cs + (int64_t)c.icol * R * 2);
+  if (NI <= 2 && pt.hi > pt.lo && c.pos[1] >= 0) {
+    const float4* t4 = reinterpret_cast<const float4*>(rp.col_cs + (int64_t)c.pos[1] * R * 2);
 #pragma unroll
     for (int i = 0; i < NI * 4; ++i) c.cs[(NI * 4 + i) & 15] = __ldg(t4 + i);
   }
 }
 
 // Start fetching the cos/sin rows of the token with packed index `packed` (-1: nothing to do).
-__device__ __forceinline__ void rope_fetch(RopeCache& c, int32_t packed, const RopeDev& rp) {
-  decode_idx(packed, rp.max_h, rp.max_w, c.irow, c.icol);
+__device__ __forceinline__ void rope_fetch(RopeRow& c, int32_t packed, const RopeParts& pt, const RopeDev& rp) {
+  decode_idx(packed, rp.max_h, rp.max_w, c.pos[0], c.pos[1]);
   switch (rp.R) {
-    case 8: rope_fetch_n<1>(c, rp); break;
-    case 16: rope_fetch_n<2>(c, rp); break;
-    case 32: rope_fetch_n<4>(c, rp); break;
-    default: c.irow = c.icol = -1; break;
+    case 8: rope_fetch_n<1>(c, pt, rp); break;
+    case 16: rope_fetch_n<2>(c, pt, rp); break;
+    case 32: rope_fetch_n<4>(c, pt, rp); break;
+    default: c.pos[0] = c.pos[1] = -1; break;
   }
 }
 
-// Rotate one half (0 = row pair, 1 = column pair) of the row with NI*4 float4 of (cos, sin).
+// Rotate one half (0 = row-angle pairs, 1 = column-angle pairs) of a row with NI*4 float4 of (cos, sin).
 template <bool BF16, int NI>
 __device__ __forceinline__ void rope_rotate_half(uint8_t* tile, uint32_t chunk_stride, int row, int half,
                                                  const float4* cs) {
   constexpr int R = 8 * NI;
+  uint32_t a0[NI], a1[NI];
+  uint4 va[NI], vb[NI];
 #pragma unroll
-  for (int it = 0; it < NI; ++it) {
-    const int d0 = 2 * half * R + it * 8, d1 = d0 + R;
-    const uint32_t a0 = ptx::smem_u32(swz(tile + (d0 >> 6) * chunk_stride, row, (d0 & 63) >> 3));
-    const uint32_t a1 = ptx::smem_u32(swz(tile + (d1 >> 6) * chunk_stride, row, (d1 & 63) >> 3));
-    uint4 va = ptx::lds128(a0), vb = ptx::lds128(a1);
-    uint32_t* pa = reinterpret_cast<uint32_t*>(&va);
-    uint32_t* pb = reinterpret_cast<uint32_t*>(&vb);
+  for (int i = 0; i < NI; ++i) {  // all loads first
+    const int d0 = 2 * half * R + i * 8, d1 = d0 + R;
+    a0[i] = ptx::smem_u32(swz(tile + (d0 >> 6) * chunk_stride, row, (d0 & 63) >> 3));
+    a1[i] = ptx::smem_u32(swz(tile + (d1 >> 6) * chunk_stride, row, (d1 & 63) >> 3));
+    va[i] = ptx::lds128(a0[i]);
+    vb[i] = ptx::lds128(a1[i]);
+  }
+#pragma unroll
+  for (int i = 0; i < NI; ++i) {
+    uint32_t* pa = reinterpret_cast<uint32_t*>(&va[i]);
+    uint32_t* pb = reinterpret_cast<uint32_t*>(&vb[i]);
 #pragma unroll
     for (int h = 0; h < 4; ++h) {
-      const float4 c = cs[it * 4 + h];  // (cos, sin) of pairs 2h and 2h+1
+      const float4 c = cs[i * 4 + h];  // (cos, sin) of pairs 2h and 2h+1
       const float2 x0 = unpack2<BF16>(pa[h]), x1 = unpack2<BF16>(pb[h]);
       pa[h] = pack2<BF16>(x0.x * c.x - x1.x * c.y, x0.y * c.z - x1.y * c.w);
       pb[h] = pack2<BF16>(x0.x * c.y + x1.x * c.x, x0.y * c.w + x1.y * c.z);
     }
-    ptx::sts128(a0, va.x, va.y, va.z, va.w);
-    ptx::sts128(a1, vb.x, vb.y, vb.z, vb.w);
+    ptx::sts128(a0[i], pa[0], pa[1], pa[2], pa[3]);
+    ptx::sts128(a1[i], pb[0], pb[1], pb[2], pb[3]);
   }
 }
 
 template <bool BF16, int NI>
-__device__ __forceinline__ void rope_apply_n(uint8_t* tile, uint32_t chunk_stride, int row, RopeCache& c,
+__device__ __forceinline__ void rope_apply_n(uint8_t* tile, uint32_t chunk_stride, RopeRow& c, const RopeParts& pt,
                                              const RopeDev& rp) {
-  if (c.irow >= 0) rope_rotate_half<BF16, NI>(tile, chunk_stride, row, 0, &c.cs[0]);
-  if (c.icol >= 0) {
+  const int first = pt.lo;
+  if ((first ? c.pos[1] : c.pos[0]) >= 0) rope_rotate_half<BF16, NI>(tile, chunk_stride, pt.row, first, &c.cs[0]);
+  if (pt.hi > pt.lo && c.pos[1] >= 0) {
     if constexpr (NI <= 2) {
-      rope_rotate_half<BF16, NI>(tile, chunk_stride, row, 1, &c.cs[NI * 4]);
-    } else {
-      const float4* t4 = reinterpret_cast<const float4*>(rp.col_cs + (int64_t)c.icol * (8 * NI) * 2);
+      rope_rotate_half<BF16, NI>(tile, chunk_stride, pt.row, 1, &c.cs[NI * 4]);
+    } else {  // n_rdim 32: the second half did not fit the register cache
+      const float4* t4 = reinterpret_cast<const float4*>(rp.col_cs + (int64_t)c.pos[1] * (8 * NI) * 2);
 #pragma unroll
       for (int i = 0; i < 16; ++i) c.cs[i] = __ldg(t4 + i);
-      rope_rotate_half<BF16, NI>(tile, chunk_stride, row, 1, &c.cs[0]);
+      rope_rotate_half<BF16, NI>(tile, chunk_stride, pt.row, 1, &c.cs[0]);
     }
   }
 }
 
-// Rotate row `row` of the tile with the values fetched by rope_fetch.
+// Rotate this thread's share of the tile with the values fetched by rope_fetch.
 template <bool BF16>
-__device__ __forceinline__ void rope_apply(uint8_t* tile, uint32_t chunk_stride, int row, RopeCache& c,
+__device__ __forceinline__ void rope_apply(uint8_t* tile, uint32_t chunk_stride, RopeRow& c, const RopeParts& pt,
                                            const RopeDev& rp) {
   switch (rp.R) {
-    case 8: rope_apply_n<BF16, 1>(tile, chunk_stride, row, c, rp); break;
-    case 16: rope_apply_n<BF16, 2>(tile, chunk_stride, row, c, rp); break;
-    case 32: rope_apply_n<BF16, 4>(tile, chunk_stride, row, c, rp); break;
+    case 8: rope_apply_n<BF16, 1>(tile, chunk_stride, c, pt, rp); break;
+    case 16: rope_apply_n<BF16, 2>(tile, chunk_stride, c, pt, rp); break;
+    case 32: rope_apply_n<BF16, 4>(tile, chunk_stride, c, pt, rp); break;
     default: break;
   }
 }

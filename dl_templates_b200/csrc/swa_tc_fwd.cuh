@@ -31,6 +31,7 @@ struct FwdBars {
   uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2];
   float xchg[2][2][128];  // [block parity][column half][row]: block maxima of the two threads of a row
   float lsum[2][128];     // [column half][row]: partial row sums, exchanged once at the end
+  PenaltyTables pen;      // window-mask penalty parts of this CTA's halo rows / columns
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -176,7 +177,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   } else if (warp < 10) {
     // ------------------------------------------------------------------ softmax, two threads per query row
     const int quarter = warp & 3;                 // TMEM lane quarter this warp may touch
-    const int half = (warp - 2) >> 2;             // which 8-column unit of every 16 columns is this thread's
+    const int half = (warp - 2) >> 2;             // lower / upper half of each block's columns is this thread's
     const int m = quarter * 32 + lane;
     const int qr = tp.r0 + m / pl.TW, qx = tp.x0 + m % pl.TW;
     const bool q_in = qr < p.t_h && qx < p.Wtok;
@@ -187,6 +188,23 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     const int sw = m & 7;
     const float c2 = p.scale_log2;
     const bool tr = (m == 0 && half == 0);
+    // This thread's nh = N/2 columns (a multiple of 8, <= 64) are held as up to eight 8-column units in
+    // fixed registers: units 0-3 one 32-column load (nh >= 32); units 4-7 a second one (nh == 64), or
+    // a 16-column load (units 4-5, nh & 16) and an 8-column load (unit 6, nh & 8).
+    const int nh = N >> 1, col0 = half * nh;
+    const int off16 = nh & ~31, off8 = nh & ~15;
+    int ucol[8];                                  // first column (within the thread's half) of each unit
+    uint32_t uvalid = 0;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      bool v;
+      if (u < 4) { v = nh >= 32; ucol[u] = u * 8; }
+      else if (nh == 64) { v = true; ucol[u] = u * 8; }
+      else if (u < 6) { v = (nh & 16) != 0; ucol[u] = off16 + (u - 4) * 8; }
+      else if (u == 6) { v = (nh & 8) != 0; ucol[u] = off8; }
+      else { v = false; ucol[u] = 0; }
+      uvalid |= (v ? 1u : 0u) << u;
+    }
     float m_used = -INFINITY, l = 0.f;
     // `ok` is kept warp-uniform, and a failed wait does not leave the loop: the two warps of a row
     // pair meet at a named barrier every block, so both must run the same number of iterations.
@@ -200,26 +218,29 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       if (tr && j == 2) trace_mark(p, 2, 21);
       wait_all(&bars->s_full[sb], (j >> 1) & 1);
       if (tr && j == 2) trace_mark(p, 2, 22);
-      uint32_t sr[64];                             // this thread's units: columns c*16 + half*8 .. +8
+      uint32_t sr[64];
       float mx = -INFINITY;
       if (ok) {
         tc_fence_after();
         if (tr) trace_mark(p, 2, 1 + 4 * j);
-#pragma unroll
-        for (int c = 0; c < 8; ++c)
-          if (c * 16 < N) tmem_ld8(lane_base + kTmemS + sb * 128 + c * 16 + half * 8, &sr[c * 8]);
-        if (tr && j == 2) trace_mark(p, 2, 23);
+        const uint32_t sbase = lane_base + kTmemS + sb * 128 + col0;
+        if (nh >= 32) tmem_ld32(sbase, &sr[0]);
+        if (nh == 64) {
+          tmem_ld32(sbase + 32, &sr[32]);
+        } else {
+          if (nh & 16) tmem_ld16(sbase + off16, &sr[32]);
+          if (nh & 8) tmem_ld8(sbase + off8, &sr[48]);
+        }
         tmem_wait_ld();
-        if (tr && j == 2) trace_mark(p, 2, 24);
         tc_fence_before();
         mbar_arrive(&bars->s_empty[sb]);
         if (tr) trace_mark(p, 2, 2 + 4 * j);
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int c = 0; c < 8; ++c)
-          if (c * 16 < N) {
+        for (int u = 0; u < 8; ++u)
+          if ((uvalid >> u) & 1u) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sr[c * 8 + i]));
+            for (int i = 0; i < 8; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sr[u * 8 + i]));
           }
         mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       }
@@ -248,18 +269,18 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         const uint32_t prow = p_base + pb * pch * 16384;
         float ls4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int c = 0; c < 8; ++c)
-          if (c * 16 < N) {
+        for (int u = 0; u < 8; ++u)
+          if ((uvalid >> u) & 1u) {
             uint32_t w[4];
 #pragma unroll
             for (int h = 0; h < 4; ++h) {
-              const float p0 = exp2f(fmaf(__uint_as_float(sr[c * 8 + 2 * h]), c2, -mc));
-              const float p1 = exp2f(fmaf(__uint_as_float(sr[c * 8 + 2 * h + 1]), c2, -mc));
+              const float p0 = exp2f(fmaf(__uint_as_float(sr[u * 8 + 2 * h]), c2, -mc));
+              const float p1 = exp2f(fmaf(__uint_as_float(sr[u * 8 + 2 * h + 1]), c2, -mc));
               ls4[h] += p0 + p1;
               w[h] = pack2<BF16>(p0, p1);
             }
-            const int u = 2 * c + half;              // 16-byte unit of the P row (8 keys)
-            sts128(prow + (u >> 3) * 16384 + (((u & 7) ^ sw) << 4), w[0], w[1], w[2], w[3]);
+            const int pu = (col0 + ucol[u]) >> 3;     // 16-byte unit of the P row (8 keys)
+            sts128(prow + (pu >> 3) * 16384 + (((pu & 7) ^ sw) << 4), w[0], w[1], w[2], w[3]);
           }
         l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
         if (tr && j == 2) trace_mark(p, 2, 27);
@@ -326,27 +347,30 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     // ------------------------------------------------------------------ fused RoPE-2D on Q and K tiles, mask tiles
     const int t = threadIdx.x - kFwdRopeThread0;
     const bool rope_on = p.rope.idx != nullptr;
+    const RopeParts qp = rope_parts(t, 128), kp = rope_parts(t, N);   // this thread's share of the Q tile / of a K block
     // packed index of this thread's row of the query tile and of its row of block 0, fetched before any wait
-    const int qr = tp.r0 + t / pl.TW, qx = tp.x0 + t % pl.TW;
+    const int qr = tp.r0 + qp.row / pl.TW, qx = tp.x0 + qp.row % pl.TW;
     const bool q_in = qr < p.t_h && qx < p.Wtok;
-    const int kjr = t / pl.KW, kx = tp.hx0 + t % pl.KW;           // this thread's row inside every streamed block
-    const bool kx_in = t < N && kx >= 0 && kx < p.Wtok;
+    const int kjr = kp.row / pl.KW, kx = tp.hx0 + kp.row % pl.KW;     // this thread's row inside every streamed block
+    const bool kx_in = kp.active && kx >= 0 && kx < p.Wtok;
     int32_t k_idx = -1;
-    RopeCache rc;
-    rc.irow = rc.icol = -1;
+    RopeRow rc;
+    rc.pos[0] = rc.pos[1] = -1;
     if (rope_on) {
-      if (q_in) rope_fetch(rc, __ldg(p.rope.idx + qr * p.Wtok + qx), p.rope);
+      if (q_in) rope_fetch(rc, __ldg(p.rope.idx + qr * p.Wtok + qx), qp, p.rope);
       const int kr0 = tp.hr_first + kjr;
       if (kx_in && kr0 < p.t_h) k_idx = __ldg(p.rope.idx + kr0 * p.Wtok + kx);
     }
-    write_indicator_row<BF16>(qx_smem, t, p);
+    write_indicator_row<BF16>(qx_smem, qp.row, qp.lo, qp.hi, p);
+    build_penalty_tables<BF16>(&bars->pen, t, p, tp);
+    named_bar_sync(5, 128);                          // the tables are complete before any of these warps reads them
     if (mbar_wait<100>(&bars->q_full, 0, abort_flag)) {
       if (t == 0) trace_mark(p, 3, 1);
-      if (rope_on && q_in) rope_apply<BF16>(q_smem, 16384, t, rc, p.rope);
+      if (rope_on && q_in) rope_apply<BF16>(q_smem, 16384, rc, qp, p.rope);
       fence_proxy_async_smem();
       mbar_arrive(&bars->q_ready);
       if (t == 0) trace_mark(p, 3, 2);
-      rope_fetch(rc, k_idx, p.rope);               // cos/sin of this thread's row of block 0
+      rope_fetch(rc, k_idx, kp, p.rope);           // cos/sin of this thread's row of block 0
       for (int j = 0; j < tp.nblk; ++j) {
         const int s = j % pl.stages;
         const int kr = tp.hr_first + j * pl.KR + kjr;
@@ -357,12 +381,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         // only after every MMA of the stage's previous block has completed
         if (!mbar_wait<100>(&bars->kv_full[s], (j / pl.stages) & 1, abort_flag)) break;
         if (t == 0) trace_mark(p, 3, 3 + 2 * j);
-        if (t < N) write_penalty_row<BF16>(kx_smem + s * kx_stage, t, p, tp.r0, tp.x0, kr, kx);
-        if (rope_on && kx_in && kr < p.t_h) rope_apply<BF16>(k_smem + s * k_stage, blk_bytes, t, rc, p.rope);
+        if (kp.active) write_penalty_row(kx_smem + s * kx_stage, kp.row, kp.lo, kp.hi, &bars->pen, j * pl.KR + kjr, kp.row % pl.KW);
+        if (rope_on && kx_in && kr < p.t_h) rope_apply<BF16>(k_smem + s * k_stage, blk_bytes, rc, kp, p.rope);
         fence_proxy_async_smem();
         mbar_arrive(&bars->k_ready[s]);
         if (t == 0) trace_mark(p, 3, 4 + 2 * j);
-        rope_fetch(rc, k_idx_next, p.rope);        // lands while this thread waits for the next block
+        rope_fetch(rc, k_idx_next, kp, p.rope);    // lands while this thread waits for the next block
       }
     }
   }
