@@ -151,7 +151,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ C
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->x_full, 1);
-    mbar_init(&bars->x_ready, 128);
+    mbar_init(&bars->x_ready, 256);
     mbar_init(&bars->acc_done, 1);
     for (int s = 0; s < kMaxStages; ++s) {
       mbar_init(&bars->y_full[s], 1);
@@ -296,6 +296,23 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ C
     }
     const uint32_t op_base = smem_u32(op_smem) + m * 128;
     const uint32_t vec_addr = smem_u32(vec_smem);
+    // Prologue: these warps have nothing to do until the first S / dP tiles exist, so they rotate the
+    // resident q/k tile (thread (m, half) takes the row-angle or the column-angle pairs of row m) while
+    // the RoPE warps already work on the first streamed blocks.
+    {
+      const bool rope_on = p.rope.idx != nullptr;
+      RopeParts xp;
+      xp.row = m; xp.lo = xp.hi = half; xp.active = true;
+      RopeRow rc;
+      rc.pos[0] = rc.pos[1] = -1;
+      if (rope_on && t_in) rope_fetch(rc, __ldg(p.rope.idx + tok), xp, p.rope);
+      wait_spin(&bars->x_full, 0);
+      if (ok) {
+        if (rope_on && t_in) rope_apply<BF16>(xqk_smem, 16384, rc, xp, p.rope);
+        fence_proxy_async_smem();
+        mbar_arrive(&bars->x_ready);
+      }
+    }
     for (int j = 0; j < tp.nblk && ok; ++j) {
       const int sb = j % nsb, pb = j % pl.pbufs, s = j % pl.stages;
       wait_spin(&bars->sd_full[sb], (j / nsb) & 1);
@@ -384,28 +401,21 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ C
     // ------------------------------------------------------------------ RoPE on the q/k tiles, mask tiles, lse/delta staging
     const int t = threadIdx.x - kBwdRopeThread0;
     const bool rope_on = p.rope.idx != nullptr;
-    const RopeParts xp = rope_parts(t, 128), yp = rope_parts(t, N);   // share of the resident tile / of a streamed block
-    const int xr = tp.r0 + xp.row / pl.TW, xx_ = tp.x0 + xp.row % pl.TW;
-    const bool x_in = xr < p.t_h && xx_ < p.Wtok;
+    const RopeParts ip = rope_parts(t, 128), yp = rope_parts(t, N);   // share of the indicator tile / of a streamed block
     const int yjr = yp.row / pl.KW, yx_ = tp.hx0 + yp.row % pl.KW;    // this thread's row inside every streamed block
     const bool yx_in = yp.active && yx_ >= 0 && yx_ < p.Wtok;
     int32_t y_idx = -1;
     RopeRow rc;
     rc.pos[0] = rc.pos[1] = -1;
     if (rope_on) {
-      if (x_in) rope_fetch(rc, __ldg(p.rope.idx + xr * p.Wtok + xx_), xp, p.rope);
       const int yr0 = tp.hr_first + yjr;
       if (yx_in && yr0 < p.t_h) y_idx = __ldg(p.rope.idx + yr0 * p.Wtok + yx_);
     }
-    write_indicator_row<BF16>(xx_smem, xp.row, xp.lo, xp.hi, p);
+    write_indicator_row<BF16>(xx_smem, ip.row, ip.lo, ip.hi, p);
     build_penalty_tables<BF16>(&bars->pen, t, p, tp);
     named_bar_sync(5, 128);                          // the tables are complete before any of these warps reads them
-    wait_park(&bars->x_full, 0);
-    if (ok) {
-      if (rope_on && x_in) rope_apply<BF16>(xqk_smem, 16384, rc, xp, p.rope);
-      fence_proxy_async_smem();
-      mbar_arrive(&bars->x_ready);
-      rope_fetch(rc, y_idx, yp, p.rope);           // cos/sin of this thread's row of block 0
+    {
+      rope_fetch(rc, y_idx, yp, p.rope);             // cos/sin of this thread's row of block 0
       for (int j = 0; j < tp.nblk; ++j) {
         const int s = j % pl.stages;
         const int yr = tp.hr_first + j * pl.KR + yjr;

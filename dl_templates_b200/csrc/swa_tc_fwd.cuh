@@ -13,8 +13,9 @@
 //                the pair exchanges its block maximum through shared memory.  tcgen05.ld
 //                of the S units, running max / sum, P written to shared memory as the A
 //                operand of the PV MMA, lazy rescale of O, final normalisation
-//   warps 10-13  fused RoPE-2D: rotate the Q tile and every K block in shared memory
-//                between TMA arrival and MMA issue, and write the window-mask tiles
+//   warps 10-13  fused RoPE-2D: rotate every K block in shared memory between TMA arrival
+//                and MMA issue, and write the window-mask tiles (the Q tile is rotated by
+//                the softmax warps, which are idle until the first S tile exists)
 // S for block j+1 is computed by the tensor core while the softmax warps work on
 // block j.  All waits are bounded; a timed-out wait raises a CTA-wide abort flag,
 // every role leaves its loop, TMEM is freed and the status word records the event.
@@ -71,7 +72,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
-    mbar_init(&bars->q_ready, 128);
+    mbar_init(&bars->q_ready, 256);
     mbar_init(&bars->o_done, 1);
     for (int s = 0; s < kMaxStages; ++s) {
       mbar_init(&bars->kv_full[s], 1);
@@ -213,6 +214,23 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       const bool r = ok && mbar_wait(bar, parity, abort_flag);
       ok = __all_sync(0xffffffffu, r);
     };
+    // Prologue: these warps have nothing to do until the first S tile exists, so they rotate the query
+    // tile (thread (m, half) takes the row-angle or the column-angle pairs of row m) while the other
+    // RoPE warps already work on the first K blocks.
+    {
+      const bool rope_on = p.rope.idx != nullptr;
+      RopeParts qp;
+      qp.row = m; qp.lo = qp.hi = half; qp.active = true;
+      RopeRow rc;
+      rc.pos[0] = rc.pos[1] = -1;
+      if (rope_on && q_in) rope_fetch(rc, __ldg(p.rope.idx + qr * p.Wtok + qx), qp, p.rope);
+      wait_all(&bars->q_full, 0);
+      if (ok) {
+        if (rope_on && q_in) rope_apply<BF16>(q_smem, 16384, rc, qp, p.rope);
+        fence_proxy_async_smem();
+        mbar_arrive(&bars->q_ready);
+      }
+    }
     for (int j = 0; j < tp.nblk; ++j) {
       const int sb = j & 1, pb = j % pl.pbufs;
       if (tr && j == 2) trace_mark(p, 2, 21);
@@ -347,47 +365,36 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     // ------------------------------------------------------------------ fused RoPE-2D on Q and K tiles, mask tiles
     const int t = threadIdx.x - kFwdRopeThread0;
     const bool rope_on = p.rope.idx != nullptr;
-    const RopeParts qp = rope_parts(t, 128), kp = rope_parts(t, N);   // this thread's share of the Q tile / of a K block
-    // packed index of this thread's row of the query tile and of its row of block 0, fetched before any wait
-    const int qr = tp.r0 + qp.row / pl.TW, qx = tp.x0 + qp.row % pl.TW;
-    const bool q_in = qr < p.t_h && qx < p.Wtok;
+    const RopeParts ip = rope_parts(t, 128), kp = rope_parts(t, N);   // share of the indicator tile / of a K block
     const int kjr = kp.row / pl.KW, kx = tp.hx0 + kp.row % pl.KW;     // this thread's row inside every streamed block
     const bool kx_in = kp.active && kx >= 0 && kx < p.Wtok;
-    int32_t k_idx = -1;
     RopeRow rc;
     rc.pos[0] = rc.pos[1] = -1;
+    int32_t k_idx = -1;
     if (rope_on) {
-      if (q_in) rope_fetch(rc, __ldg(p.rope.idx + qr * p.Wtok + qx), qp, p.rope);
       const int kr0 = tp.hr_first + kjr;
       if (kx_in && kr0 < p.t_h) k_idx = __ldg(p.rope.idx + kr0 * p.Wtok + kx);
     }
-    write_indicator_row<BF16>(qx_smem, qp.row, qp.lo, qp.hi, p);
+    write_indicator_row<BF16>(qx_smem, ip.row, ip.lo, ip.hi, p);
     build_penalty_tables<BF16>(&bars->pen, t, p, tp);
     named_bar_sync(5, 128);                          // the tables are complete before any of these warps reads them
-    if (mbar_wait<100>(&bars->q_full, 0, abort_flag)) {
-      if (t == 0) trace_mark(p, 3, 1);
-      if (rope_on && q_in) rope_apply<BF16>(q_smem, 16384, rc, qp, p.rope);
+    rope_fetch(rc, k_idx, kp, p.rope);               // cos/sin of this thread's row of block 0
+    for (int j = 0; j < tp.nblk; ++j) {
+      const int s = j % pl.stages;
+      const int kr = tp.hr_first + j * pl.KR + kjr;
+      // index of the same row of the next block: in flight while this block is rotated
+      int32_t k_idx_next = -1;
+      if (rope_on && kx_in && j + 1 < tp.nblk && kr + pl.KR < p.t_h) k_idx_next = __ldg(p.rope.idx + (kr + pl.KR) * p.Wtok + kx);
+      // the stage (K, V and penalty rows) is free once its refill has landed: the producer refills
+      // only after every MMA of the stage's previous block has completed
+      if (!mbar_wait<100>(&bars->kv_full[s], (j / pl.stages) & 1, abort_flag)) break;
+      if (t == 0) trace_mark(p, 3, 3 + 2 * j);
+      if (kp.active) write_penalty_row(kx_smem + s * kx_stage, kp.row, kp.lo, kp.hi, &bars->pen, j * pl.KR + kjr, kp.row % pl.KW);
+      if (rope_on && kx_in && kr < p.t_h) rope_apply<BF16>(k_smem + s * k_stage, blk_bytes, rc, kp, p.rope);
       fence_proxy_async_smem();
-      mbar_arrive(&bars->q_ready);
-      if (t == 0) trace_mark(p, 3, 2);
-      rope_fetch(rc, k_idx, kp, p.rope);           // cos/sin of this thread's row of block 0
-      for (int j = 0; j < tp.nblk; ++j) {
-        const int s = j % pl.stages;
-        const int kr = tp.hr_first + j * pl.KR + kjr;
-        // index of the same row of the next block: in flight while this block is rotated
-        int32_t k_idx_next = -1;
-        if (rope_on && kx_in && j + 1 < tp.nblk && kr + pl.KR < p.t_h) k_idx_next = __ldg(p.rope.idx + (kr + pl.KR) * p.Wtok + kx);
-        // the stage (K, V and penalty rows) is free once its refill has landed: the producer refills
-        // only after every MMA of the stage's previous block has completed
-        if (!mbar_wait<100>(&bars->kv_full[s], (j / pl.stages) & 1, abort_flag)) break;
-        if (t == 0) trace_mark(p, 3, 3 + 2 * j);
-        if (kp.active) write_penalty_row(kx_smem + s * kx_stage, kp.row, kp.lo, kp.hi, &bars->pen, j * pl.KR + kjr, kp.row % pl.KW);
-        if (rope_on && kx_in && kr < p.t_h) rope_apply<BF16>(k_smem + s * k_stage, blk_bytes, rc, kp, p.rope);
-        fence_proxy_async_smem();
-        mbar_arrive(&bars->k_ready[s]);
-        if (t == 0) trace_mark(p, 3, 4 + 2 * j);
-        rope_fetch(rc, k_idx_next, kp, p.rope);    // lands while this thread waits for the next block
-      }
+      mbar_arrive(&bars->k_ready[s]);
+      if (t == 0) trace_mark(p, 3, 4 + 2 * j);
+      rope_fetch(rc, k_idx_next, kp, p.rope);        // lands while this thread waits for the next block
     }
   }
 
