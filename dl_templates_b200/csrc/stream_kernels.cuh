@@ -35,6 +35,26 @@ __global__ void __launch_bounds__(256) delta_vec_kernel(View4 o, View4 d_o, floa
   if (row < total_rows && part == 0) delta[row] = acc;
 }
 
+// Same for fully contiguous o and do ([rows, d_v] row-major): no per-thread index decomposition.
+template <typename T>
+__global__ void __launch_bounds__(256) delta_flat_kernel(const T* __restrict__ o, const T* __restrict__ d_o,
+                                                         float* __restrict__ delta, int dv, int64_t total_rows) {
+  const int tpr = dv >> 3;  // threads per row
+  const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t row = gid / tpr;
+  float acc = 0.f;
+  if (row < total_rows) {
+    const uint4 a = __ldg(reinterpret_cast<const uint4*>(o) + gid);
+    const uint4 b = __ldg(reinterpret_cast<const uint4*>(d_o) + gid);
+    const T* pa = reinterpret_cast<const T*>(&a);
+    const T* pb = reinterpret_cast<const T*>(&b);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc += to_f(pa[i]) * to_f(pb[i]);
+  }
+  for (int off = tpr >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (row < total_rows && (gid - row * tpr) == 0) delta[row] = acc;
+}
+
 // Element path: one warp per token, any dtype / stride / head dim.
 template <typename T>
 __global__ void __launch_bounds__(256) delta_generic_kernel(View4 o, View4 d_o, float* __restrict__ delta, int H,

@@ -143,6 +143,17 @@ int swa_bwd_delta(const swa_geom_t* g, const swa_tensor_t* o, const swa_tensor_t
   if (esz == 2 && pow2 && dv >= 8 && dv <= 256 && vec_ok(o) && vec_ok(d_o)) {
     const int64_t threads = rows * (dv / 8);
     const unsigned blocks = (unsigned)((threads + 255) / 256);
+    auto flat = [&](const swa_tensor_t* t) {
+      return t->stride[2] == dv && t->stride[1] == N * dv && (g->B == 1 || t->stride[0] == (int64_t)g->H * N * dv);
+    };
+    if (flat(o) && flat(d_o)) {
+      if (g->dtype == SWA_F16)
+        swa::delta_flat_kernel<__half><<<blocks, 256, 0, st>>>((const __half*)o->ptr, (const __half*)d_o->ptr, delta, dv, rows);
+      else
+        swa::delta_flat_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)o->ptr,
+                                                                      (const __nv_bfloat16*)d_o->ptr, delta, dv, rows);
+      return launch_ok("delta");
+    }
     if (g->dtype == SWA_F16)
       swa::delta_vec_kernel<__half><<<blocks, 256, 0, st>>>(swa::make_view(o), swa::make_view(d_o), delta, g->H, N,
                                                             dv, rows);

@@ -178,3 +178,60 @@ def test_batch_head_slices_are_independent():
     part, _ = run_gpu(c["q"][:, 2:4], c["k"][:, 2:4], c["v"][:, 2:4], c["do"][:, 2:4], rope, c["win"], c["sm_scale"])
     for x, y in zip(full, part):
         assert torch.equal(x[:, 2:4], y)
+
+
+@pytest.mark.parametrize("b_size,G,wr,wc", [(2, 10, 2, 1), (4, 9, 1, 1), (16, 6, 1, 1)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_tiles_of_several_tokens_on_the_tensor_core_path(b_size, G, wr, wc, dtype):
+    """b_size > 1 (the reference's own regime is 16): every token of a tile attends every token of
+    the tiles in the window; RoPE indices are per token (tokens of a tile share its coordinates)."""
+    torch.manual_seed(b_size)
+    B, H, d = 1, 2, 64
+    N = G * G * b_size
+    q, k, v, do = (torch.randn(B, H, N, d).to(dtype) for _ in range(4))
+    rows = torch.arange(G)[:, None, None].expand(G, G, b_size)
+    cols = torch.arange(G)[None, :, None].expand(G, G, b_size)
+    idx = ((rows << 16) | cols).reshape(-1).to(torch.int32)
+    idx[5] = -1
+    tab = orc.make_cs_table(8, G)
+    rope = (idx, tab, tab.clone())
+    win = (b_size, G, G, wr, wc)
+    qd, vd = q.to(DEV), v.to(DEV)
+    assert swa.selected_impl(qd, vd, tuple(t.to(DEV) for t in rope), *win, 0.125) == "tc"
+    got, _ = run_gpu(q, k, v, do, rope, win, 0.125)
+    want = orc.fused_ref(q.float(), k.float(), v.float(), do.float(), *rope, *win, 0.125)
+    assert_close(got, want, dtype, what=f"b_size={b_size}")
+
+
+def test_config5_geometry_on_a_smaller_grid():
+    """d_qk = d_v = 128, 31x31 window, RoPE on all 128 dims (n_rdim 32) as in the largest configuration,
+    on a 96x96 grid the windowed oracle finishes in seconds."""
+    cfg = dict(CONFIGS["cfg5"])
+    cfg["grid"] = 96
+    c = make_case(cfg, B=1, H=1)
+    rope = (c["idx"], c["row_cs"], c["col_cs"])
+    got, _ = run_gpu(c["q"], c["k"], c["v"], c["do"], rope, c["win"], c["sm_scale"])
+    want = orc.fused_ref(*(c[x].float() for x in ("q", "k", "v", "do")), *rope, *c["win"], c["sm_scale"], windowed=True)
+    assert_close(got, want, cfg["dtype"], what="cfg5 geometry")
+
+
+def test_config5_full_grid_properties():
+    """Full 256x256 grid of the largest configuration on two (batch, head) slices: with v = 1 the
+    output is 1 (rows of P sum to 1 for all 65 536 queries, borders included), gradients are finite,
+    dV sums to the sum of dO over the grid (columns of P^T dO), and two runs agree bitwise."""
+    cfg = CONFIGS["cfg5"]
+    c = make_case(cfg, B=1, H=2)
+    rope = tuple(t.to(DEV) for t in (c["idx"], c["row_cs"], c["col_cs"]))
+    q, k, do = (c[x].to(DEV) for x in ("q", "k", "do"))
+    ones = torch.ones_like(c["v"]).to(DEV)
+    o, lse = swa.swa_forward(q, k, ones, rope, *c["win"], c["sm_scale"])
+    assert (o.float() - 1).abs().max().item() < 1e-2
+    dq, dk, dv = swa.swa_backward(q, k, ones, o, lse, do, rope, *c["win"], c["sm_scale"])
+    dq2, dk2, dv2 = swa.swa_backward(q, k, ones, o, lse, do, rope, *c["win"], c["sm_scale"])
+    swa.check_status()
+    for a, b in ((dq, dq2), (dk, dk2), (dv, dv2)):
+        assert torch.isfinite(a.float()).all() and torch.equal(a, b)
+    # sum_k dV[k, :] = sum_q (sum_k P[q, k]) dO[q, :] = sum_q dO[q, :]
+    lhs, rhs = dv.double().sum(2), do.double().sum(2)
+    rel = ((lhs - rhs).norm() / rhs.norm()).item()
+    assert rel < 1e-2, rel
