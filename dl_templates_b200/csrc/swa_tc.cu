@@ -61,6 +61,19 @@ bool make_map(CUtensorMap* m, const swa_tensor_t* t, const swa_geom_t* g, int d,
   return true;
 }
 
+// SMs of the current device (cached per device ordinal).
+int sm_count() {
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 int env_int(const char* name, int dflt) {
   const char* v = getenv(name);
   return v ? atoi(v) : dflt;
@@ -94,7 +107,8 @@ bool make_plan(const swa_geom_t* g, int which, Plan* out) {
   //   fwd : stage = K + V            fixed = Q              p-operands = 1 (P)
   //   dq  : stage = K + V            fixed = Q + dO         p-operands = 1 (dS)
   //   dkdv: stage = Q + dO (+lse,delta)  fixed = K + V      p-operands = 2 (P^T, dS^T)
-  const uint32_t fixed = (which == 0 ? qch : qch + vch) * 16384u + 128u * kXRowBytes;
+  // forward: the query tile is double-buffered (persistent kernel)
+  const uint32_t fixed = (which == 0 ? 2 * qch : qch + vch) * 16384u + 128u * kXRowBytes;
   const uint32_t row_bytes = (qch + vch) * 128u + kXRowBytes;
   const int p_ops = which == 2 ? 2 : 1;
   // blocks of up to 128 streamed tokens (the backward kernels double-buffer S and dP in TMEM up to 64)
@@ -167,9 +181,11 @@ KParams make_params(const swa_geom_t* g, const swa_rope_t* rope, const Plan& pl,
   mask_constants(g->sm_scale, &p.mask_a, &p.mask_b);
   p.pl = pl;
   p.rope = make_rope(rope);
+  p.n_items = pl.n_tiles_x * pl.n_tiles_y * g->B * g->H;
   p.status = status;
   // the Python layer hands a 4 KiB status buffer: words 0-3 status, bytes 16.. = 4 roles x 32 clock samples
   p.trace = (status != nullptr && getenv("SWA_TC_TRACE")) ? reinterpret_cast<long long*>(status + 4) : nullptr;
+  p.trace_it = env_int("SWA_TC_TRACE_IT", 1);
   return p;
 }
 
@@ -212,7 +228,10 @@ int launch_fwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* 
       !make_map(&tv, v, g, g->d_v, pl.KW, pl.KR))
     return -1;
   const KParams p = make_params(g, rope, pl, status);
-  dim3 grid(pl.n_tiles_x * pl.n_tiles_y, g->B * g->H), block(kFwdThreads);
+  // persistent: one CTA per SM, each walks the items blockIdx.x, blockIdx.x + gridDim.x, ...
+  const int n_items = pl.n_tiles_x * pl.n_tiles_y * g->B * g->H;
+  const int sms = sm_count();
+  dim3 grid(n_items < sms ? n_items : sms), block(kFwdThreads);
   auto kern = g->dtype == SWA_BF16 ? fwd_kernel<true> : fwd_kernel<false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem_bytes);
   if (e != cudaSuccess) {
@@ -220,8 +239,8 @@ int launch_fwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* 
     return -1;
   }
   if (getenv("SWA_TC_VERBOSE"))
-    fprintf(stderr, "[swa2d] fwd plan: tile %dx%d, block %dx%d (N=%d), stages %d, pbufs %d, smem %u, grid %ux%u\n", pl.TH,
-            pl.TW, pl.KR, pl.KW, pl.N, pl.stages, pl.pbufs, pl.smem_bytes, grid.x, grid.y);
+    fprintf(stderr, "[swa2d] fwd plan: tile %dx%d, block %dx%d (N=%d), stages %d, pbufs %d, smem %u, %d items on %u CTAs\n",
+            pl.TH, pl.TW, pl.KR, pl.KW, pl.N, pl.stages, pl.pbufs, pl.smem_bytes, n_items, grid.x);
   kern<<<grid, block, pl.smem_bytes, st>>>(tq, tk, tv, p, make_view(o), lse);
   return 0;
 }

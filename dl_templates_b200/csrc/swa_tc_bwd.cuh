@@ -49,24 +49,56 @@ constexpr int kBwdRopeThread0 = 320;
 constexpr uint32_t kBwdTmemCols = 512;
 constexpr uint32_t kTmS = 0, kTmDP = 128, kTmAccQK = 256, kTmAccV = 384;
 
-// Rotate back (transposed rotation) W consecutive dims, starting at dim BASE, of a dQ/dK row held
-// in registers.  For the supported n_rdim (8, 16, 32) and piece widths both elements of a pair
-// fall into the same piece.
+// cos/sin pairs needed to rotate back W consecutive dims (starting at dim BASE) of a dQ/dK row: pair e of
+// the piece is dims (BASE+e, BASE+e+R).  Fetched before the final wait so that the table latency (L2)
+// is hidden.  For the supported n_rdim (8, 16, 32) and piece widths both elements of a pair fall into
+// the same piece.
+template <int W>
+struct EpiRope {
+  float2 cs[W / 2];
+};
+
 template <int R, int BASE, int W>
-__device__ __forceinline__ void inv_rotate_piece(float (&v)[W], int irow, int icol, const RopeDev& rp) {
+__device__ __forceinline__ void epi_fetch_n(EpiRope<W>& c, int irow, int icol, const RopeDev& rp) {
+  int n = 0;
 #pragma unroll
   for (int e = 0; e < W; ++e) {
     const int d = BASE + e;
     if (d < 4 * R && ((d / R) & 1) == 0 && e + R < W) {
       const int seg = d / R;
       const int pos = seg >= 2 ? icol : irow;
-      if (pos >= 0) {
-        const float2 cs =
-            __ldg(reinterpret_cast<const float2*>((seg >= 2 ? rp.col_cs : rp.row_cs) + ((int64_t)pos * R + (d - seg * R)) * 2));
-        const float x0 = v[e], x1 = v[(e + R) % W];
-        v[e] = x0 * cs.x + x1 * cs.y;
-        v[(e + R) % W] = x1 * cs.x - x0 * cs.y;
-      }
+      c.cs[n] = pos >= 0 ? __ldg(reinterpret_cast<const float2*>((seg >= 2 ? rp.col_cs : rp.row_cs) +
+                                                                 ((int64_t)pos * R + (d - seg * R)) * 2))
+                         : make_float2(1.f, 0.f);
+      ++n;
+    }
+  }
+}
+
+template <int BASE, int W>
+__device__ __forceinline__ void epi_fetch(EpiRope<W>& c, bool rot, int irow, int icol, const RopeDev& rp) {
+  if (!rot) return;
+  switch (rp.R) {
+    case 8: epi_fetch_n<8, BASE, W>(c, irow, icol, rp); break;
+    case 16: epi_fetch_n<16, BASE, W>(c, irow, icol, rp); break;
+    case 32: epi_fetch_n<32, BASE, W>(c, irow, icol, rp); break;
+    default: break;
+  }
+}
+
+// Rotate back (transposed rotation) the piece held in registers with the prefetched pairs.
+template <int R, int BASE, int W>
+__device__ __forceinline__ void inv_rotate_piece(float (&v)[W], const EpiRope<W>& c) {
+  int n = 0;
+#pragma unroll
+  for (int e = 0; e < W; ++e) {
+    const int d = BASE + e;
+    if (d < 4 * R && ((d / R) & 1) == 0 && e + R < W) {
+      const float2 cs = c.cs[n];
+      ++n;
+      const float x0 = v[e], x1 = v[(e + R) % W];
+      v[e] = x0 * cs.x + x1 * cs.y;
+      v[(e + R) % W] = x1 * cs.x - x0 * cs.y;
     }
   }
 }
@@ -74,21 +106,21 @@ __device__ __forceinline__ void inv_rotate_piece(float (&v)[W], int irow, int ic
 // Load W accumulator columns (starting at column BASE) of this thread's TMEM lane, scale,
 // optionally rotate back, store W 16-bit elements at dst_row + BASE.
 template <bool BF16, int BASE, int W>
-__device__ __forceinline__ void store_acc_piece(uint32_t taddr, float scale, bool rot, int irow, int icol,
-                                                const RopeDev& rp, void* dst_row, bool in_grid) {
+__device__ __forceinline__ void store_acc_piece(uint32_t taddr, float scale, bool rot, const EpiRope<W>& c, int R,
+                                                void* dst_row, bool in_grid) {
   using namespace ptx;
   uint32_t raw[W];
 #pragma unroll
-  for (int c = 0; c < W / 16; ++c) tmem_ld16(taddr + BASE + c * 16, &raw[c * 16]);
+  for (int k = 0; k < W / 16; ++k) tmem_ld16(taddr + BASE + k * 16, &raw[k * 16]);
   tmem_wait_ld();
   float v[W];
 #pragma unroll
   for (int e = 0; e < W; ++e) v[e] = __uint_as_float(raw[e]) * scale;
   if (rot) {
-    switch (rp.R) {
-      case 8: inv_rotate_piece<8, BASE, W>(v, irow, icol, rp); break;
-      case 16: inv_rotate_piece<16, BASE, W>(v, irow, icol, rp); break;
-      case 32: inv_rotate_piece<32, BASE, W>(v, irow, icol, rp); break;
+    switch (R) {
+      case 8: inv_rotate_piece<8, BASE, W>(v, c); break;
+      case 16: inv_rotate_piece<16, BASE, W>(v, c); break;
+      case 32: inv_rotate_piece<32, BASE, W>(v, c); break;
       default: break;
     }
   }
@@ -98,20 +130,6 @@ __device__ __forceinline__ void store_acc_piece(uint32_t taddr, float scale, boo
     for (int u = 0; u < W / 8; ++u)
       dst[u] = make_uint4(pack2<BF16>(v[u * 8], v[u * 8 + 1]), pack2<BF16>(v[u * 8 + 2], v[u * 8 + 3]),
                           pack2<BF16>(v[u * 8 + 4], v[u * 8 + 5]), pack2<BF16>(v[u * 8 + 6], v[u * 8 + 7]));
-  }
-}
-
-// One accumulator row of `chunks` x 64 columns, shared between the two threads of a row: with one
-// chunk each takes 32 columns, with two chunks each takes one chunk.
-template <bool BF16>
-__device__ __forceinline__ void store_acc_row(uint32_t taddr, int chunks, int half, float scale, bool rot, int irow,
-                                              int icol, const RopeDev& rp, void* dst_row, bool in_grid) {
-  if (chunks == 1) {
-    if (half == 0) store_acc_piece<BF16, 0, 32>(taddr, scale, rot, irow, icol, rp, dst_row, in_grid);
-    else store_acc_piece<BF16, 32, 32>(taddr, scale, rot, irow, icol, rp, dst_row, in_grid);
-  } else {
-    if (half == 0) store_acc_piece<BF16, 0, 64>(taddr, scale, rot, irow, icol, rp, dst_row, in_grid);
-    else store_acc_piece<BF16, 64, 64>(taddr, scale, rot, irow, icol, rp, dst_row, in_grid);
   }
 }
 
@@ -379,20 +397,43 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ C
       mbar_arrive(&bars->op_full[pb]);
       if (m == 0 && half == 0) trace_mark(p, 2, 2 * j + 1);
     }
-    // epilogue: the two threads of a row each store half of the accumulator row(s)
+    // epilogue: the two threads of a row each store half of the accumulator row(s): with one 64-column chunk
+    // each takes 32 columns, with two chunks each takes one chunk.  The cos/sin pairs for rotating dQ / dK
+    // back are fetched before the final wait.
+    using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+    const bool rot = p.rope.idx != nullptr && t_in;
+    int irow = -1, icol = -1;
+    if (rot) decode_idx(__ldg(p.rope.idx + tok), p.rope.max_h, p.rope.max_w, irow, icol);
+    EpiRope<32> c32;
+    EpiRope<64> c64;
+    if (p.qch == 1) {
+      if (half == 0) epi_fetch<0, 32>(c32, rot, irow, icol, p.rope); else epi_fetch<32, 32>(c32, rot, irow, icol, p.rope);
+    } else {
+      if (half == 0) epi_fetch<0, 64>(c64, rot, irow, icol, p.rope); else epi_fetch<64, 64>(c64, rot, irow, icol, p.rope);
+    }
     wait_spin(&bars->acc_done, 0);
     if (ok) {
       tc_fence_after();
       if (m == 0 && half == 0) trace_mark(p, 2, 30);
-      using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
-      const bool rot = p.rope.idx != nullptr && t_in;
-      int irow = -1, icol = -1;
-      if (rot) decode_idx(p.rope.idx[tok], p.rope.max_h, p.rope.max_w, irow, icol);
       T* qk_row = (T*)out_qk.ptr + bi * out_qk.s0 + hi * out_qk.s1 + tok * out_qk.s2;
-      store_acc_row<BF16>(lane_base + kTmAccQK, p.qch, half, p.sm_scale, rot, irow, icol, p.rope, qk_row, t_in);
+      const uint32_t aqk = lane_base + kTmAccQK;
+      if (p.qch == 1) {
+        if (half == 0) store_acc_piece<BF16, 0, 32>(aqk, p.sm_scale, rot, c32, p.rope.R, qk_row, t_in);
+        else store_acc_piece<BF16, 32, 32>(aqk, p.sm_scale, rot, c32, p.rope.R, qk_row, t_in);
+      } else {
+        if (half == 0) store_acc_piece<BF16, 0, 64>(aqk, p.sm_scale, rot, c64, p.rope.R, qk_row, t_in);
+        else store_acc_piece<BF16, 64, 64>(aqk, p.sm_scale, rot, c64, p.rope.R, qk_row, t_in);
+      }
       if constexpr (DKDV) {
         T* v_row = (T*)out_v.ptr + bi * out_v.s0 + hi * out_v.s1 + tok * out_v.s2;
-        store_acc_row<BF16>(lane_base + kTmAccV, p.vch, half, 1.f, false, -1, -1, p.rope, v_row, t_in);
+        const uint32_t av = lane_base + kTmAccV;
+        if (p.vch == 1) {
+          if (half == 0) store_acc_piece<BF16, 0, 32>(av, 1.f, false, c32, 0, v_row, t_in);
+          else store_acc_piece<BF16, 32, 32>(av, 1.f, false, c32, 0, v_row, t_in);
+        } else {
+          if (half == 0) store_acc_piece<BF16, 0, 64>(av, 1.f, false, c64, 0, v_row, t_in);
+          else store_acc_piece<BF16, 64, 64>(av, 1.f, false, c64, 0, v_row, t_in);
+        }
       }
       tc_fence_before();
       if (m == 0 && half == 0) trace_mark(p, 2, 31);

@@ -40,8 +40,10 @@ struct KParams {
   float mask_a, mask_b;  // window mask through the MMA: indicator value and penalty magnitude (powers of two)
   Plan pl;
   RopeDev rope;
+  int n_items;         // persistent kernels: work items = tiles per head x batch x heads
   int32_t* status;
   long long* trace;    // optional per-role clock64() samples of one CTA (performance debugging), else null
+  int trace_it;        // which work item of that CTA is sampled
 };
 
 // Position of a resident-tile CTA and the halo it streams.
@@ -346,7 +348,7 @@ __device__ __forceinline__ void rope_apply(uint8_t* tile, uint32_t chunk_stride,
 
 // Performance tracing of one CTA: role `role` stores its k-th clock sample.
 __device__ __forceinline__ void trace_mark(const KParams& p, int role, int k) {
-  if (p.trace != nullptr && blockIdx.x == 37 && blockIdx.y == 1 && k < 32) p.trace[role * 32 + k] = clock64();
+  if (p.trace != nullptr && blockIdx.x == 37 && blockIdx.y == (gridDim.y > 1 ? 1 : 0) && k < 32) p.trace[role * 32 + k] = clock64();
 }
 
 // Record a timed-out wait (first one wins) so the host can report it.
