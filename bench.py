@@ -209,6 +209,7 @@ def main():
     ap.add_argument("--rope-dims", type=int, default=-1, help="override the number of rotated q/k dims (0 = no RoPE)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--e2e-chunk", type=int, default=32, help="(batch*head) slices per pipelined chunk of the e2e path")
     ap.add_argument("--verify", action="store_true", help="gather outputs over NCCL and compare rank slices")
     args = ap.parse_args()
 
@@ -317,20 +318,15 @@ def main():
     # ---------------------------------------------------------------- e2e with host buffers
     e2e = None
     if not args.no_e2e:
+        from dl_templates_b200.host_pipeline import HostPipeline
         host_in = [x.cpu().pin_memory() for x in (q, k, v, do)]
-        dev_in = [torch.empty_like(x) for x in (q, k, v, do)]
         n_out = 4 if cfg["bwd"] else 1
         host_out = [torch.empty_like(x, device="cpu").pin_memory() for x in ((v, q, k, v) if cfg["bwd"] else (v,))]
+        pipe = HostPipeline(device, chunk_slices=args.e2e_chunk)
 
         def e2e_step():
-            for h, d in zip(host_in, dev_in):
-                d.copy_(h, non_blocking=True)
-            qq, kk, vv, dd = dev_in
-            o, lse = swa.swa_forward(qq, kk, vv, rope, *win, sm, impl=impl)
-            outs = (o,) + (tuple(swa.swa_backward(qq, kk, vv, o, lse, dd, rope, *win, sm, impl=impl))
-                           if cfg["bwd"] else ())
-            for h, d in zip(host_out, outs):
-                h.copy_(d, non_blocking=True)
+            # public host-buffer entry: chunks of (batch, head) slices pipelined over copy-in / compute / copy-out streams
+            pipe.run(host_in[0], host_in[1], host_in[2], host_in[3] if cfg["bwd"] else None, host_out, rope, win, sm)
 
         e2e_steps = max(2, min(args.steps, 10))
         for _ in range(2):
@@ -350,7 +346,7 @@ def main():
                "h2d_bytes_per_step": sum(x.numel() * x.element_size() for x in host_in),
                "d2h_bytes_per_step": sum(x.numel() * x.element_size() for x in host_out[:n_out]),
                "ms_per_step": ms_e2e, "steps": e2e_steps}
-        del host_in, dev_in, host_out
+        del host_in, host_out, pipe
 
     # ---------------------------------------------------------------- optional verification gather
     verified = None
