@@ -11,6 +11,7 @@
 #include "swa_tc.cuh"
 #include "swa_tc_bwd.cuh"
 #include "swa_tc_fwd.cuh"
+#include "swa_tc_fwd2.cuh"
 
 namespace swa {
 namespace tc {
@@ -155,6 +156,61 @@ bool make_plan(const swa_geom_t* g, int which, Plan* out) {
   return pl.smem_bytes <= kSmemLimit;
 }
 
+// Plan for the kernels that keep P / dS in tensor memory (no shared-memory operand buffers) and
+// double-buffer the resident tile.  Tile shapes tried: 16 x 8 first -- a warp's 32 rows then span
+// 4 grid rows and skip 3 of the 7 streamed blocks of a 13-row window -- then 8 x 16.
+bool make_plan2_shape(const swa_geom_t* g, int which, int TH, int TW, Plan* out) {
+  Plan pl;
+  pl.TH = TH;
+  pl.TW = TW;
+  pl.pbufs = 0;
+  const int hw = halo_width(g, pl.TW);
+  if (hw > 64) return false;
+  const int halo_rows = pl.TH + 2 * g->row_size;
+  const int qch = g->d_qk / 64, vch = g->d_v / 64;
+  const uint32_t fixed = 2 * (which == 0 ? qch : qch + vch) * 16384u + 128u * kXRowBytes;
+  const uint32_t row_bytes = (qch + vch) * 128u + kXRowBytes;
+  // tensor-memory budget (512 columns): forward S_0, S_1 at 128-column strides + two O accumulators
+  int nmax = 128;
+  nmax = env_int("SWA_TC_NMAX", nmax);
+  long best_cost = -1;
+  for (int KW = hw; KW <= 64; ++KW)
+    for (int KR = 1; KR <= 16; ++KR) {
+      const int N = KW * KR;
+      if (N > nmax || N % 16) continue;
+      if (fixed + 3 * (uint32_t)N * row_bytes + kSmemSlack > kSmemLimit) continue;
+      const long nblk = (halo_rows + KR - 1) / KR;
+      const long cost = nblk * N * 16 + nblk * 400;  // executed columns + a per-block overhead
+      if (best_cost < 0 || cost < best_cost) {
+        best_cost = cost;
+        pl.KR = KR; pl.KW = KW; pl.N = N;
+      }
+    }
+  if (best_cost < 0) return false;
+  if (int v = env_int("SWA_TC_KR", 0)) {
+    pl.KR = v;
+    pl.KW = env_int("SWA_TC_KW", pl.KW);
+    pl.N = pl.KR * pl.KW;
+  }
+  const uint32_t stage = (uint32_t)pl.N * row_bytes;
+  const int Wtok = g->t_width * g->b_size;
+  pl.n_tiles_x = (Wtok + pl.TW - 1) / pl.TW;
+  pl.n_tiles_y = (g->t_height + pl.TH - 1) / pl.TH;
+  pl.stages = 3;
+  while (pl.stages < kFwd2MaxStages && fixed + (pl.stages + 1) * stage + kSmemSlack <= kSmemLimit) ++pl.stages;
+  pl.stages = env_int("SWA_TC_STAGES", pl.stages);
+  pl.smem_bytes = fixed + pl.stages * stage + kSmemSlack;
+  *out = pl;
+  return pl.smem_bytes <= kSmemLimit && pl.N % 16 == 0 && pl.N <= 128;
+}
+
+bool make_plan2(const swa_geom_t* g, int which, Plan* out) {
+  const int th = env_int("SWA_TC_TH", 0);
+  if (th == 8) return make_plan2_shape(g, which, 8, 16, out);
+  if (th == 16) return make_plan2_shape(g, which, 16, 8, out);
+  return make_plan2_shape(g, which, 16, 8, out) || make_plan2_shape(g, which, 8, 16, out);
+}
+
 // Indicator value a and penalty b (powers of two, exact in fp16 and bf16) of the window mask that
 // rides on the score MMA: a*b*scale*log2(e) >= 4000, so exp2 of a masked score is exactly 0.
 bool mask_constants(float sm_scale, float* a, float* b) {
@@ -206,11 +262,13 @@ const char* unsupported_reason(const swa_geom_t* g, const swa_rope_t* rope, cons
   if (!(g->sm_scale > 0.f)) return "sm_scale must be positive";
   float ma, mb;
   if (!mask_constants(g->sm_scale, &ma, &mb)) return "sm_scale too small for the MMA-side window mask";
-  if (rope && rope->idx && rope->n_rdim % 8) return "n_rdim must be a multiple of 8";
+  if (rope && rope->idx && rope->n_rdim != 8 && rope->n_rdim != 16 && rope->n_rdim != 32)
+    return "n_rdim must be 8, 16 or 32 (RoPE on 32, 64 or 128 dims)";
   if (g->row_size > 64) return "row window too tall for the penalty tables";
   if ((int64_t)g->t_height * g->t_width * g->b_size > (1 << 30)) return "grid too large";
   Plan pl;
-  if (!make_plan(g, which, &pl)) return "no tile plan fits (window too wide for one streamed block)";
+  if (!(which == 0 && !getenv("SWA_TC_FWD1") ? make_plan2(g, which, &pl) : make_plan(g, which, &pl)))
+    return "no tile plan fits (window too wide for one streamed block)";
   for (int i = 0; i < n_tensors; ++i)
     if (!tensor_ok(tensors[i])) return "tensors need unit last stride and 16-byte aligned rows";
   return nullptr;
@@ -219,7 +277,8 @@ const char* unsupported_reason(const swa_geom_t* g, const swa_rope_t* rope, cons
 int launch_fwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
                const swa_tensor_t* v, const swa_tensor_t* o, float* lse, int32_t* status, cudaStream_t st) {
   Plan pl;
-  if (!make_plan(g, 0, &pl)) {
+  const bool v2 = !getenv("SWA_TC_FWD1");
+  if (!(v2 ? make_plan2(g, 0, &pl) : make_plan(g, 0, &pl))) {
     snprintf(g_tc_err, sizeof(g_tc_err), "no tile plan");
     return -1;
   }
@@ -231,8 +290,19 @@ int launch_fwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* 
   // persistent: one CTA per SM, each walks the items blockIdx.x, blockIdx.x + gridDim.x, ...
   const int n_items = pl.n_tiles_x * pl.n_tiles_y * g->B * g->H;
   const int sms = sm_count();
-  dim3 grid(n_items < sms ? n_items : sms), block(kFwdThreads);
-  auto kern = g->dtype == SWA_BF16 ? fwd_kernel<true> : fwd_kernel<false>;
+  dim3 grid(n_items < sms ? n_items : sms), block(v2 ? kFwd2Threads : kFwdThreads);
+  using FwdKernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, KParams, View4, float*);
+  // the RoPE table width is a template parameter of the kernel (index: n_rdim / 8, 0 = no rotation)
+  static const FwdKernel fwd2_table[2][5] = {
+      {fwd2_kernel<false, 0>, fwd2_kernel<false, 1>, fwd2_kernel<false, 2>, nullptr, fwd2_kernel<false, 4>},
+      {fwd2_kernel<true, 0>, fwd2_kernel<true, 1>, fwd2_kernel<true, 2>, nullptr, fwd2_kernel<true, 4>}};
+  const int ni = (rope && rope->idx) ? rope->n_rdim / 8 : 0;
+  FwdKernel kern = v2 ? fwd2_table[g->dtype == SWA_BF16 ? 1 : 0][ni]
+                      : (g->dtype == SWA_BF16 ? fwd_kernel<true> : fwd_kernel<false>);
+  if (kern == nullptr) {
+    snprintf(g_tc_err, sizeof(g_tc_err), "n_rdim %d has no tensor-core kernel", rope ? rope->n_rdim : 0);
+    return -1;
+  }
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem_bytes);
   if (e != cudaSuccess) {
     snprintf(g_tc_err, sizeof(g_tc_err), "cudaFuncSetAttribute(%u bytes): %s", pl.smem_bytes, cudaGetErrorString(e));

@@ -78,12 +78,16 @@ __device__ __forceinline__ void epi_fetch_n(EpiRope<W>& c, int irow, int icol, c
 template <int BASE, int W>
 __device__ __forceinline__ void epi_fetch(EpiRope<W>& c, bool rot, int irow, int icol, const RopeDev& rp) {
   if (!rot) return;
+#ifdef SWA_ROPE_ONLY_R
+  epi_fetch_n<SWA_ROPE_ONLY_R, BASE, W>(c, irow, icol, rp);
+#else
   switch (rp.R) {
     case 8: epi_fetch_n<8, BASE, W>(c, irow, icol, rp); break;
     case 16: epi_fetch_n<16, BASE, W>(c, irow, icol, rp); break;
     case 32: epi_fetch_n<32, BASE, W>(c, irow, icol, rp); break;
     default: break;
   }
+#endif
 }
 
 // Rotate back (transposed rotation) the piece held in registers with the prefetched pairs.
@@ -117,12 +121,16 @@ __device__ __forceinline__ void store_acc_piece(uint32_t taddr, float scale, boo
 #pragma unroll
   for (int e = 0; e < W; ++e) v[e] = __uint_as_float(raw[e]) * scale;
   if (rot) {
+#ifdef SWA_ROPE_ONLY_R
+    inv_rotate_piece<SWA_ROPE_ONLY_R, BASE, W>(v, c);
+#else
     switch (R) {
       case 8: inv_rotate_piece<8, BASE, W>(v, c); break;
       case 16: inv_rotate_piece<16, BASE, W>(v, c); break;
       case 32: inv_rotate_piece<32, BASE, W>(v, c); break;
       default: break;
     }
+#endif
   }
   if (in_grid) {
     uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(dst_row) + BASE * 2);
@@ -481,7 +489,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ C
         if (!ok) break;
         if (t == 0) trace_mark(p, 3, 2 * j);
         if (yp.active) {
-          write_penalty_row(yx_smem + s * yx_stage, yp.row, yp.lo, yp.hi, &bars->pen, j * pl.KR + yjr, yp.row % pl.KW);
+          write_penalty_row(yx_smem + s * yx_stage, yp.row, yp.lo, yp.hi, &bars->pen, j * pl.KR + yjr, yp.row % pl.KW, pl.TH >> 3, pl.TW >> 3);
           if (rope_on && in) rope_apply<BF16>(yqk_smem + s * yqk_stage, blk_bytes, rc, yp, p.rope);
         }
         if constexpr (DKDV) {

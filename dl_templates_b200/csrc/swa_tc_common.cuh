@@ -125,12 +125,12 @@ __device__ __forceinline__ float2 unpack2(uint32_t u) {
 
 // ---- window mask as extra contraction columns ------------------------------------------------
 // The score MMA contracts over 32 extra columns.  The resident token at tile position (i, c)
-// carries mask_a in column i (its row in the tile, i < 8) and in column 8+c (its column in the
-// tile, c < 16); a streamed token carries -mask_b in column i when it is outside the row window
-// of tile row i (or outside the grid) and in column 8+c when it is outside the column window of
-// tile column c.  The product adds 0 to every allowed pair and at most -mask_a*mask_b to every
-// other pair, so exp2 of the scaled score underflows to exactly 0 there and the threads that
-// own the rows do no masking work at all.
+// carries mask_a in column i (its row in the tile, i < TH) and in column TH+c (its column in the
+// tile, c < TW; TH + TW <= 32, both multiples of 8); a streamed token carries -mask_b in column i
+// when it is outside the row window of tile row i (or outside the grid) and in column TH+c when it
+// is outside the column window of tile column c.  The product adds 0 to every allowed pair and at
+// most -mask_a*mask_b to every other pair, so exp2 of the scaled score underflows to exactly 0
+// there and the threads that own the rows do no masking work at all.
 //
 // These "x tiles" are written by threads, not by TMA, in the unswizzled K-major core-matrix
 // layout: 16-byte unit u (0..3) of row r at (r/8)*512 + u*128 + (r%8)*16.
@@ -145,6 +145,7 @@ __device__ __forceinline__ uint8_t* xtile_unit(uint8_t* tile, int row, int unit)
 template <bool BF16>
 __device__ __forceinline__ void write_indicator_row(uint8_t* tile, int row, int part_lo, int part_hi, const KParams& p) {
   const int ti = row / p.pl.TW, tc = row - ti * p.pl.TW;
+  const int hot_r = ti, hot_c = p.pl.TH + tc;
   const float a = p.mask_a;
 #pragma unroll
   for (int u = 0; u < 4; ++u) {
@@ -153,21 +154,19 @@ __device__ __forceinline__ void write_indicator_row(uint8_t* tile, int row, int 
 #pragma unroll
     for (int h = 0; h < 4; ++h) {
       const int d0 = u * 8 + 2 * h, d1 = d0 + 1;
-      const float v0 = (d0 < 8 ? d0 == ti : d0 - 8 == tc) ? a : 0.f;
-      const float v1 = (d1 < 8 ? d1 == ti : d1 - 8 == tc) ? a : 0.f;
-      w[h] = pack2<BF16>(v0, v1);
+      w[h] = pack2<BF16>((d0 == hot_r || d0 == hot_c) ? a : 0.f, (d1 == hot_r || d1 == hot_c) ? a : 0.f);
     }
     *reinterpret_cast<uint4*>(xtile_unit(tile, row, u)) = make_uint4(w[0], w[1], w[2], w[3]);
   }
 }
 
-// The penalty row of a streamed token is [row part (8 values) | column part (16 values) | 8 zeros]:
+// The penalty row of a streamed token is [row part (TH values) | column part (TW values) | zeros]:
 // the row part depends only on the token's halo row, the column part only on its halo column.  Both
-// are tabulated once per CTA; per block a thread only copies 16-byte units.
-constexpr int kPenRows = 160;   // >= 8 + 2*wr + KR halo rows (wr <= 64)
+// are tabulated once per resident tile; per block a thread only copies 16-byte units.
+constexpr int kPenRows = 160;   // >= TH + 2*wr + KR halo rows (wr <= 64)
 struct PenaltyTables {
-  uint4 row[kPenRows];          // [halo row - hr_first]
-  uint4 col[64][2];             // [halo column - hx0]
+  uint4 row[kPenRows][2];       // [halo row - hr_first][tile rows 0-7 | 8-15]
+  uint4 col[64][2];             // [halo column - hx0][tile columns 0-7 | 8-15]
 };
 
 template <bool BF16>
@@ -179,15 +178,18 @@ __device__ __forceinline__ uint4 penalty_unit(int lo, int hi, float nb) {  // 8 
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-// Called by the 128 threads that write the mask tiles, once per CTA.
+// Called by the 128 threads that write the mask tiles, once per resident tile.
 template <bool BF16>
-__device__ __forceinline__ void build_penalty_tables(PenaltyTables* tab, int t, const KParams& p, const TilePos& tp) {
+__device__ __forceinline__ void build_penalty_tables(PenaltyTables* tab, int t, const KParams& p, const TilePos& tp,
+                                                     int nthreads = 128) {
   const float nb = -p.mask_b;
-  for (int hr = t; hr < kPenRows; hr += 128) {
+#pragma unroll 1
+  for (int hr = t; hr < kPenRows; hr += nthreads) {
     const int yr = tp.hr_first + hr;
     const bool in = yr <= tp.hr_last;                       // hr_first >= 0 and hr_last < t_h by construction
     const int lo = in ? yr - p.wr - tp.r0 : 1, hi = in ? yr + p.wr - tp.r0 : 0;
-    tab->row[hr] = penalty_unit<BF16>(lo, hi, nb);
+    tab->row[hr][0] = penalty_unit<BF16>(lo, hi, nb);
+    tab->row[hr][1] = penalty_unit<BF16>(lo - 8, hi - 8, nb);
   }
   if (t < 64) {
     const int yx = tp.hx0 + t;
@@ -204,16 +206,16 @@ __device__ __forceinline__ void build_penalty_tables(PenaltyTables* tab, int t, 
 }
 
 // Penalty row of the streamed token at halo row index `hr` / halo column `jc` into row `row` of an x tile;
-// part 0 = units 0-1, part 1 = units 2-3 (a row may be shared by two threads).
+// part 0 = units 0-1, part 1 = units 2-3 (a row may be shared by two threads).  `th8` = TH / 8.
 __device__ __forceinline__ void write_penalty_row(uint8_t* tile, int row, int part_lo, int part_hi,
-                                                  const PenaltyTables* tab, int hr, int jc) {
-  if (part_lo == 0) {
-    *reinterpret_cast<uint4*>(xtile_unit(tile, row, 0)) = tab->row[hr];
-    *reinterpret_cast<uint4*>(xtile_unit(tile, row, 1)) = tab->col[jc][0];
-  }
-  if (part_hi == 1) {
-    *reinterpret_cast<uint4*>(xtile_unit(tile, row, 2)) = tab->col[jc][1];
-    *reinterpret_cast<uint4*>(xtile_unit(tile, row, 3)) = make_uint4(0u, 0u, 0u, 0u);
+                                                  const PenaltyTables* tab, int hr, int jc, int th8, int tw8) {
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    if ((u >> 1) < part_lo || (u >> 1) > part_hi) continue;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (u < th8) v = tab->row[hr][u];
+    else if (u - th8 < tw8) v = tab->col[jc][u - th8];
+    *reinterpret_cast<uint4*>(xtile_unit(tile, row, u)) = v;
   }
 }
 
@@ -242,6 +244,24 @@ struct RopeParts {
   int row, lo, hi;
   bool active;
 };
+
+// The same for `nthreads` threads: the first nthreads - rows rows are split between two threads
+// (thread t: row-angle half of row t; thread rows + t: column-angle half), the others are whole.
+__device__ __forceinline__ RopeParts rope_parts_n(int t, int rows, int nthreads) {
+  RopeParts r;
+  const int split = min(rows, nthreads - rows);
+  if (t < rows) {
+    r.active = true;
+    r.row = t;
+    r.lo = 0;
+    r.hi = t < split ? 0 : 1;
+  } else {
+    r.row = t - rows;
+    r.active = r.row < split;
+    r.lo = r.hi = 1;
+  }
+  return r;
+}
 
 __device__ __forceinline__ RopeParts rope_parts(int t, int rows) {
   RopeParts r;
@@ -278,12 +298,16 @@ __device__ __forceinline__ void rope_fetch_n(RopeRow& c, const RopeParts& pt, co
 // Start fetching the cos/sin rows of the token with packed index `packed` (-1: nothing to do).
 __device__ __forceinline__ void rope_fetch(RopeRow& c, int32_t packed, const RopeParts& pt, const RopeDev& rp) {
   decode_idx(packed, rp.max_h, rp.max_w, c.pos[0], c.pos[1]);
+#ifdef SWA_ROPE_ONLY_R
+  rope_fetch_n<SWA_ROPE_ONLY_R / 8>(c, pt, rp);
+#else
   switch (rp.R) {
     case 8: rope_fetch_n<1>(c, pt, rp); break;
     case 16: rope_fetch_n<2>(c, pt, rp); break;
     case 32: rope_fetch_n<4>(c, pt, rp); break;
     default: c.pos[0] = c.pos[1] = -1; break;
   }
+#endif
 }
 
 // Rotate one half (0 = row-angle pairs, 1 = column-angle pairs) of a row with NI*4 float4 of (cos, sin).
@@ -338,17 +362,39 @@ __device__ __forceinline__ void rope_apply_n(uint8_t* tile, uint32_t chunk_strid
 template <bool BF16>
 __device__ __forceinline__ void rope_apply(uint8_t* tile, uint32_t chunk_stride, RopeRow& c, const RopeParts& pt,
                                            const RopeDev& rp) {
+#ifdef SWA_ROPE_ONLY_R
+  rope_apply_n<BF16, SWA_ROPE_ONLY_R / 8>(tile, chunk_stride, c, pt, rp);
+#else
   switch (rp.R) {
     case 8: rope_apply_n<BF16, 1>(tile, chunk_stride, c, pt, rp); break;
     case 16: rope_apply_n<BF16, 2>(tile, chunk_stride, c, pt, rp); break;
     case 32: rope_apply_n<BF16, 4>(tile, chunk_stride, c, pt, rp); break;
     default: break;
   }
+#endif
+}
+
+// The same with the table width fixed at compile time (NI = n_rdim / 8; 0 = no rotation): a kernel
+// instantiated for one width carries one copy of the rotation code instead of three.
+template <int NI>
+__device__ __forceinline__ void rope_fetch_t(RopeRow& c, int32_t packed, const RopeParts& pt, const RopeDev& rp) {
+  if constexpr (NI > 0) {
+    decode_idx(packed, rp.max_h, rp.max_w, c.pos[0], c.pos[1]);
+    rope_fetch_n<NI>(c, pt, rp);
+  }
+}
+template <bool BF16, int NI>
+__device__ __forceinline__ void rope_apply_t(uint8_t* tile, uint32_t chunk_stride, RopeRow& c, const RopeParts& pt,
+                                             const RopeDev& rp) {
+  if constexpr (NI > 0) rope_apply_n<BF16, NI>(tile, chunk_stride, c, pt, rp);
 }
 
 // Performance tracing of one CTA: role `role` stores its k-th clock sample.
+// Compiled in only with -DSWA_TC_TRACE: the marks cost instructions in the scalar roles.
 __device__ __forceinline__ void trace_mark(const KParams& p, int role, int k) {
+#ifdef SWA_TC_TRACE
   if (p.trace != nullptr && blockIdx.x == 37 && blockIdx.y == (gridDim.y > 1 ? 1 : 0) && k < 32) p.trace[role * 32 + k] = clock64();
+#endif
 }
 
 // Record a timed-out wait (first one wins) so the host can report it.

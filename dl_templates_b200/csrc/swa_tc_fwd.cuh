@@ -420,7 +420,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         // only after every MMA of the stage's previous block has completed
         wait_park(&bars->kv_full[s], (kv / pl.stages) & 1);
         if (ok) {
-          if (kp.active) write_penalty_row(kx_smem + s * kx_stage, kp.row, kp.lo, kp.hi, &bars->pen, j * pl.KR + kjr, kp.row % pl.KW);
+          if (kp.active) write_penalty_row(kx_smem + s * kx_stage, kp.row, kp.lo, kp.hi, &bars->pen, j * pl.KR + kjr, kp.row % pl.KW, pl.TH >> 3, pl.TW >> 3);
           if (rope_on && kx_in && kr < p.t_h) rope_apply<BF16>(k_smem + s * k_stage, blk_bytes, rc, kp, p.rope);
           fence_proxy_async_smem();
           mbar_arrive(&bars->k_ready[s]);

@@ -48,6 +48,12 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// Per-warpgroup register budget (all four warps of the group execute it).
+template <uint32_t REGS>
+__device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS)); }
+template <uint32_t REGS>
+__device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS)); }
+
 // ---- mbarrier ----------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
@@ -63,6 +69,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Non-blocking test of the phase: never suspends the thread, so a polling loop reacts within a few cycles.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(smem_u32(bar)), "r"(parity)
@@ -92,11 +111,19 @@ constexpr uint32_t kWaitMaxPolls = 1u << 22;  // polls (spinning) resp. sleeps b
 // PARK_NS == 0: spin on try_wait (warps on the critical path).  PARK_NS > 0: each poll lets the
 // hardware park the thread for up to PARK_NS nanoseconds and wake it when the phase completes, so
 // a waiting warp takes (almost) no issue slots from the working warps of its sub-partition.
-template <uint32_t PARK_NS = 0>
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
+// PARK_NS == kPollNoSuspend: spin on the non-blocking test_wait.
+//
+// Only the first probe is inlined at the call site; the polling loop is one shared out-of-line
+// function per mode.  The kernels are instruction-fetch bound in their rarely executed scalar
+// parts, so every call site has to stay small.
+constexpr uint32_t kPollNoSuspend = 0xffffffffu;
+template <uint32_t PARK_NS>
+__device__ __forceinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   for (uint32_t it = 0; it < kWaitMaxPolls; ++it) {
-    if constexpr (PARK_NS == 0) {
+    if constexpr (PARK_NS == kPollNoSuspend) {
+      if (mbar_test_wait(bar, parity)) return true;
+      if ((it & 1023u) == 1023u && *abort_flag) return false;
+    } else if constexpr (PARK_NS == 0) {
       if (mbar_try_wait(bar, parity)) return true;
       if ((it & 1023u) == 1023u && *abort_flag) return false;
     } else {
@@ -106,6 +133,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
   *abort_flag = 1;
   return false;
+}
+template <uint32_t PARK_NS = 0>
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (PARK_NS == kPollNoSuspend ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow<PARK_NS>(bar, parity, abort_flag);
 }
 
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
@@ -186,6 +218,18 @@ __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (128 rows x 16 contraction elements) is read from
+// tensor memory, row r on lane r, elements 2c and 2c+1 of the contraction packed (low half first)
+// in 32-bit column a_tmem + c.  Costs about half of the shared-memory form for N <= 64, whose A
+// read (128 rows x 32 bytes per instruction) is what bounds it.
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Arrive on `bar` once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -224,6 +268,11 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
       ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
       "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
