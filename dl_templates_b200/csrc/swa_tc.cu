@@ -12,6 +12,7 @@
 #include "swa_tc_bwd.cuh"
 #include "swa_tc_fwd.cuh"
 #include "swa_tc_fwd2.cuh"
+#include "swa_tc_bwd2.cuh"
 
 namespace swa {
 namespace tc {
@@ -159,6 +160,9 @@ bool make_plan(const swa_geom_t* g, int which, Plan* out) {
 // Plan for the kernels that keep P / dS in tensor memory (no shared-memory operand buffers) and
 // double-buffer the resident tile.  Tile shapes tried: 16 x 8 first -- a warp's 32 rows then span
 // 4 grid rows and skip 3 of the 7 streamed blocks of a 13-row window -- then 8 x 16.
+//   tensor memory (512 columns): forward  score buffers at 128-column strides + two O accumulators (N <= 128);
+//                                backward nsb pairs (S, dP) of 2N columns + the accumulators
+//   shared memory:               nxb resident-tile buffers + indicator rows + stages x (block + penalty rows [+ lse, delta])
 bool make_plan2_shape(const swa_geom_t* g, int which, int TH, int TW, Plan* out) {
   Plan pl;
   pl.TH = TH;
@@ -168,40 +172,52 @@ bool make_plan2_shape(const swa_geom_t* g, int which, int TH, int TW, Plan* out)
   if (hw > 64) return false;
   const int halo_rows = pl.TH + 2 * g->row_size;
   const int qch = g->d_qk / 64, vch = g->d_v / 64;
-  const uint32_t fixed = 2 * (which == 0 ? qch : qch + vch) * 16384u + 128u * kXRowBytes;
+  const uint32_t x_bytes = (which == 0 ? qch : qch + vch) * 16384u;
   const uint32_t row_bytes = (qch + vch) * 128u + kXRowBytes;
-  // tensor-memory budget (512 columns): forward S_0, S_1 at 128-column strides + two O accumulators
-  int nmax = 128;
-  nmax = env_int("SWA_TC_NMAX", nmax);
-  long best_cost = -1;
-  for (int KW = hw; KW <= 64; ++KW)
-    for (int KR = 1; KR <= 16; ++KR) {
-      const int N = KW * KR;
-      if (N > nmax || N % 16) continue;
-      if (fixed + 3 * (uint32_t)N * row_bytes + kSmemSlack > kSmemLimit) continue;
-      const long nblk = (halo_rows + KR - 1) / KR;
-      const long cost = nblk * N * 16 + nblk * 400;  // executed columns + a per-block overhead
-      if (best_cost < 0 || cost < best_cost) {
-        best_cost = cost;
-        pl.KR = KR; pl.KW = KW; pl.N = N;
+  const uint32_t stage_extra = which == 0 ? 0u : 1024u;       // lse / delta slots of a streamed block
+  const int acc_cols = which == 0 ? 0 : (which == 1 ? 64 * qch : 64 * (qch + vch));
+  const int min_stages = 3;
+  for (int nsb = 2; nsb >= 1; --nsb) {
+    int nmax = which == 0 ? 128 : (512 - acc_cols) / (2 * nsb);
+    nmax = nmax > 128 ? 128 : nmax;
+    nmax = env_int("SWA_TC_NMAX", nmax);
+    for (int nxb = 2; nxb >= 1; --nxb) {
+      const uint32_t fixed = nxb * x_bytes + 128u * kXRowBytes;
+      long best_cost = -1;
+      for (int KW = hw; KW <= 64; ++KW)
+        for (int KR = 1; KR <= 16; ++KR) {
+          const int N = KW * KR;
+          if (N > nmax || N % 16) continue;
+          if (fixed + min_stages * ((uint32_t)N * row_bytes + stage_extra) + kSmemSlack > kSmemLimit) continue;
+          const long nblk = (halo_rows + KR - 1) / KR;
+          const long cost = nblk * N * 16 + nblk * 400;  // executed columns + a per-block overhead
+          if (best_cost < 0 || cost < best_cost) {
+            best_cost = cost;
+            pl.KR = KR; pl.KW = KW; pl.N = N;
+          }
+        }
+      if (best_cost < 0) continue;
+      if (int v = env_int("SWA_TC_KR", 0)) {
+        pl.KR = v;
+        pl.KW = env_int("SWA_TC_KW", pl.KW);
+        pl.N = pl.KR * pl.KW;
       }
+      const uint32_t stage = (uint32_t)pl.N * row_bytes + stage_extra;
+      const int Wtok = g->t_width * g->b_size;
+      pl.n_tiles_x = (Wtok + pl.TW - 1) / pl.TW;
+      pl.n_tiles_y = (g->t_height + pl.TH - 1) / pl.TH;
+      pl.nsb = nsb;
+      pl.nxb = nxb;
+      pl.stages = min_stages;
+      while (pl.stages < kFwd2MaxStages && fixed + (pl.stages + 1) * stage + kSmemSlack <= kSmemLimit) ++pl.stages;
+      pl.stages = env_int("SWA_TC_STAGES", pl.stages);
+      pl.smem_bytes = fixed + pl.stages * stage + kSmemSlack;
+      *out = pl;
+      return pl.smem_bytes <= kSmemLimit && pl.N % 16 == 0 && pl.N <= nmax && pl.stages >= 2;
     }
-  if (best_cost < 0) return false;
-  if (int v = env_int("SWA_TC_KR", 0)) {
-    pl.KR = v;
-    pl.KW = env_int("SWA_TC_KW", pl.KW);
-    pl.N = pl.KR * pl.KW;
+    if (which == 0) break;
   }
-  const uint32_t stage = (uint32_t)pl.N * row_bytes;
-  const int Wtok = g->t_width * g->b_size;
-  pl.n_tiles_x = (Wtok + pl.TW - 1) / pl.TW;
-  pl.n_tiles_y = (g->t_height + pl.TH - 1) / pl.TH;
-  pl.stages = 3;
-  while (pl.stages < kFwd2MaxStages && fixed + (pl.stages + 1) * stage + kSmemSlack <= kSmemLimit) ++pl.stages;
-  pl.stages = env_int("SWA_TC_STAGES", pl.stages);
-  pl.smem_bytes = fixed + pl.stages * stage + kSmemSlack;
-  *out = pl;
-  return pl.smem_bytes <= kSmemLimit && pl.N % 16 == 0 && pl.N <= 128;
+  return false;
 }
 
 bool make_plan2(const swa_geom_t* g, int which, Plan* out) {
@@ -267,7 +283,8 @@ const char* unsupported_reason(const swa_geom_t* g, const swa_rope_t* rope, cons
   if (g->row_size > 64) return "row window too tall for the penalty tables";
   if ((int64_t)g->t_height * g->t_width * g->b_size > (1 << 30)) return "grid too large";
   Plan pl;
-  if (!(which == 0 && !getenv("SWA_TC_FWD1") ? make_plan2(g, which, &pl) : make_plan(g, which, &pl)))
+  const bool v2 = which == 0 ? !getenv("SWA_TC_FWD1") : !getenv("SWA_TC_BWD1");
+  if (!(v2 ? make_plan2(g, which, &pl) : make_plan(g, which, &pl)))
     return "no tile plan fits (window too wide for one streamed block)";
   for (int i = 0; i < n_tensors; ++i)
     if (!tensor_ok(tensors[i])) return "tensors need unit last stride and 16-byte aligned rows";
@@ -322,7 +339,8 @@ int launch_bwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* 
                const swa_tensor_t* yqk, const swa_tensor_t* yv, const float* lse, const float* delta,
                const swa_tensor_t* out_qk, const swa_tensor_t* out_v, int32_t* status, cudaStream_t st) {
   Plan pl;
-  if (!make_plan(g, DKDV ? 2 : 1, &pl)) {
+  const bool v2 = !getenv("SWA_TC_BWD1");
+  if (!(v2 ? make_plan2(g, DKDV ? 2 : 1, &pl) : make_plan(g, DKDV ? 2 : 1, &pl))) {
     snprintf(g_tc_err, sizeof(g_tc_err), "no tile plan");
     return -1;
   }
@@ -331,16 +349,32 @@ int launch_bwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* 
       !make_map(&myqk, yqk, g, g->d_qk, pl.KW, pl.KR) || !make_map(&myv, yv, g, g->d_v, pl.KW, pl.KR))
     return -1;
   const KParams p = make_params(g, rope, pl, status);
+  const int sms = sm_count();
   dim3 grid(pl.n_tiles_x * pl.n_tiles_y, g->B * g->H), block(kBwdThreads);
-  auto kern = g->dtype == SWA_BF16 ? bwd_kernel<true, DKDV> : bwd_kernel<false, DKDV>;
+  if (v2) {   // persistent: one CTA per SM walks the items
+    grid = dim3(p.n_items < sms ? p.n_items : sms);
+    block = dim3(kBwd2Threads);
+  }
+  using BwdKernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, KParams, const float*,
+                             const float*, View4, View4);
+  static const BwdKernel bwd2_table[2][5] = {
+      {bwd2_kernel<false, DKDV, 0>, bwd2_kernel<false, DKDV, 1>, bwd2_kernel<false, DKDV, 2>, nullptr, bwd2_kernel<false, DKDV, 4>},
+      {bwd2_kernel<true, DKDV, 0>, bwd2_kernel<true, DKDV, 1>, bwd2_kernel<true, DKDV, 2>, nullptr, bwd2_kernel<true, DKDV, 4>}};
+  const int ni = (rope && rope->idx) ? rope->n_rdim / 8 : 0;
+  BwdKernel kern = v2 ? bwd2_table[g->dtype == SWA_BF16 ? 1 : 0][ni]
+                      : (g->dtype == SWA_BF16 ? bwd_kernel<true, DKDV> : bwd_kernel<false, DKDV>);
+  if (kern == nullptr) {
+    snprintf(g_tc_err, sizeof(g_tc_err), "n_rdim %d has no tensor-core kernel", rope ? rope->n_rdim : 0);
+    return -1;
+  }
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem_bytes);
   if (e != cudaSuccess) {
     snprintf(g_tc_err, sizeof(g_tc_err), "cudaFuncSetAttribute(%u bytes): %s", pl.smem_bytes, cudaGetErrorString(e));
     return -1;
   }
   if (getenv("SWA_TC_VERBOSE"))
-    fprintf(stderr, "[swa2d] %s plan: tile %dx%d, block %dx%d (N=%d), stages %d, pbufs %d, smem %u, grid %ux%u\n",
-            DKDV ? "dkdv" : "dq", pl.TH, pl.TW, pl.KR, pl.KW, pl.N, pl.stages, pl.pbufs, pl.smem_bytes, grid.x, grid.y);
+    fprintf(stderr, "[swa2d] %s plan: tile %dx%d, block %dx%d (N=%d), stages %d, pbufs %d, nsb %d, nxb %d, smem %u, grid %ux%u\n",
+            DKDV ? "dkdv" : "dq", pl.TH, pl.TW, pl.KR, pl.KW, pl.N, pl.stages, pl.pbufs, pl.nsb, pl.nxb, pl.smem_bytes, grid.x, grid.y);
   kern<<<grid, block, pl.smem_bytes, st>>>(mxqk, mxv, myqk, myv, p, lse, delta, make_view(out_qk),
                                           out_v ? make_view(out_v) : View4{nullptr, 0, 0, 0, 0});
   return 0;

@@ -30,6 +30,7 @@ struct Plan {
   int KR, KW, N;       // streamed block: rows x token columns, N = KR*KW
   int n_tiles_x, n_tiles_y;
   int stages, pbufs;   // streamed-block pipeline depth, buffers for the P/dS operand
+  int nsb, nxb;        // backward: (S, dP) buffer pairs in tensor memory, resident-tile buffers in shared memory
   uint32_t smem_bytes;
 };
 
@@ -65,6 +66,13 @@ __device__ __forceinline__ TilePos tile_pos(const KParams& p, int tile_idx) {
   t.hr_last = min(t.r0 + p.pl.TH - 1 + p.wr, p.t_h - 1);
   t.nblk = (t.hr_last - t.hr_first + p.pl.KR) / p.pl.KR;
   return t;
+}
+
+// Streamed blocks of work item `item`.
+__device__ __forceinline__ int item_blocks(const KParams& p, int item, int tiles_per_head) {
+  const int tile = item % tiles_per_head, ty = tile / p.pl.n_tiles_x, r0 = ty * p.pl.TH;
+  const int first = max(r0 - p.wr, 0), last = min(r0 + p.pl.TH - 1 + p.wr, p.t_h - 1);
+  return (last - first + p.pl.KR) / p.pl.KR;
 }
 
 // Bit jc of the result: halo column jc (token column hx0+jc) is inside the grid and

@@ -57,13 +57,6 @@ constexpr int kFwd2RopeThreads = 192;     // warps 2-3 and 12-15
 constexpr uint32_t kFwd2TmemCols = 512;
 constexpr float kRescaleThreshold2 = 8.f;       // lazy rescale when the running max grows by > 2^8
 
-// Streamed blocks of work item `item`.
-__device__ __forceinline__ int item_blocks(const KParams& p, int item, int tiles_per_head) {
-  const int tile = item % tiles_per_head, ty = tile / p.pl.n_tiles_x, r0 = ty * p.pl.TH;
-  const int first = max(r0 - p.wr, 0), last = min(r0 + p.pl.TH - 1 + p.wr, p.t_h - 1);
-  return (last - first + p.pl.KR) / p.pl.KR;
-}
-
 template <bool BF16, int NI>
 __global__ void __launch_bounds__(kFwd2Threads, 1)
 fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,

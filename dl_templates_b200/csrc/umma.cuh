@@ -117,18 +117,26 @@ constexpr uint32_t kWaitMaxPolls = 1u << 22;  // polls (spinning) resp. sleeps b
 // function per mode.  The kernels are instruction-fetch bound in their rarely executed scalar
 // parts, so every call site has to stay small.
 constexpr uint32_t kPollNoSuspend = 0xffffffffu;
+constexpr unsigned long long kWaitBudgetNs = 200ull * 1000 * 1000;   // a wait gives up after 0.2 s of wall time
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
 template <uint32_t PARK_NS>
 __device__ __forceinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  const unsigned long long t0 = global_ns();
   for (uint32_t it = 0; it < kWaitMaxPolls; ++it) {
     if constexpr (PARK_NS == kPollNoSuspend) {
       if (mbar_test_wait(bar, parity)) return true;
-      if ((it & 1023u) == 1023u && *abort_flag) return false;
     } else if constexpr (PARK_NS == 0) {
       if (mbar_try_wait(bar, parity)) return true;
-      if ((it & 1023u) == 1023u && *abort_flag) return false;
     } else {
       if (mbar_try_wait_hint(bar, parity, PARK_NS)) return true;
-      if ((it & 15u) == 15u && *abort_flag) return false;
+    }
+    if ((it & 15u) == 15u) {
+      if (*abort_flag) return false;
+      if (global_ns() - t0 > kWaitBudgetNs) break;
     }
   }
   *abort_flag = 1;

@@ -237,6 +237,34 @@ def test_config5_full_grid_properties():
     assert rel < 1e-2, rel
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("grid,w", [((21, 21), 7), ((37, 19), 5), ((9, 50), 9)])
+def test_ragged_grids_tensor_core_path(grid, w, dtype):
+    """Grids that are no multiple of the resident tile in rows or columns (partly empty tiles, one-block
+    items), RoPE with dropped tokens and tokens whose row or column half alone is -1, forward + backward
+    on the tcgen05 kernels against the oracle."""
+    th, tw = grid
+    N = th * tw
+    q, k, v, do = orc.seeded_inputs(1, 3, N, 64, 64, dtype, 7)
+    idx = orc.encode_idx(th, tw)
+    gsel = torch.Generator().manual_seed(11)
+    r = torch.rand(N, generator=gsel)
+    idx[r < 0.05] = -1                                              # token not rotated at all
+    row_only = (r >= 0.05) & (r < 0.10)
+    idx[row_only] = (idx[row_only] & ~0xFFFF) | 0xFFFF              # column half -1: only the row angle applies
+    col_only = (r >= 0.10) & (r < 0.15)
+    idx[col_only] = idx[col_only] | -65536                          # row half -1
+    idx = idx.to(torch.int32)
+    tab_r, tab_c = orc.make_cs_table(16, th, 10000.0), orc.make_cs_table(16, tw, 10000.0)
+    half = (w - 1) // 2
+    win = (1, th, tw, half, half)
+    rope = (idx, tab_r, tab_c)
+    assert swa.selected_impl(q.to(DEV), v.to(DEV), tuple(t.to(DEV) for t in rope), *win, 0.125, which=1, impl="auto") == "tc"
+    got, _ = run_gpu(q, k, v, do, rope, win, 0.125, impl="tc")
+    want = orc.fused_ref(q.float(), k.float(), v.float(), do.float(), *rope, *win, 0.125)
+    assert_close(got, want, dtype, what=f"ragged {grid}")
+
+
 def test_host_pipeline_matches_direct_calls():
     """Chunked, stream-pipelined host-buffer path (uneven last chunk, buffers reused) == direct calls, bitwise."""
     from dl_templates_b200.host_pipeline import HostPipeline
