@@ -11,8 +11,6 @@
 #include "swa_tc.cuh"
 #include "swa_tc_bwd.cuh"
 #include "swa_tc_fwd.cuh"
-#include "swa_tc_fwd2.cuh"
-#include "swa_tc_bwd2.cuh"
 
 namespace swa {
 namespace tc {
@@ -93,81 +91,16 @@ int halo_width(const swa_geom_t* g, int TW) {
   return best;
 }
 
-// Choose the resident tile and streamed-block shape.  `fixed_bytes` = shared memory that
-// does not scale with the pipeline depth; `stage_bytes_per_row` = bytes one streamed
-// token row (all its operands) takes; `pbuf_bytes(N)` handled by the caller through
-// `p_operands` (number of 16-bit [128 x N] operand buffers written by the softmax warps).
-bool make_plan(const swa_geom_t* g, int which, Plan* out) {
-  Plan pl;
-  pl.TH = 8;   // the window-mask columns are laid out for 8 tile rows x 16 tile columns
-  pl.TW = 16;
-  const int hw = halo_width(g, pl.TW);
-  if (hw > 64) return false;
-  const int halo_rows = pl.TH + 2 * g->row_size;
-  const int qch = g->d_qk / 64, vch = g->d_v / 64;
-  // per-row bytes of one pipeline stage and fixed bytes, per kernel
-  //   fwd : stage = K + V            fixed = Q              p-operands = 1 (P)
-  //   dq  : stage = K + V            fixed = Q + dO         p-operands = 1 (dS)
-  //   dkdv: stage = Q + dO (+lse,delta)  fixed = K + V      p-operands = 2 (P^T, dS^T)
-  // forward: the query tile is double-buffered (persistent kernel)
-  const uint32_t fixed = (which == 0 ? 2 * qch : qch + vch) * 16384u + 128u * kXRowBytes;
-  const uint32_t row_bytes = (qch + vch) * 128u + kXRowBytes;
-  const int p_ops = which == 2 ? 2 : 1;
-  // blocks of up to 128 streamed tokens (the backward kernels double-buffer S and dP in TMEM up to 64)
-  const int nmax = env_int("SWA_TC_NMAX", 128);
-  long best_cost = -1;
-  for (int KW = hw; KW <= 64; ++KW)
-    for (int KR = 1; KR <= 16; ++KR) {
-      const int N = KW * KR;
-      if (N > nmax || N % 16) continue;
-      const int pch = (N + 63) / 64;
-      const uint32_t stage = (uint32_t)N * row_bytes;
-      const uint32_t pbuf = (uint32_t)p_ops * pch * 16384u;
-      const uint32_t need = fixed + 2 * stage + pbuf + kSmemSlack;
-      if (need > kSmemLimit) continue;
-      const long nblk = (halo_rows + KR - 1) / KR;
-      const long cost = nblk * N * 16 + nblk * 400;  // executed columns + a per-block overhead
-      if (best_cost < 0 || cost < best_cost) {
-        best_cost = cost;
-        pl.KR = KR; pl.KW = KW; pl.N = N;
-      }
-    }
-  if (best_cost < 0) return false;
-  if (int v = env_int("SWA_TC_KR", 0)) {
-    pl.KR = v;
-    pl.KW = env_int("SWA_TC_KW", pl.KW);
-    pl.N = pl.KR * pl.KW;
-  }
-  const int pch = (pl.N + 63) / 64;
-  const uint32_t stage = (uint32_t)pl.N * row_bytes;
-  const uint32_t pbuf1 = (uint32_t)p_ops * pch * 16384u;
-  const int Wtok = g->t_width * g->b_size;
-  pl.n_tiles_x = (Wtok + pl.TW - 1) / pl.TW;
-  pl.n_tiles_y = (g->t_height + pl.TH - 1) / pl.TH;
-  const int max_blocks = (halo_rows + pl.KR - 1) / pl.KR;
-  pl.pbufs = (fixed + 2 * stage + 2 * pbuf1 + kSmemSlack <= kSmemLimit) ? 2 : 1;
-  pl.pbufs = env_int("SWA_TC_PBUFS", pl.pbufs);
-  pl.stages = 2;
-  while (pl.stages < kMaxStages && pl.stages < max_blocks &&
-         fixed + (pl.stages + 1) * stage + pl.pbufs * pbuf1 + kSmemSlack <= kSmemLimit)
-    ++pl.stages;
-  pl.stages = env_int("SWA_TC_STAGES", pl.stages);
-  pl.smem_bytes = fixed + pl.stages * stage + pl.pbufs * pbuf1 + kSmemSlack;
-  *out = pl;
-  return pl.smem_bytes <= kSmemLimit;
-}
-
-// Plan for the kernels that keep P / dS in tensor memory (no shared-memory operand buffers) and
-// double-buffer the resident tile.  Tile shapes tried: 16 x 8 first -- a warp's 32 rows then span
+// Choose the resident tile, the streamed-block shape and the pipeline depths.  Tile shapes tried: 16 x 8 first -- a warp's 32 rows then span
 // 4 grid rows and skip 3 of the 7 streamed blocks of a 13-row window -- then 8 x 16.
 //   tensor memory (512 columns): forward  score buffers at 128-column strides + two O accumulators (N <= 128);
 //                                backward nsb pairs (S, dP) of 2N columns + the accumulators
 //   shared memory:               nxb resident-tile buffers + indicator rows + stages x (block + penalty rows [+ lse, delta])
-bool make_plan2_shape(const swa_geom_t* g, int which, int TH, int TW, Plan* out) {
+bool make_plan_shape(const swa_geom_t* g, int which, int TH, int TW, uint32_t tab_bytes, Plan* out) {
   Plan pl;
+  pl.tab_bytes = tab_bytes;
   pl.TH = TH;
   pl.TW = TW;
-  pl.pbufs = 0;
   const int hw = halo_width(g, pl.TW);
   if (hw > 64) return false;
   const int halo_rows = pl.TH + 2 * g->row_size;
@@ -182,7 +115,7 @@ bool make_plan2_shape(const swa_geom_t* g, int which, int TH, int TW, Plan* out)
     nmax = nmax > 128 ? 128 : nmax;
     nmax = env_int("SWA_TC_NMAX", nmax);
     for (int nxb = 2; nxb >= 1; --nxb) {
-      const uint32_t fixed = nxb * x_bytes + 128u * kXRowBytes;
+      const uint32_t fixed = nxb * x_bytes + 128u * kXRowBytes + tab_bytes;
       long best_cost = -1;
       for (int KW = hw; KW <= 64; ++KW)
         for (int KR = 1; KR <= 16; ++KR) {
@@ -209,7 +142,7 @@ bool make_plan2_shape(const swa_geom_t* g, int which, int TH, int TW, Plan* out)
       pl.nsb = nsb;
       pl.nxb = nxb;
       pl.stages = min_stages;
-      while (pl.stages < kFwd2MaxStages && fixed + (pl.stages + 1) * stage + kSmemSlack <= kSmemLimit) ++pl.stages;
+      while (pl.stages < kMaxStages && fixed + (pl.stages + 1) * stage + kSmemSlack <= kSmemLimit) ++pl.stages;
       pl.stages = env_int("SWA_TC_STAGES", pl.stages);
       pl.smem_bytes = fixed + pl.stages * stage + kSmemSlack;
       *out = pl;
@@ -220,11 +153,21 @@ bool make_plan2_shape(const swa_geom_t* g, int which, int TH, int TW, Plan* out)
   return false;
 }
 
-bool make_plan2(const swa_geom_t* g, int which, Plan* out) {
+// Bytes of the cos/sin tables when they are small enough to be staged in shared memory, else 0.
+uint32_t rope_table_bytes(const swa_rope_t* rope) {
+  if (!rope || !rope->idx) return 0;
+  const uint64_t b = (uint64_t)(rope->max_h + rope->max_w) * rope->n_rdim * 8;
+  return b <= 48 * 1024 && !getenv("SWA_TC_NO_TABS") ? (uint32_t)((b + 15) & ~15ull) : 0;
+}
+
+bool make_plan(const swa_geom_t* g, const swa_rope_t* rope, int which, Plan* out) {
   const int th = env_int("SWA_TC_TH", 0);
-  if (th == 8) return make_plan2_shape(g, which, 8, 16, out);
-  if (th == 16) return make_plan2_shape(g, which, 16, 8, out);
-  return make_plan2_shape(g, which, 16, 8, out) || make_plan2_shape(g, which, 8, 16, out);
+  for (uint32_t tab = rope_table_bytes(rope);; tab = 0) {   // with the staged tables if a plan fits, else without
+    if (th == 8) { if (make_plan_shape(g, which, 8, 16, tab, out)) return true; }
+    else if (th == 16) { if (make_plan_shape(g, which, 16, 8, tab, out)) return true; }
+    else if (make_plan_shape(g, which, 16, 8, tab, out) || make_plan_shape(g, which, 8, 16, tab, out)) return true;
+    if (tab == 0) return false;
+  }
 }
 
 // Indicator value a and penalty b (powers of two, exact in fp16 and bf16) of the window mask that
@@ -283,8 +226,7 @@ const char* unsupported_reason(const swa_geom_t* g, const swa_rope_t* rope, cons
   if (g->row_size > 64) return "row window too tall for the penalty tables";
   if ((int64_t)g->t_height * g->t_width * g->b_size > (1 << 30)) return "grid too large";
   Plan pl;
-  const bool v2 = which == 0 ? !getenv("SWA_TC_FWD1") : !getenv("SWA_TC_BWD1");
-  if (!(v2 ? make_plan2(g, which, &pl) : make_plan(g, which, &pl)))
+  if (!make_plan(g, rope, which, &pl))
     return "no tile plan fits (window too wide for one streamed block)";
   for (int i = 0; i < n_tensors; ++i)
     if (!tensor_ok(tensors[i])) return "tensors need unit last stride and 16-byte aligned rows";
@@ -294,8 +236,7 @@ const char* unsupported_reason(const swa_geom_t* g, const swa_rope_t* rope, cons
 int launch_fwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
                const swa_tensor_t* v, const swa_tensor_t* o, float* lse, int32_t* status, cudaStream_t st) {
   Plan pl;
-  const bool v2 = !getenv("SWA_TC_FWD1");
-  if (!(v2 ? make_plan2(g, 0, &pl) : make_plan(g, 0, &pl))) {
+  if (!make_plan(g, rope, 0, &pl)) {
     snprintf(g_tc_err, sizeof(g_tc_err), "no tile plan");
     return -1;
   }
@@ -307,15 +248,17 @@ int launch_fwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* 
   // persistent: one CTA per SM, each walks the items blockIdx.x, blockIdx.x + gridDim.x, ...
   const int n_items = pl.n_tiles_x * pl.n_tiles_y * g->B * g->H;
   const int sms = sm_count();
-  dim3 grid(n_items < sms ? n_items : sms), block(v2 ? kFwd2Threads : kFwdThreads);
+  dim3 grid(n_items < sms ? n_items : sms), block(kFwdThreads);
   using FwdKernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, KParams, View4, float*);
   // the RoPE table width is a template parameter of the kernel (index: n_rdim / 8, 0 = no rotation)
-  static const FwdKernel fwd2_table[2][5] = {
-      {fwd2_kernel<false, 0>, fwd2_kernel<false, 1>, fwd2_kernel<false, 2>, nullptr, fwd2_kernel<false, 4>},
-      {fwd2_kernel<true, 0>, fwd2_kernel<true, 1>, fwd2_kernel<true, 2>, nullptr, fwd2_kernel<true, 4>}};
+  // ... and so is whether the cos/sin tables are staged in shared memory
+  static const FwdKernel fwd_table[2][2][5] = {
+      {{fwd_kernel<false, 0, false>, fwd_kernel<false, 1, false>, fwd_kernel<false, 2, false>, nullptr, fwd_kernel<false, 4, false>},
+       {fwd_kernel<false, 0, false>, fwd_kernel<false, 1, true>, fwd_kernel<false, 2, true>, nullptr, fwd_kernel<false, 4, true>}},
+      {{fwd_kernel<true, 0, false>, fwd_kernel<true, 1, false>, fwd_kernel<true, 2, false>, nullptr, fwd_kernel<true, 4, false>},
+       {fwd_kernel<true, 0, false>, fwd_kernel<true, 1, true>, fwd_kernel<true, 2, true>, nullptr, fwd_kernel<true, 4, true>}}};
   const int ni = (rope && rope->idx) ? rope->n_rdim / 8 : 0;
-  FwdKernel kern = v2 ? fwd2_table[g->dtype == SWA_BF16 ? 1 : 0][ni]
-                      : (g->dtype == SWA_BF16 ? fwd_kernel<true> : fwd_kernel<false>);
+  FwdKernel kern = fwd_table[g->dtype == SWA_BF16 ? 1 : 0][pl.tab_bytes ? 1 : 0][ni];
   if (kern == nullptr) {
     snprintf(g_tc_err, sizeof(g_tc_err), "n_rdim %d has no tensor-core kernel", rope ? rope->n_rdim : 0);
     return -1;
@@ -326,8 +269,8 @@ int launch_fwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* 
     return -1;
   }
   if (getenv("SWA_TC_VERBOSE"))
-    fprintf(stderr, "[swa2d] fwd plan: tile %dx%d, block %dx%d (N=%d), stages %d, pbufs %d, smem %u, %d items on %u CTAs\n",
-            pl.TH, pl.TW, pl.KR, pl.KW, pl.N, pl.stages, pl.pbufs, pl.smem_bytes, n_items, grid.x);
+    fprintf(stderr, "[swa2d] fwd plan: tile %dx%d, block %dx%d (N=%d), stages %d, tables %u, smem %u, %d items on %u CTAs\n",
+            pl.TH, pl.TW, pl.KR, pl.KW, pl.N, pl.stages, pl.tab_bytes, pl.smem_bytes, n_items, grid.x);
   kern<<<grid, block, pl.smem_bytes, st>>>(tq, tk, tv, p, make_view(o), lse);
   return 0;
 }
@@ -339,8 +282,7 @@ int launch_bwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* 
                const swa_tensor_t* yqk, const swa_tensor_t* yv, const float* lse, const float* delta,
                const swa_tensor_t* out_qk, const swa_tensor_t* out_v, int32_t* status, cudaStream_t st) {
   Plan pl;
-  const bool v2 = !getenv("SWA_TC_BWD1");
-  if (!(v2 ? make_plan2(g, DKDV ? 2 : 1, &pl) : make_plan(g, DKDV ? 2 : 1, &pl))) {
+  if (!make_plan(g, rope, DKDV ? 2 : 1, &pl)) {
     snprintf(g_tc_err, sizeof(g_tc_err), "no tile plan");
     return -1;
   }
@@ -350,19 +292,20 @@ int launch_bwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* 
     return -1;
   const KParams p = make_params(g, rope, pl, status);
   const int sms = sm_count();
-  dim3 grid(pl.n_tiles_x * pl.n_tiles_y, g->B * g->H), block(kBwdThreads);
-  if (v2) {   // persistent: one CTA per SM walks the items
-    grid = dim3(p.n_items < sms ? p.n_items : sms);
-    block = dim3(kBwd2Threads);
-  }
+  dim3 grid(p.n_items < sms ? p.n_items : sms), block(kBwdThreads);   // persistent: one CTA per SM walks the items
   using BwdKernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, KParams, const float*,
                              const float*, View4, View4);
-  static const BwdKernel bwd2_table[2][5] = {
-      {bwd2_kernel<false, DKDV, 0>, bwd2_kernel<false, DKDV, 1>, bwd2_kernel<false, DKDV, 2>, nullptr, bwd2_kernel<false, DKDV, 4>},
-      {bwd2_kernel<true, DKDV, 0>, bwd2_kernel<true, DKDV, 1>, bwd2_kernel<true, DKDV, 2>, nullptr, bwd2_kernel<true, DKDV, 4>}};
+  static const BwdKernel bwd_table[2][2][5] = {
+      {{bwd_kernel<false, DKDV, 0, false>, bwd_kernel<false, DKDV, 1, false>, bwd_kernel<false, DKDV, 2, false>, nullptr,
+        bwd_kernel<false, DKDV, 4, false>},
+       {bwd_kernel<false, DKDV, 0, false>, bwd_kernel<false, DKDV, 1, true>, bwd_kernel<false, DKDV, 2, true>, nullptr,
+        bwd_kernel<false, DKDV, 4, true>}},
+      {{bwd_kernel<true, DKDV, 0, false>, bwd_kernel<true, DKDV, 1, false>, bwd_kernel<true, DKDV, 2, false>, nullptr,
+        bwd_kernel<true, DKDV, 4, false>},
+       {bwd_kernel<true, DKDV, 0, false>, bwd_kernel<true, DKDV, 1, true>, bwd_kernel<true, DKDV, 2, true>, nullptr,
+        bwd_kernel<true, DKDV, 4, true>}}};
   const int ni = (rope && rope->idx) ? rope->n_rdim / 8 : 0;
-  BwdKernel kern = v2 ? bwd2_table[g->dtype == SWA_BF16 ? 1 : 0][ni]
-                      : (g->dtype == SWA_BF16 ? bwd_kernel<true, DKDV> : bwd_kernel<false, DKDV>);
+  BwdKernel kern = bwd_table[g->dtype == SWA_BF16 ? 1 : 0][pl.tab_bytes ? 1 : 0][ni];
   if (kern == nullptr) {
     snprintf(g_tc_err, sizeof(g_tc_err), "n_rdim %d has no tensor-core kernel", rope ? rope->n_rdim : 0);
     return -1;
@@ -373,8 +316,8 @@ int launch_bwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* 
     return -1;
   }
   if (getenv("SWA_TC_VERBOSE"))
-    fprintf(stderr, "[swa2d] %s plan: tile %dx%d, block %dx%d (N=%d), stages %d, pbufs %d, nsb %d, nxb %d, smem %u, grid %ux%u\n",
-            DKDV ? "dkdv" : "dq", pl.TH, pl.TW, pl.KR, pl.KW, pl.N, pl.stages, pl.pbufs, pl.nsb, pl.nxb, pl.smem_bytes, grid.x, grid.y);
+    fprintf(stderr, "[swa2d] %s plan: tile %dx%d, block %dx%d (N=%d), stages %d, nsb %d, nxb %d, tables %u, smem %u, %d items on %u CTAs\n",
+            DKDV ? "dkdv" : "dq", pl.TH, pl.TW, pl.KR, pl.KW, pl.N, pl.stages, pl.nsb, pl.nxb, pl.tab_bytes, pl.smem_bytes, p.n_items, grid.x);
   kern<<<grid, block, pl.smem_bytes, st>>>(mxqk, mxv, myqk, myv, p, lse, delta, make_view(out_qk),
                                           out_v ? make_view(out_v) : View4{nullptr, 0, 0, 0, 0});
   return 0;

@@ -23,14 +23,15 @@ namespace swa {
 namespace tc {
 
 constexpr int kTileTokens = 128;  // rows of the resident tile = MMA M
-constexpr int kMaxStages = 4;
+constexpr int kMaxStages = 8;   // depth limit of the streamed-block ring
 
 struct Plan {
   int TH, TW;          // resident tile: rows x token columns (TH*TW == 128)
   int KR, KW, N;       // streamed block: rows x token columns, N = KR*KW
   int n_tiles_x, n_tiles_y;
-  int stages, pbufs;   // streamed-block pipeline depth, buffers for the P/dS operand
+  int stages;          // streamed-block pipeline depth
   int nsb, nxb;        // backward: (S, dP) buffer pairs in tensor memory, resident-tile buffers in shared memory
+  uint32_t tab_bytes;  // cos/sin tables staged in shared memory (0: read from global memory)
   uint32_t smem_bytes;
 };
 
@@ -73,43 +74,6 @@ __device__ __forceinline__ int item_blocks(const KParams& p, int item, int tiles
   const int tile = item % tiles_per_head, ty = tile / p.pl.n_tiles_x, r0 = ty * p.pl.TH;
   const int first = max(r0 - p.wr, 0), last = min(r0 + p.pl.TH - 1 + p.wr, p.t_h - 1);
   return (last - first + p.pl.KR) / p.pl.KR;
-}
-
-// Bit jc of the result: halo column jc (token column hx0+jc) is inside the grid and
-// within wc tile columns of token column `x`.  Zero when `x` itself is outside.
-__device__ __forceinline__ uint64_t column_mask(const KParams& p, int hx0, int x, bool row_in_grid) {
-  if (!row_in_grid || x >= p.Wtok) return 0ull;
-  const int c = x / p.b;
-  const int lo = max(0, (c - p.wc) * p.b) - hx0;
-  const int hi = min(p.Wtok, (c + p.wc + 1) * p.b) - hx0;  // exclusive
-  const int n = hi - lo;
-  if (n <= 0) return 0ull;
-  const uint64_t ones = n >= 64 ? ~0ull : ((1ull << n) - 1ull);
-  return ones << lo;
-}
-
-// vm (128 bits) |= colmask << shift, 0 <= shift < 128, with static word indexing.
-__device__ __forceinline__ void or_shifted(uint32_t (&vm)[4], uint64_t colmask, int shift) {
-#pragma unroll
-  for (int w = 0; w < 4; ++w) {
-    const int rel = 32 * w - shift;  // bit `rel` of colmask lands on bit 0 of word w
-    uint32_t part;
-    if (rel >= 64 || rel <= -32) part = 0u;
-    else if (rel >= 0) part = (uint32_t)(colmask >> rel);
-    else part = (uint32_t)(colmask << (-rel));
-    vm[w] |= part;
-  }
-}
-
-// Validity bits of the N = KR*KW entries of one streamed block for the resident token
-// at row `r` (column validity precomputed in colmask): entry j = jr*KW + jc.
-__device__ __forceinline__ void block_mask(uint32_t (&vm)[4], const KParams& p, uint64_t colmask, int brow0, int r,
-                                           int hr_last) {
-  vm[0] = vm[1] = vm[2] = vm[3] = 0u;
-  for (int jr = 0; jr < p.pl.KR; ++jr) {
-    const int kr = brow0 + jr;
-    if (kr <= hr_last && kr - r <= p.wr && r - kr <= p.wr) or_shifted(vm, colmask, jr * p.pl.KW);
-  }
 }
 
 template <bool BF16>
@@ -253,7 +217,7 @@ struct RopeParts {
   bool active;
 };
 
-// The same for `nthreads` threads: the first nthreads - rows rows are split between two threads
+// Share of thread t of `nthreads`: the first nthreads - rows rows are split between two threads
 // (thread t: row-angle half of row t; thread rows + t: column-angle half), the others are whole.
 __device__ __forceinline__ RopeParts rope_parts_n(int t, int rows, int nthreads) {
   RopeParts r;
@@ -267,21 +231,6 @@ __device__ __forceinline__ RopeParts rope_parts_n(int t, int rows, int nthreads)
     r.row = t - rows;
     r.active = r.row < split;
     r.lo = r.hi = 1;
-  }
-  return r;
-}
-
-__device__ __forceinline__ RopeParts rope_parts(int t, int rows) {
-  RopeParts r;
-  if (2 * rows <= 128) {
-    r.active = t < 2 * rows;
-    r.lo = r.hi = t >= rows ? 1 : 0;
-    r.row = t - r.lo * rows;
-  } else {
-    r.active = t < rows;
-    r.lo = 0;
-    r.hi = 1;
-    r.row = t;
   }
   return r;
 }
@@ -301,21 +250,6 @@ __device__ __forceinline__ void rope_fetch_n(RopeRow& c, const RopeParts& pt, co
 #pragma unroll
     for (int i = 0; i < NI * 4; ++i) c.cs[(NI * 4 + i) & 15] = __ldg(t4 + i);
   }
-}
-
-// Start fetching the cos/sin rows of the token with packed index `packed` (-1: nothing to do).
-__device__ __forceinline__ void rope_fetch(RopeRow& c, int32_t packed, const RopeParts& pt, const RopeDev& rp) {
-  decode_idx(packed, rp.max_h, rp.max_w, c.pos[0], c.pos[1]);
-#ifdef SWA_ROPE_ONLY_R
-  rope_fetch_n<SWA_ROPE_ONLY_R / 8>(c, pt, rp);
-#else
-  switch (rp.R) {
-    case 8: rope_fetch_n<1>(c, pt, rp); break;
-    case 16: rope_fetch_n<2>(c, pt, rp); break;
-    case 32: rope_fetch_n<4>(c, pt, rp); break;
-    default: c.pos[0] = c.pos[1] = -1; break;
-  }
-#endif
 }
 
 // Rotate one half (0 = row-angle pairs, 1 = column-angle pairs) of a row with NI*4 float4 of (cos, sin).
@@ -366,24 +300,10 @@ __device__ __forceinline__ void rope_apply_n(uint8_t* tile, uint32_t chunk_strid
   }
 }
 
-// Rotate this thread's share of the tile with the values fetched by rope_fetch.
-template <bool BF16>
-__device__ __forceinline__ void rope_apply(uint8_t* tile, uint32_t chunk_stride, RopeRow& c, const RopeParts& pt,
-                                           const RopeDev& rp) {
-#ifdef SWA_ROPE_ONLY_R
-  rope_apply_n<BF16, SWA_ROPE_ONLY_R / 8>(tile, chunk_stride, c, pt, rp);
-#else
-  switch (rp.R) {
-    case 8: rope_apply_n<BF16, 1>(tile, chunk_stride, c, pt, rp); break;
-    case 16: rope_apply_n<BF16, 2>(tile, chunk_stride, c, pt, rp); break;
-    case 32: rope_apply_n<BF16, 4>(tile, chunk_stride, c, pt, rp); break;
-    default: break;
-  }
-#endif
-}
-
-// The same with the table width fixed at compile time (NI = n_rdim / 8; 0 = no rotation): a kernel
-// instantiated for one width carries one copy of the rotation code instead of three.
+// Entry points with the table width fixed at compile time (NI = n_rdim / 8; 0 = no rotation): a
+// kernel instantiated for one width carries one copy of the rotation code instead of three.
+// rope_fetch_t starts fetching the cos/sin rows of the token with packed index `packed` (-1: nothing
+// to do), rope_apply_t rotates this thread's share of the tile with the fetched values.
 template <int NI>
 __device__ __forceinline__ void rope_fetch_t(RopeRow& c, int32_t packed, const RopeParts& pt, const RopeDev& rp) {
   if constexpr (NI > 0) {
@@ -395,6 +315,67 @@ template <bool BF16, int NI>
 __device__ __forceinline__ void rope_apply_t(uint8_t* tile, uint32_t chunk_stride, RopeRow& c, const RopeParts& pt,
                                              const RopeDev& rp) {
   if constexpr (NI > 0) rope_apply_n<BF16, NI>(tile, chunk_stride, c, pt, rp);
+}
+
+// ---- the same rotation with the cos/sin tables staged in shared memory ------------------------
+// When both tables fit ((max_h + max_w) * n_rdim * 8 bytes), a persistent CTA copies them into
+// shared memory once; a rotating thread then reads its (cos, sin) values with shared-memory
+// latency, no register cache and no look-ahead are needed, and the rotation code shrinks to one
+// loop over the (at most two) halves of a row.
+struct RopeTabs {
+  uint32_t row_addr, col_addr;   // shared-space byte addresses of the row / column table
+};
+
+__device__ __forceinline__ void stage_rope_tables(uint8_t* dst, const RopeDev& rp, int tid, int nthreads) {
+  const int n_row = rp.max_h * rp.R / 2, n_col = rp.max_w * rp.R / 2;   // float4 = two (cos, sin) pairs
+  const float4* src_r = reinterpret_cast<const float4*>(rp.row_cs);
+  const float4* src_c = reinterpret_cast<const float4*>(rp.col_cs);
+  float4* d = reinterpret_cast<float4*>(dst);
+#pragma unroll 1
+  for (int i = tid; i < n_row; i += nthreads) d[i] = __ldg(src_r + i);
+#pragma unroll 1
+  for (int i = tid; i < n_col; i += nthreads) d[n_row + i] = __ldg(src_c + i);
+}
+
+template <bool BF16, int NI>
+__device__ __forceinline__ void rope_apply_s(uint8_t* tile, uint32_t chunk_stride, int32_t packed, const RopeParts& pt,
+                                             const RopeDev& rp, const RopeTabs& tabs) {
+  if constexpr (NI > 0) {
+    constexpr int R = 8 * NI;
+    int pos[2];
+    decode_idx(packed, rp.max_h, rp.max_w, pos[0], pos[1]);
+#pragma unroll 1
+    for (int half = pt.lo; half <= pt.hi; ++half) {
+      const int ps = half ? pos[1] : pos[0];
+      if (ps < 0) continue;
+      const uint32_t cs_addr = (half ? tabs.col_addr : tabs.row_addr) + (uint32_t)ps * (R * 8);
+      uint32_t a0[NI], a1[NI];
+      uint4 va[NI], vb[NI];
+#pragma unroll
+      for (int i = 0; i < NI; ++i) {  // all loads first
+        const int d0 = 2 * half * R + i * 8, d1 = d0 + R;
+        a0[i] = ptx::smem_u32(swz(tile + (d0 >> 6) * chunk_stride, pt.row, (d0 & 63) >> 3));
+        a1[i] = ptx::smem_u32(swz(tile + (d1 >> 6) * chunk_stride, pt.row, (d1 & 63) >> 3));
+        va[i] = ptx::lds128(a0[i]);
+        vb[i] = ptx::lds128(a1[i]);
+      }
+#pragma unroll
+      for (int i = 0; i < NI; ++i) {
+        uint32_t* pa = reinterpret_cast<uint32_t*>(&va[i]);
+        uint32_t* pb = reinterpret_cast<uint32_t*>(&vb[i]);
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+          const uint4 cu = ptx::lds128(cs_addr + (i * 4 + h) * 16);   // (cos, sin) of pairs 2h and 2h+1
+          const float cx = __uint_as_float(cu.x), cy = __uint_as_float(cu.y), cz = __uint_as_float(cu.z), cw = __uint_as_float(cu.w);
+          const float2 x0 = unpack2<BF16>(pa[h]), x1 = unpack2<BF16>(pb[h]);
+          pa[h] = pack2<BF16>(x0.x * cx - x1.x * cy, x0.y * cz - x1.y * cw);
+          pb[h] = pack2<BF16>(x0.x * cy + x1.x * cx, x0.y * cw + x1.y * cz);
+        }
+        ptx::sts128(a0[i], pa[0], pa[1], pa[2], pa[3]);
+        ptx::sts128(a1[i], pb[0], pb[1], pb[2], pb[3]);
+      }
+    }
+  }
 }
 
 // Performance tracing of one CTA: role `role` stores its k-th clock sample.
