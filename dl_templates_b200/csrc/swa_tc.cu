@@ -156,16 +156,24 @@ bool make_plan_shape(const swa_geom_t* g, int which, int TH, int TW, uint32_t ta
 // Bytes of the cos/sin tables when they are small enough to be staged in shared memory, else 0.
 uint32_t rope_table_bytes(const swa_rope_t* rope) {
   if (!rope || !rope->idx) return 0;
-  const uint64_t b = (uint64_t)(rope->max_h + rope->max_w) * rope->n_rdim * 8;
+  const uint64_t b = (uint64_t)(rope->max_h + rope->max_w) * rope_tab_stride(rope->n_rdim);
   return b <= 48 * 1024 && !getenv("SWA_TC_NO_TABS") ? (uint32_t)((b + 15) & ~15ull) : 0;
 }
 
 bool make_plan(const swa_geom_t* g, const swa_rope_t* rope, int which, Plan* out) {
-  const int th = env_int("SWA_TC_TH", 0);
+  const char* th_names[3] = {"SWA_TC_TH_FWD", "SWA_TC_TH_DQ", "SWA_TC_TH_DKDV"};
+  const int th = env_int(th_names[which], env_int("SWA_TC_TH", 0));
   for (uint32_t tab = rope_table_bytes(rope);; tab = 0) {   // with the staged tables if a plan fits, else without
     if (th == 8) { if (make_plan_shape(g, which, 8, 16, tab, out)) return true; }
     else if (th == 16) { if (make_plan_shape(g, which, 16, 8, tab, out)) return true; }
-    else if (make_plan_shape(g, which, 16, 8, tab, out) || make_plan_shape(g, which, 8, 16, tab, out)) return true;
+    else {
+      // measured at the 13 x 13 window: with fused RoPE 16 x 8 wins (80-token blocks, every block row shared by
+      // two rotating threads), without it 8 x 16 wins for the forward and dQ kernels (fewer, wider blocks)
+      const bool wide_first = which != 2 && !(rope && rope->idx);
+      if (wide_first ? (make_plan_shape(g, which, 8, 16, tab, out) || make_plan_shape(g, which, 16, 8, tab, out))
+                     : (make_plan_shape(g, which, 16, 8, tab, out) || make_plan_shape(g, which, 8, 16, tab, out)))
+        return true;
+    }
     if (tab == 0) return false;
   }
 }

@@ -499,7 +499,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ C
     rc.pos[0] = rc.pos[1] = -1;
     RopeTabs tabs;
     tabs.row_addr = smem_u32(tab_smem);
-    tabs.col_addr = tabs.row_addr + (uint32_t)(p.rope.max_h * p.rope.R * 8);
+    tabs.col_addr = tabs.row_addr + (uint32_t)p.rope.max_h * rope_tab_stride(p.rope.R);
     float nlse_cur = -INFINITY, delta_cur = 0.f;       // lse / delta of this thread's row of the current unit
 #pragma unroll 1
     for (int it = 0, item = blockIdx.x; item < n_items; ++it, item += gridDim.x) {

@@ -322,19 +322,29 @@ __device__ __forceinline__ void rope_apply_t(uint8_t* tile, uint32_t chunk_strid
 // shared memory once; a rotating thread then reads its (cos, sin) values with shared-memory
 // latency, no register cache and no look-ahead are needed, and the rotation code shrinks to one
 // loop over the (at most two) halves of a row.
+// A staged table row takes n_rdim*8 + 16 bytes: the threads of a warp read the rows of neighbouring
+// positions with 16-byte loads, and the 16 bytes of padding spread them over the banks.
 struct RopeTabs {
   uint32_t row_addr, col_addr;   // shared-space byte addresses of the row / column table
 };
+__host__ __device__ __forceinline__ uint32_t rope_tab_stride(int n_rdim) { return (uint32_t)n_rdim * 8u + 16u; }
 
 __device__ __forceinline__ void stage_rope_tables(uint8_t* dst, const RopeDev& rp, int tid, int nthreads) {
-  const int n_row = rp.max_h * rp.R / 2, n_col = rp.max_w * rp.R / 2;   // float4 = two (cos, sin) pairs
+  const int per_row = rp.R / 2;                                         // float4 = two (cos, sin) pairs
+  const uint32_t stride = rope_tab_stride(rp.R);
   const float4* src_r = reinterpret_cast<const float4*>(rp.row_cs);
   const float4* src_c = reinterpret_cast<const float4*>(rp.col_cs);
-  float4* d = reinterpret_cast<float4*>(dst);
+  uint8_t* dst_c = dst + (size_t)rp.max_h * stride;
 #pragma unroll 1
-  for (int i = tid; i < n_row; i += nthreads) d[i] = __ldg(src_r + i);
+  for (int i = tid; i < rp.max_h * per_row; i += nthreads) {
+    const int r = i / per_row, c = i - r * per_row;
+    *reinterpret_cast<float4*>(dst + (size_t)r * stride + c * 16) = __ldg(src_r + i);
+  }
 #pragma unroll 1
-  for (int i = tid; i < n_col; i += nthreads) d[n_row + i] = __ldg(src_c + i);
+  for (int i = tid; i < rp.max_w * per_row; i += nthreads) {
+    const int r = i / per_row, c = i - r * per_row;
+    *reinterpret_cast<float4*>(dst_c + (size_t)r * stride + c * 16) = __ldg(src_c + i);
+  }
 }
 
 template <bool BF16, int NI>
@@ -348,7 +358,7 @@ __device__ __forceinline__ void rope_apply_s(uint8_t* tile, uint32_t chunk_strid
     for (int half = pt.lo; half <= pt.hi; ++half) {
       const int ps = half ? pos[1] : pos[0];
       if (ps < 0) continue;
-      const uint32_t cs_addr = (half ? tabs.col_addr : tabs.row_addr) + (uint32_t)ps * (R * 8);
+      const uint32_t cs_addr = (half ? tabs.col_addr : tabs.row_addr) + (uint32_t)ps * rope_tab_stride(R);
       uint32_t a0[NI], a1[NI];
       uint4 va[NI], vb[NI];
 #pragma unroll
