@@ -138,6 +138,222 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ C
   };
   const int n_items = p.n_items, tiles_per_head = pl.n_tiles_x * pl.n_tiles_y;
 
+  // Registers follow the work: the kernel starts with 128 per thread; the producer / issuer / RoPE
+  // warpgroups (warps 0-3 and 12-15) give some back, the two compute warpgroups take them.
+  // (2 * 104 + 2 * 152) * 128 = 64 Ki.  Each setmaxnreg is the first instruction of its branch, so that the
+  // whole branch is compiled for that budget.
+  if (warp >= 4 && warp < 12) {
+    setmaxnreg_inc<152>();
+    // ------------------------------------------------------------------ P / dS, one thread per resident row and group
+    const int lane = threadIdx.x & 31;
+    const int g = (warp - 4) >> 2;
+    const int quarter = warp & 3;
+    const int m = quarter * 32 + lane;
+    const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
+    const float c2 = p.scale_log2;
+    const int ng = N >> 4;
+    uint32_t gbase = 0, own_next = g;
+    // this group's next block: buffer pair, its parity, stage of the ring and its parity
+    // (two pairs: group g owns pair g, every block flips its parity; one pair: both groups alternate
+    // on it, so the blocks of group g always wait for parity g)
+    int buf = nsb == 2 ? g : 0, buf_par = nsb == 2 ? 0 : g;
+    int stage = g % pl.stages, stage_par = (g / pl.stages) & 1;
+    using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+    // (cos, sin) of NP consecutive pairs starting at pair `first` of table row `pos` (row or column table):
+    // from the staged tables in shared memory when there are any, else from global memory; identity for pos < 0
+    const uint32_t tab_row_addr = smem_u32(tab_smem), tab_col_addr = tab_row_addr + (uint32_t)p.rope.max_h * rope_tab_stride(Rd);
+    auto load_pairs = [&](float2* cs, bool col, int pos, int first) {
+      constexpr int NP = R >= 16 ? 16 : 8;
+      if (pos < 0) {
+#pragma unroll
+        for (int e = 0; e < NP; ++e) cs[e] = make_float2(1.f, 0.f);
+      } else if constexpr (TABS) {
+        const uint32_t a = (col ? tab_col_addr : tab_row_addr) + (uint32_t)pos * rope_tab_stride(Rd) + first * 8;
+#pragma unroll
+        for (int e = 0; e < NP; e += 2) {
+          const uint4 u = lds128(a + e * 8);
+          cs[e] = make_float2(__uint_as_float(u.x), __uint_as_float(u.y));
+          cs[e + 1] = make_float2(__uint_as_float(u.z), __uint_as_float(u.w));
+        }
+      } else {
+        const float2* trow = reinterpret_cast<const float2*>((col ? p.rope.col_cs : p.rope.row_cs) + (int64_t)pos * Rd * 2) + first;
+#pragma unroll
+        for (int e = 0; e < NP; ++e) cs[e] = __ldg(trow + e);
+      }
+    };
+#pragma unroll 1
+    for (int it = 0, item = blockIdx.x; item < n_items; ++it, item += gridDim.x) {
+      const int bh = item / tiles_per_head, bi = bh / p.H, hi = bh - bi * p.H;
+      const TilePos tp = tile_pos(p, item - bh * tiles_per_head);
+      const int tr = tp.r0 + m / pl.TW, tx = tp.x0 + m % pl.TW;
+      const bool t_in = tr < p.t_h && tx < p.Wtok;
+      const int64_t tok = (int64_t)tr * p.Wtok + tx;
+      const int64_t vec_base = (int64_t)bh * p.t_h * p.Wtok;
+      const int see_lo = tp.r0 + (quarter * 32) / pl.TW - p.wr, see_hi = tp.r0 + (quarter * 32 + 31) / pl.TW + p.wr;
+      float my_nlse = -INFINITY, my_delta = 0.f;     // dQ: -lse and delta of this thread's query
+      if (!DKDV && t_in) {
+        my_nlse = -__ldg(lse + vec_base + tok);
+        my_delta = __ldg(delta + vec_base + tok);
+      }
+#pragma unroll 1
+      for (int j = (int)(own_next - gbase); j < tp.nblk; j += 2, own_next += 2) {
+        const uint32_t s_tm = lane_base + buf * 2 * N, d_tm = s_tm + N;
+        uint64_t* const ds_bar = &sh->ds_full[buf];
+        wait_spin(&sh->sd_full[buf], buf_par, 7);
+        if (m == 0 && g == 0 && it == p.trace_it) trace_mark(p, 2, 1 + 2 * (j >> 1));
+        const float* vec = vec_smem + stage * 256;
+        if (DKDV) wait_spin(&sh->y_ready[stage], stage_par, 8);   // -lse / delta of the block's queries are staged
+        // advance by two positions in the rings
+        if (nsb == 2) buf_par ^= 1;
+        stage += 2;
+        if (stage >= pl.stages) { stage -= pl.stages; stage_par ^= 1; }
+        const int blk_first = tp.hr_first + j * pl.KR, blk_last = blk_first + pl.KR - 1;
+        const bool seen = !(blk_last < see_lo || blk_first > see_hi);
+        if (!ok) continue;
+        tc_fence_after();
+        uint32_t sa[16], sb[16], da[16], db[16];
+        if (!seen) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) sa[i] = 0u;
+#pragma unroll 1
+          for (int c0 = 0; c0 < (N >> 1); c0 += 8) {
+            tmem_st8(s_tm + c0, sa);
+            if (DKDV) tmem_st8(d_tm + c0, sa);
+          }
+        } else {
+          // 16 columns at a time, the loads of the next 16 in flight while these are worked on
+          auto work = [&](int i, uint32_t* s, uint32_t* d) {
+            uint32_t wp[8];
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              float nl[4], dl[4];
+              if constexpr (DKDV) {
+                const float4 a = *reinterpret_cast<const float4*>(vec + 16 * i + 4 * q4);
+                const float4 b = *reinterpret_cast<const float4*>(vec + 128 + 16 * i + 4 * q4);
+                nl[0] = a.x; nl[1] = a.y; nl[2] = a.z; nl[3] = a.w;
+                dl[0] = b.x; dl[1] = b.y; dl[2] = b.z; dl[3] = b.w;
+              } else {
+                nl[0] = nl[1] = nl[2] = nl[3] = my_nlse;
+                dl[0] = dl[1] = dl[2] = dl[3] = my_delta;
+              }
+              float pv[4], dsv[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                pv[e] = exp2f(fmaf(__uint_as_float(s[4 * q4 + e]), c2, nl[e]));
+                dsv[e] = pv[e] * (__uint_as_float(d[4 * q4 + e]) - dl[e]);
+              }
+              s[2 * q4] = pack2<BF16>(dsv[0], dsv[1]);
+              s[2 * q4 + 1] = pack2<BF16>(dsv[2], dsv[3]);
+              if constexpr (DKDV) {
+                wp[2 * q4] = pack2<BF16>(pv[0], pv[1]);
+                wp[2 * q4 + 1] = pack2<BF16>(pv[2], pv[3]);
+              }
+            }
+            if constexpr (DKDV) {
+              tmem_st8(s_tm + 8 * i, wp);      // P^T over S^T
+              tmem_st8(d_tm + 8 * i, s);       // dS^T over dP^T
+            } else {
+              tmem_st8(s_tm + 8 * i, s);       // dS over S
+            }
+          };
+          tmem_ld16(s_tm, sa);
+          tmem_ld16(d_tm, da);
+#pragma unroll 1
+          for (int i = 0; i < ng; i += 2) {
+            tmem_wait_ld();
+            if (i + 1 < ng) { tmem_ld16(s_tm + 16 * (i + 1), sb); tmem_ld16(d_tm + 16 * (i + 1), db); }
+            work(i, sa, da);
+            if (i + 1 < ng) {
+              tmem_wait_ld();
+              if (i + 2 < ng) { tmem_ld16(s_tm + 16 * (i + 2), sa); tmem_ld16(d_tm + 16 * (i + 2), da); }
+              work(i + 1, sb, db);
+            }
+          }
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(ds_bar);
+        if (m == 0 && g == 0 && it == p.trace_it) trace_mark(p, 2, 2 + 2 * (j >> 1));
+      }
+      // ---- the item ends: this group stores its half of the accumulator row(s)
+      // dQ / dK: columns [g W, g W + W), W = 32 qch; the partner of a rotated dim lies in the same half
+      // Control flow below is warp-uniform (the tensor-memory loads are warp-collective): whether a
+      // granule is rotated depends only on its dims; a thread whose token is outside the grid or has a
+      // negative index half rotates by the identity.
+      const bool rope_on = NI > 0 && p.rope.idx != nullptr;
+      int irow = -1, icol = -1;
+      if (rope_on && t_in) decode_idx(__ldg(p.rope.idx + tok), p.rope.max_h, p.rope.max_w, irow, icol);
+      const int W = 32 * p.qch, base = g * W;
+      // cos/sin of the first rotated pairs of this thread, fetched before the wait (served by L2)
+      float2 cs[16];
+      int pre_d0 = -1;                                // first dim of the granule(s) the prefetched pairs belong to
+      if constexpr (NI > 0) {
+        if (rope_on && base < 4 * R && ((base / Rd) & 1) == 0) {
+          pre_d0 = base;
+          const int seg = base / Rd;
+          load_pairs(cs, seg >= 2, seg >= 2 ? icol : irow, base - seg * R);
+        }
+      }
+      if (m == 0 && g == 0 && it == p.trace_it) trace_mark(p, 2, 29);
+      wait_spin(&sh->acc_full, it & 1, 9);
+      if (ok) {
+        tc_fence_after();
+        if (m == 0 && g == 0 && it == p.trace_it) trace_mark(p, 2, 30);
+        T* qk_row = (T*)out_qk.ptr + bi * out_qk.s0 + hi * out_qk.s1 + tok * out_qk.s2;
+        const uint32_t aqk = lane_base + acc_qk;
+        const float scale = p.sm_scale;
+#pragma unroll 1
+        for (int d0 = base; d0 < base + W; d0 += 16) {
+          const bool roped = NI > 0 && rope_on && d0 < 4 * R;   // warp-uniform
+          if (roped && R >= 16 && ((d0 / Rd) & 1) == 1) continue;        // stored together with its partner granule
+          uint32_t ra[16], rb[16];
+          float va[16], vb[16];
+          tmem_ld16(aqk + d0, ra);
+          if (roped && R >= 16) tmem_ld16(aqk + d0 + R, rb);
+          tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 16; ++e) va[e] = __uint_as_float(ra[e]) * scale;
+          if constexpr (NI > 0) {
+            if (roped) {
+              if (d0 != pre_d0) {                                         // pairs that were not prefetched
+                const int seg = d0 / Rd;
+                load_pairs(cs, seg >= 2, seg >= 2 ? icol : irow, d0 - seg * R);
+              }
+              if constexpr (R >= 16) {
+#pragma unroll
+                for (int e = 0; e < 16; ++e) vb[e] = __uint_as_float(rb[e]) * scale;
+                inv_rotate_pairs<16>(va, vb, cs);
+                if (t_in) store16<BF16>(qk_row + d0 + R, vb);
+              } else {
+                inv_rotate_pairs<8>(va, va + 8, cs);
+              }
+            }
+          }
+          if (t_in) store16<BF16>(qk_row + d0, va);
+        }
+        if constexpr (DKDV) {
+          T* v_row = (T*)out_v.ptr + bi * out_v.s0 + hi * out_v.s1 + tok * out_v.s2;
+          const uint32_t av = lane_base + acc_v;
+          const int Wv = 32 * p.vch;
+#pragma unroll 1
+          for (int d0 = g * Wv; d0 < g * Wv + Wv; d0 += 16) {
+            uint32_t ra[16];
+            float va[16];
+            tmem_ld16(av + d0, ra);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 16; ++e) va[e] = __uint_as_float(ra[e]);
+            if (t_in) store16<BF16>(v_row + d0, va);
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(&sh->acc_free);
+        if (m == 0 && g == 0 && it == p.trace_it) trace_mark(p, 2, 31);
+      }
+      gbase += tp.nblk;
+    }
+  } else {
+    setmaxnreg_dec<104>();
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (elect_one()) {
@@ -292,199 +508,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ C
         lead = 0;
       }
     }
-  } else if (warp >= 4 && warp < 12) {
-    // ------------------------------------------------------------------ P / dS, one thread per resident row and group
-    const int lane = threadIdx.x & 31;
-    const int g = (warp - 4) >> 2;
-    const int quarter = warp & 3;
-    const int m = quarter * 32 + lane;
-    const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
-    const float c2 = p.scale_log2;
-    const int ng = N >> 4;
-    uint32_t gbase = 0, own_next = g;
-    // this group's next block: buffer pair, its parity, stage of the ring and its parity
-    // (two pairs: group g owns pair g, every block flips its parity; one pair: both groups alternate
-    // on it, so the blocks of group g always wait for parity g)
-    int buf = nsb == 2 ? g : 0, buf_par = nsb == 2 ? 0 : g;
-    int stage = g % pl.stages, stage_par = (g / pl.stages) & 1;
-    using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
-#pragma unroll 1
-    for (int it = 0, item = blockIdx.x; item < n_items; ++it, item += gridDim.x) {
-      const int bh = item / tiles_per_head, bi = bh / p.H, hi = bh - bi * p.H;
-      const TilePos tp = tile_pos(p, item - bh * tiles_per_head);
-      const int tr = tp.r0 + m / pl.TW, tx = tp.x0 + m % pl.TW;
-      const bool t_in = tr < p.t_h && tx < p.Wtok;
-      const int64_t tok = (int64_t)tr * p.Wtok + tx;
-      const int64_t vec_base = (int64_t)bh * p.t_h * p.Wtok;
-      const int see_lo = tp.r0 + (quarter * 32) / pl.TW - p.wr, see_hi = tp.r0 + (quarter * 32 + 31) / pl.TW + p.wr;
-      float my_nlse = -INFINITY, my_delta = 0.f;     // dQ: -lse and delta of this thread's query
-      if (!DKDV && t_in) {
-        my_nlse = -__ldg(lse + vec_base + tok);
-        my_delta = __ldg(delta + vec_base + tok);
-      }
-#pragma unroll 1
-      for (int j = (int)(own_next - gbase); j < tp.nblk; j += 2, own_next += 2) {
-        const uint32_t s_tm = lane_base + buf * 2 * N, d_tm = s_tm + N;
-        uint64_t* const ds_bar = &sh->ds_full[buf];
-        wait_spin(&sh->sd_full[buf], buf_par, 7);
-        if (m == 0 && g == 0 && it == p.trace_it) trace_mark(p, 2, 1 + 2 * (j >> 1));
-        const float* vec = vec_smem + stage * 256;
-        if (DKDV) wait_spin(&sh->y_ready[stage], stage_par, 8);   // -lse / delta of the block's queries are staged
-        // advance by two positions in the rings
-        if (nsb == 2) buf_par ^= 1;
-        stage += 2;
-        if (stage >= pl.stages) { stage -= pl.stages; stage_par ^= 1; }
-        const int blk_first = tp.hr_first + j * pl.KR, blk_last = blk_first + pl.KR - 1;
-        const bool seen = !(blk_last < see_lo || blk_first > see_hi);
-        if (!ok) continue;
-        tc_fence_after();
-        uint32_t sa[16], sb[16], da[16], db[16];
-        if (!seen) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) sa[i] = 0u;
-#pragma unroll 1
-          for (int c0 = 0; c0 < (N >> 1); c0 += 8) {
-            tmem_st8(s_tm + c0, sa);
-            if (DKDV) tmem_st8(d_tm + c0, sa);
-          }
-        } else {
-          // 16 columns at a time, the loads of the next 16 in flight while these are worked on
-          auto work = [&](int i, uint32_t* s, uint32_t* d) {
-            uint32_t wp[8];
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-              float nl[4], dl[4];
-              if constexpr (DKDV) {
-                const float4 a = *reinterpret_cast<const float4*>(vec + 16 * i + 4 * q4);
-                const float4 b = *reinterpret_cast<const float4*>(vec + 128 + 16 * i + 4 * q4);
-                nl[0] = a.x; nl[1] = a.y; nl[2] = a.z; nl[3] = a.w;
-                dl[0] = b.x; dl[1] = b.y; dl[2] = b.z; dl[3] = b.w;
-              } else {
-                nl[0] = nl[1] = nl[2] = nl[3] = my_nlse;
-                dl[0] = dl[1] = dl[2] = dl[3] = my_delta;
-              }
-              float pv[4], dsv[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                pv[e] = exp2f(fmaf(__uint_as_float(s[4 * q4 + e]), c2, nl[e]));
-                dsv[e] = pv[e] * (__uint_as_float(d[4 * q4 + e]) - dl[e]);
-              }
-              s[2 * q4] = pack2<BF16>(dsv[0], dsv[1]);
-              s[2 * q4 + 1] = pack2<BF16>(dsv[2], dsv[3]);
-              if constexpr (DKDV) {
-                wp[2 * q4] = pack2<BF16>(pv[0], pv[1]);
-                wp[2 * q4 + 1] = pack2<BF16>(pv[2], pv[3]);
-              }
-            }
-            if constexpr (DKDV) {
-              tmem_st8(s_tm + 8 * i, wp);      // P^T over S^T
-              tmem_st8(d_tm + 8 * i, s);       // dS^T over dP^T
-            } else {
-              tmem_st8(s_tm + 8 * i, s);       // dS over S
-            }
-          };
-          tmem_ld16(s_tm, sa);
-          tmem_ld16(d_tm, da);
-#pragma unroll 1
-          for (int i = 0; i < ng; i += 2) {
-            tmem_wait_ld();
-            if (i + 1 < ng) { tmem_ld16(s_tm + 16 * (i + 1), sb); tmem_ld16(d_tm + 16 * (i + 1), db); }
-            work(i, sa, da);
-            if (i + 1 < ng) {
-              tmem_wait_ld();
-              if (i + 2 < ng) { tmem_ld16(s_tm + 16 * (i + 2), sa); tmem_ld16(d_tm + 16 * (i + 2), da); }
-              work(i + 1, sb, db);
-            }
-          }
-        }
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(ds_bar);
-        if (m == 0 && g == 0 && it == p.trace_it) trace_mark(p, 2, 2 + 2 * (j >> 1));
-      }
-      // ---- the item ends: this group stores its half of the accumulator row(s)
-      // dQ / dK: columns [g W, g W + W), W = 32 qch; the partner of a rotated dim lies in the same half
-      // Control flow below is warp-uniform (the tensor-memory loads are warp-collective): whether a
-      // granule is rotated depends only on its dims; a thread whose token is outside the grid or has a
-      // negative index half rotates by the identity.
-      const bool rope_on = NI > 0 && p.rope.idx != nullptr;
-      int irow = -1, icol = -1;
-      if (rope_on && t_in) decode_idx(__ldg(p.rope.idx + tok), p.rope.max_h, p.rope.max_w, irow, icol);
-      const int W = 32 * p.qch, base = g * W;
-      // cos/sin of the first rotated pairs of this thread, fetched before the wait (served by L2)
-      float2 cs[16];
-      int pre_d0 = -1;                                // first dim of the granule(s) the prefetched pairs belong to
-      if constexpr (NI > 0) {
-        if (rope_on && base < 4 * R && ((base / Rd) & 1) == 0) {
-          pre_d0 = base;
-          const int seg = base / Rd, pos = seg >= 2 ? icol : irow;
-          const float2* trow = reinterpret_cast<const float2*>((seg >= 2 ? p.rope.col_cs : p.rope.row_cs) + (int64_t)max(pos, 0) * R * 2) + (base - seg * R);
-          constexpr int NPRE = R >= 16 ? 16 : 8;
-#pragma unroll
-          for (int e = 0; e < NPRE; ++e) cs[e] = pos >= 0 ? __ldg(trow + e) : make_float2(1.f, 0.f);
-        }
-      }
-      if (m == 0 && g == 0 && it == p.trace_it) trace_mark(p, 2, 29);
-      wait_spin(&sh->acc_full, it & 1, 9);
-      if (ok) {
-        tc_fence_after();
-        if (m == 0 && g == 0 && it == p.trace_it) trace_mark(p, 2, 30);
-        T* qk_row = (T*)out_qk.ptr + bi * out_qk.s0 + hi * out_qk.s1 + tok * out_qk.s2;
-        const uint32_t aqk = lane_base + acc_qk;
-        const float scale = p.sm_scale;
-#pragma unroll 1
-        for (int d0 = base; d0 < base + W; d0 += 16) {
-          const bool roped = NI > 0 && rope_on && d0 < 4 * R;   // warp-uniform
-          if (roped && R >= 16 && ((d0 / Rd) & 1) == 1) continue;        // stored together with its partner granule
-          uint32_t ra[16], rb[16];
-          float va[16], vb[16];
-          tmem_ld16(aqk + d0, ra);
-          if (roped && R >= 16) tmem_ld16(aqk + d0 + R, rb);
-          tmem_wait_ld();
-#pragma unroll
-          for (int e = 0; e < 16; ++e) va[e] = __uint_as_float(ra[e]) * scale;
-          if constexpr (NI > 0) {
-            if (roped) {
-              if (d0 != pre_d0) {                                         // pairs that were not prefetched
-                const int seg = d0 / Rd, pos = seg >= 2 ? icol : irow;
-                const float2* trow = reinterpret_cast<const float2*>((seg >= 2 ? p.rope.col_cs : p.rope.row_cs) + (int64_t)max(pos, 0) * R * 2) + (d0 - seg * R);
-                constexpr int NPRE = R >= 16 ? 16 : 8;
-#pragma unroll
-                for (int e = 0; e < NPRE; ++e) cs[e] = pos >= 0 ? __ldg(trow + e) : make_float2(1.f, 0.f);
-              }
-              if constexpr (R >= 16) {
-#pragma unroll
-                for (int e = 0; e < 16; ++e) vb[e] = __uint_as_float(rb[e]) * scale;
-                inv_rotate_pairs<16>(va, vb, cs);
-                if (t_in) store16<BF16>(qk_row + d0 + R, vb);
-              } else {
-                inv_rotate_pairs<8>(va, va + 8, cs);
-              }
-            }
-          }
-          if (t_in) store16<BF16>(qk_row + d0, va);
-        }
-        if constexpr (DKDV) {
-          T* v_row = (T*)out_v.ptr + bi * out_v.s0 + hi * out_v.s1 + tok * out_v.s2;
-          const uint32_t av = lane_base + acc_v;
-          const int Wv = 32 * p.vch;
-#pragma unroll 1
-          for (int d0 = g * Wv; d0 < g * Wv + Wv; d0 += 16) {
-            uint32_t ra[16];
-            float va[16];
-            tmem_ld16(av + d0, ra);
-            tmem_wait_ld();
-#pragma unroll
-            for (int e = 0; e < 16; ++e) va[e] = __uint_as_float(ra[e]);
-            if (t_in) store16<BF16>(v_row + d0, va);
-          }
-        }
-        tc_fence_before();
-        mbar_arrive(&sh->acc_free);
-        if (m == 0 && g == 0 && it == p.trace_it) trace_mark(p, 2, 31);
-      }
-      gbase += tp.nblk;
-    }
   } else {
     // ------------------------------------------------------------------ RoPE on the qk tiles, mask tiles, lse / delta staging
     // One loop over the "units" of an item: unit -1 is the resident tile, units 0.. are the streamed blocks.
@@ -572,6 +595,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ C
         parts = yp;
       }
     }
+  }
   }
 
   // ------------------------------------------------------------------ teardown

@@ -129,139 +129,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   };
   const int n_items = p.n_items, tiles_per_head = pl.n_tiles_x * pl.n_tiles_y;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
-    if (elect_one()) {
-      prefetch_tmap(&tm_q);
-      prefetch_tmap(&tm_k);
-      prefetch_tmap(&tm_v);
-    }
-    __syncwarp();
-    int stage = 0, stage_par = 1;        // parity of the "empty" phase a refill of this stage waits for
-    bool ring_full = false;              // all stages have been filled once
-#pragma unroll 1
-    for (int it = 0, item = blockIdx.x; item < n_items; ++it, item += gridDim.x) {
-      const int bh = item / tiles_per_head, bi = bh / p.H, hi = bh - bi * p.H;
-      const TilePos tp = tile_pos(p, item - bh * tiles_per_head);
-      const int qb = it & 1;
-      if (it >= 2) wait_park(&sh->q_empty[qb], ((it >> 1) - 1) & 1);
-      if (ok && elect_one()) {
-        mbar_arrive_expect_tx(&sh->q_full[qb], q_bytes);
-#pragma unroll 1
-        for (int c = 0; c < p.qch; ++c)
-          tma_load_5d(q_smem + qb * q_bytes + c * 16384, &tm_q, &sh->q_full[qb], c * 64, tp.x0, tp.r0, hi, bi);
-      }
-      __syncwarp();
-#pragma unroll 1
-      for (int j = 0; j < tp.nblk; ++j) {
-        if (ring_full) wait_park(&sh->kv_empty[stage], stage_par);
-        if (ok && elect_one()) {
-          mbar_arrive_expect_tx(&sh->kv_full[stage], k_stage + v_stage);
-          const int row = tp.hr_first + j * pl.KR;
-#pragma unroll 1
-          for (int c = 0; c < p.qch; ++c)
-            tma_load_5d(k_smem + stage * k_stage + c * blk_bytes, &tm_k, &sh->kv_full[stage], c * 64, tp.hx0, row, hi, bi);
-#pragma unroll 1
-          for (int c = 0; c < p.vch; ++c)
-            tma_load_5d(v_smem + stage * v_stage + c * blk_bytes, &tm_v, &sh->kv_full[stage], c * 64, tp.hx0, row, hi, bi);
-        }
-        __syncwarp();
-        if (++stage == pl.stages) { stage = 0; stage_par ^= 1; ring_full = true; }
-      }
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    // Everything this warp needs per block is kept incrementally (ring indices, barrier parities,
-    // descriptor bases), and each kind of MMA group has exactly one issue site.
-    const uint32_t fmt = BF16 ? 1u : 0u;
-    const uint32_t idesc_s = instr_desc(fmt, 128, N, 0, 0);
-    const uint32_t idesc_pv = instr_desc(fmt, 128, o_cols, 0, 1);
-    const uint32_t hi_sw = smem_desc_hi(1024, true), hi_ns = smem_desc_hi(kXSbo, false);
-    const uint64_t q_desc0 = smem_desc_from(smem_u32(q_smem), 16, hi_sw), k_desc0 = smem_desc_from(smem_u32(k_smem), 16, hi_sw),
-                   v_desc0 = smem_desc_from(smem_u32(v_smem), blk_bytes, hi_sw),
-                   qx_desc0 = smem_desc_from(smem_u32(qx_smem), kXLbo, hi_ns), kx_desc0 = smem_desc_from(smem_u32(kx_smem), kXLbo, hi_ns);
-    const uint32_t k_stage16 = k_stage >> 4, v_stage16 = v_stage >> 4, kx_stage16 = kx_stage >> 4, blk16 = blk_bytes >> 4;
-    const int nks = N >> 4;
-    // score side: runs `nsb` blocks ahead of the PV side
-    int s_it = 0, s_item = blockIdx.x, s_j = 0, s_nblk = 1, s_stage = 0, s_stage_par = 0, s_buf = 0;
-    // PV side
-    int p_it = 0, p_item = blockIdx.x, p_j = 0, p_nblk = 1, p_stage = 0, p_buf = 0, p_buf_par = 0, p_grp = 0;
-    if (s_item < n_items) s_nblk = p_nblk = item_blocks(p, s_item, tiles_per_head);
-    int lead = nsb;
-    while (true) {
-      if (lead > 0) {
-        --lead;
-      } else {
-        if (p_item >= n_items) break;
-        // ---- O_g += P V for the block at the PV cursor
-        const bool first = p_j < 2;                       // first block of this item for group p_grp: O_g starts over
-        wait_spin(&sh->p_full[p_buf], p_buf_par);
-        if (first && p_it >= 1) wait_spin(&sh->o_free, (p_it - 1) & 1);   // the previous item's O_g has been read
-        if (ok) {
-          tc_fence_after();
-          if (elect_one()) {
-            const uint32_t pa = tmem + p_buf * 128, od = tmem + o_base + p_grp * o_cols;
-            uint64_t vd = v_desc0 + (uint64_t)(p_stage * v_stage16);
-            uint32_t acc = first ? 0u : 1u;
-#pragma unroll 1
-            for (int ks = 0; ks < nks; ++ks, vd += 128, acc = 1u) umma_ts(od, pa + ks * 8, vd, idesc_pv, acc);
-            umma_commit(&sh->kv_empty[p_stage]);
-            umma_commit(&sh->pv_done[p_grp]);
-            if (p_j == p_nblk - 1) umma_commit(&sh->o_full);
-            if (p_it == p.trace_it) trace_mark(p, 1, 2 + 2 * p_j);
-          }
-          __syncwarp();
-        }
-        p_grp ^= 1;
-        if (++p_stage == pl.stages) p_stage = 0;
-        if (++p_buf == nsb) { p_buf = 0; p_buf_par ^= 1; }
-        if (++p_j == p_nblk) {
-          p_j = 0;
-          ++p_it;
-          p_item += gridDim.x;
-          if (p_item < n_items) p_nblk = item_blocks(p, p_item, tiles_per_head);
-        }
-      }
-      if (s_item < n_items) {
-        // ---- S = Q K^T + mask for the block at the score cursor
-        const int qb = s_it & 1;
-        if (s_j == 0) wait_spin(&sh->q_ready[qb], (s_it >> 1) & 1);
-        wait_spin(&sh->k_ready[s_stage], s_stage_par);
-        // score buffer s_buf is free: the PV MMA of the block that used it last was issued before this one
-        if (ok) {
-          tc_fence_after();
-          if (elect_one()) {
-            const uint32_t sd = tmem + s_buf * 128;
-            uint64_t qd = q_desc0 + (uint64_t)(qb * (q_bytes >> 4)), kd = k_desc0 + (uint64_t)(s_stage * k_stage16);
-            uint32_t acc = 0u;
-#pragma unroll 1
-            for (int c = 0; c < p.qch; ++c, qd += 1024 - 8, kd += blk16 - 8) {
-#pragma unroll
-              for (int k = 0; k < 4; ++k, qd += 2, kd += 2, acc = 1u) umma_ss(sd, qd, kd, idesc_s, acc);
-            }
-            const uint64_t kxd = kx_desc0 + (uint64_t)(s_stage * kx_stage16);
-#pragma unroll
-            for (int k = 0; k < 2; ++k)  // + indicator x penalty: the window mask
-              umma_ss(sd, qx_desc0 + (uint64_t)(k * (kXStepBytes >> 4)), kxd + (uint64_t)(k * (kXStepBytes >> 4)), idesc_s, 1u);
-            umma_commit(&sh->s_full[s_buf]);
-            if (s_j == s_nblk - 1) umma_commit(&sh->q_empty[qb]);   // last read of this query buffer
-            if (s_it == p.trace_it) trace_mark(p, 1, 1 + 2 * s_j);
-          }
-          __syncwarp();
-        }
-        if (++s_stage == pl.stages) { s_stage = 0; s_stage_par ^= 1; }
-        if (++s_buf == nsb) s_buf = 0;
-        if (++s_j == s_nblk) {
-          s_j = 0;
-          ++s_it;
-          s_item += gridDim.x;
-          if (s_item < n_items) s_nblk = item_blocks(p, s_item, tiles_per_head);
-        }
-      } else {
-        lead = 0;                        // nothing left to issue ahead
-      }
-    }
-  } else if (warp >= 4 && warp < 12) {
+  // Registers follow the work: the kernel starts with 128 per thread; the producer / issuer / RoPE
+  // warpgroups (warps 0-3 and 12-15) give some back, the two softmax warpgroups take them.
+  // (2 * 104 + 2 * 152) * 128 = 64 Ki.  Each setmaxnreg is the first instruction of its branch, so that the
+  // whole branch is compiled for that budget.
+  if (warp >= 4 && warp < 12) {
+    setmaxnreg_inc<152>();
     // ------------------------------------------------------------------ softmax, one thread per query row and group
     const int lane = threadIdx.x & 31;
     const int g = (warp - 4) >> 2;                // group: takes the blocks whose stream position has parity g
@@ -450,6 +323,140 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       gbase += tp.nblk;
     }
   } else {
+    setmaxnreg_dec<104>();
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      prefetch_tmap(&tm_q);
+      prefetch_tmap(&tm_k);
+      prefetch_tmap(&tm_v);
+    }
+    __syncwarp();
+    int stage = 0, stage_par = 1;        // parity of the "empty" phase a refill of this stage waits for
+    bool ring_full = false;              // all stages have been filled once
+#pragma unroll 1
+    for (int it = 0, item = blockIdx.x; item < n_items; ++it, item += gridDim.x) {
+      const int bh = item / tiles_per_head, bi = bh / p.H, hi = bh - bi * p.H;
+      const TilePos tp = tile_pos(p, item - bh * tiles_per_head);
+      const int qb = it & 1;
+      if (it >= 2) wait_park(&sh->q_empty[qb], ((it >> 1) - 1) & 1);
+      if (ok && elect_one()) {
+        mbar_arrive_expect_tx(&sh->q_full[qb], q_bytes);
+#pragma unroll 1
+        for (int c = 0; c < p.qch; ++c)
+          tma_load_5d(q_smem + qb * q_bytes + c * 16384, &tm_q, &sh->q_full[qb], c * 64, tp.x0, tp.r0, hi, bi);
+      }
+      __syncwarp();
+#pragma unroll 1
+      for (int j = 0; j < tp.nblk; ++j) {
+        if (ring_full) wait_park(&sh->kv_empty[stage], stage_par);
+        if (ok && elect_one()) {
+          mbar_arrive_expect_tx(&sh->kv_full[stage], k_stage + v_stage);
+          const int row = tp.hr_first + j * pl.KR;
+#pragma unroll 1
+          for (int c = 0; c < p.qch; ++c)
+            tma_load_5d(k_smem + stage * k_stage + c * blk_bytes, &tm_k, &sh->kv_full[stage], c * 64, tp.hx0, row, hi, bi);
+#pragma unroll 1
+          for (int c = 0; c < p.vch; ++c)
+            tma_load_5d(v_smem + stage * v_stage + c * blk_bytes, &tm_v, &sh->kv_full[stage], c * 64, tp.hx0, row, hi, bi);
+        }
+        __syncwarp();
+        if (++stage == pl.stages) { stage = 0; stage_par ^= 1; ring_full = true; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    // Everything this warp needs per block is kept incrementally (ring indices, barrier parities,
+    // descriptor bases), and each kind of MMA group has exactly one issue site.
+    const uint32_t fmt = BF16 ? 1u : 0u;
+    const uint32_t idesc_s = instr_desc(fmt, 128, N, 0, 0);
+    const uint32_t idesc_pv = instr_desc(fmt, 128, o_cols, 0, 1);
+    const uint32_t hi_sw = smem_desc_hi(1024, true), hi_ns = smem_desc_hi(kXSbo, false);
+    const uint64_t q_desc0 = smem_desc_from(smem_u32(q_smem), 16, hi_sw), k_desc0 = smem_desc_from(smem_u32(k_smem), 16, hi_sw),
+                   v_desc0 = smem_desc_from(smem_u32(v_smem), blk_bytes, hi_sw),
+                   qx_desc0 = smem_desc_from(smem_u32(qx_smem), kXLbo, hi_ns), kx_desc0 = smem_desc_from(smem_u32(kx_smem), kXLbo, hi_ns);
+    const uint32_t k_stage16 = k_stage >> 4, v_stage16 = v_stage >> 4, kx_stage16 = kx_stage >> 4, blk16 = blk_bytes >> 4;
+    const int nks = N >> 4;
+    // score side: runs `nsb` blocks ahead of the PV side
+    int s_it = 0, s_item = blockIdx.x, s_j = 0, s_nblk = 1, s_stage = 0, s_stage_par = 0, s_buf = 0;
+    // PV side
+    int p_it = 0, p_item = blockIdx.x, p_j = 0, p_nblk = 1, p_stage = 0, p_buf = 0, p_buf_par = 0, p_grp = 0;
+    if (s_item < n_items) s_nblk = p_nblk = item_blocks(p, s_item, tiles_per_head);
+    int lead = nsb;
+    while (true) {
+      if (lead > 0) {
+        --lead;
+      } else {
+        if (p_item >= n_items) break;
+        // ---- O_g += P V for the block at the PV cursor
+        const bool first = p_j < 2;                       // first block of this item for group p_grp: O_g starts over
+        wait_spin(&sh->p_full[p_buf], p_buf_par);
+        if (first && p_it >= 1) wait_spin(&sh->o_free, (p_it - 1) & 1);   // the previous item's O_g has been read
+        if (ok) {
+          tc_fence_after();
+          if (elect_one()) {
+            const uint32_t pa = tmem + p_buf * 128, od = tmem + o_base + p_grp * o_cols;
+            uint64_t vd = v_desc0 + (uint64_t)(p_stage * v_stage16);
+            uint32_t acc = first ? 0u : 1u;
+#pragma unroll 1
+            for (int ks = 0; ks < nks; ++ks, vd += 128, acc = 1u) umma_ts(od, pa + ks * 8, vd, idesc_pv, acc);
+            umma_commit(&sh->kv_empty[p_stage]);
+            umma_commit(&sh->pv_done[p_grp]);
+            if (p_j == p_nblk - 1) umma_commit(&sh->o_full);
+            if (p_it == p.trace_it) trace_mark(p, 1, 2 + 2 * p_j);
+          }
+          __syncwarp();
+        }
+        p_grp ^= 1;
+        if (++p_stage == pl.stages) p_stage = 0;
+        if (++p_buf == nsb) { p_buf = 0; p_buf_par ^= 1; }
+        if (++p_j == p_nblk) {
+          p_j = 0;
+          ++p_it;
+          p_item += gridDim.x;
+          if (p_item < n_items) p_nblk = item_blocks(p, p_item, tiles_per_head);
+        }
+      }
+      if (s_item < n_items) {
+        // ---- S = Q K^T + mask for the block at the score cursor
+        const int qb = s_it & 1;
+        if (s_j == 0) wait_spin(&sh->q_ready[qb], (s_it >> 1) & 1);
+        wait_spin(&sh->k_ready[s_stage], s_stage_par);
+        // score buffer s_buf is free: the PV MMA of the block that used it last was issued before this one
+        if (ok) {
+          tc_fence_after();
+          if (elect_one()) {
+            const uint32_t sd = tmem + s_buf * 128;
+            uint64_t qd = q_desc0 + (uint64_t)(qb * (q_bytes >> 4)), kd = k_desc0 + (uint64_t)(s_stage * k_stage16);
+            uint32_t acc = 0u;
+#pragma unroll 1
+            for (int c = 0; c < p.qch; ++c, qd += 1024 - 8, kd += blk16 - 8) {
+#pragma unroll
+              for (int k = 0; k < 4; ++k, qd += 2, kd += 2, acc = 1u) umma_ss(sd, qd, kd, idesc_s, acc);
+            }
+            const uint64_t kxd = kx_desc0 + (uint64_t)(s_stage * kx_stage16);
+#pragma unroll
+            for (int k = 0; k < 2; ++k)  // + indicator x penalty: the window mask
+              umma_ss(sd, qx_desc0 + (uint64_t)(k * (kXStepBytes >> 4)), kxd + (uint64_t)(k * (kXStepBytes >> 4)), idesc_s, 1u);
+            umma_commit(&sh->s_full[s_buf]);
+            if (s_j == s_nblk - 1) umma_commit(&sh->q_empty[qb]);   // last read of this query buffer
+            if (s_it == p.trace_it) trace_mark(p, 1, 1 + 2 * s_j);
+          }
+          __syncwarp();
+        }
+        if (++s_stage == pl.stages) { s_stage = 0; s_stage_par ^= 1; }
+        if (++s_buf == nsb) s_buf = 0;
+        if (++s_j == s_nblk) {
+          s_j = 0;
+          ++s_it;
+          s_item += gridDim.x;
+          if (s_item < n_items) s_nblk = item_blocks(p, s_item, tiles_per_head);
+        }
+      } else {
+        lead = 0;                        // nothing left to issue ahead
+      }
+    }
+  } else {
     // ------------------------------------------------------------------ fused RoPE-2D on Q and K tiles, mask tiles
     // One loop over the "units" of an item: unit -1 is the query tile, units 0.. are the K blocks.
     const int t = warp < 4 ? (int)threadIdx.x - 64 : (int)threadIdx.x - 384 + 64;
@@ -510,6 +517,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         parts = kp;
       }
     }
+  }
   }
 
   // ------------------------------------------------------------------ teardown
