@@ -150,19 +150,29 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     // this group's next block: stream position, its score buffer and that buffer's barrier parity
     uint32_t own_next = g, n_own = 0;
     int sbuf = g, spar = 0;
+    // The merge / store of an item is deferred until this thread has worked on its first block of the
+    // NEXT item: the last PV MMAs of an item complete long after a group has finished its own last block,
+    // and the score MMAs of the next item's first blocks have been issued by then.
+    bool pend = false, pend_even = false;
+    int pend_item = 0, pend_it = 0, pend_cnt = 0, pend_cnt_other = 0;
+    float pend_m = 0.f, pend_l = 0.f;
 #pragma unroll 1
-    for (int it = 0, item = blockIdx.x; item < n_items; ++it, item += gridDim.x) {
-      const int bh = item / tiles_per_head, bi = bh / p.H, hi = bh - bi * p.H;
-      const TilePos tp = tile_pos(p, item - bh * tiles_per_head);
-      const int qr = tp.r0 + m / pl.TW, qx = tp.x0 + m % pl.TW;
-      const bool q_in = qr < p.t_h && qx < p.Wtok;
+    for (int it = 0, item = blockIdx.x;; ++it, item += gridDim.x) {
+      const bool have = item < n_items;
+      TilePos tp;
+      tp.r0 = tp.x0 = tp.hx0 = tp.hr_first = tp.hr_last = 0;
+      tp.nblk = 0;
+      if (have) tp = tile_pos(p, item % tiles_per_head);
       // rows of the grid the 32 queries of this warp can see
       const int see_lo = tp.r0 + (quarter * 32) / pl.TW - p.wr, see_hi = tp.r0 + (quarter * 32 + 31) / pl.TW + p.wr;
       float m_used = -INFINITY, l = 0.f;
       int cnt = 0;                                // blocks of this item this group has handed to the PV MMA
       if (tr && it == p.trace_it) trace_mark(p, 2, 29);
+      int j = have ? (int)(own_next - gbase) : 0;
+      bool first = true;
 #pragma unroll 1
-      for (int j = (int)(own_next - gbase); j < tp.nblk; j += 2, own_next += 2, ++n_own, ++cnt) {
+      while (true) {
+      if (j < tp.nblk) {
         const uint32_t s_tm = lane_base + sbuf * 128;
         uint64_t* const p_bar = &sh->p_full[sbuf];
         wait_spin(&sh->s_full[sbuf], spar);
@@ -171,7 +181,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         const int blk_first = tp.hr_first + j * pl.KR, blk_last = blk_first + pl.KR - 1;
         const bool seen = !(blk_last < see_lo || blk_first > see_hi);
         if (tr && it == p.trace_it) trace_mark(p, 2, 1 + 4 * (j >> 1));
-        if (!ok) continue;
+        if (ok) {
         tc_fence_after();
         uint32_t ra[16], rb[16];
         if (!seen) {
@@ -260,25 +270,37 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(p_bar);
+        }
         if (tr && it == p.trace_it) trace_mark(p, 2, 4 + 4 * (j >> 1));
+        j += 2;
+        own_next += 2;
+        ++n_own;
+        ++cnt;
       }
-      // the item ends: merge the two groups' partial results; each group stores one half of the row
-      const int par = it & 1;
-      const int cnt_other = (int)((tp.nblk + (((gbase & 1u) == (uint32_t)(g ^ 1)) ? 1 : 0)) >> 1);
-      wait_spin(&sh->o_full, it & 1);
-      sh->ml[par][g][0][m] = m_used;
-      sh->ml[par][g][1][m] = l;
+      if (first) {
+      first = false;
+      if (pend) {
+      pend = false;
+      // merge the two groups' partial results of the pending item; each group stores one half of the row
+      const int e_bh = pend_item / tiles_per_head, bi = e_bh / p.H, hi = e_bh - bi * p.H;
+      const TilePos e_tp = tile_pos(p, pend_item - e_bh * tiles_per_head);
+      const int qr = e_tp.r0 + m / pl.TW, qx = e_tp.x0 + m % pl.TW;
+      const bool q_in = qr < p.t_h && qx < p.Wtok;
+      const int par = pend_it & 1;
+      wait_spin(&sh->o_full, pend_it & 1);
+      sh->ml[par][g][0][m] = pend_m;
+      sh->ml[par][g][1][m] = pend_l;
       named_bar_sync(1 + quarter, 64);
       const float m_o = sh->ml[par][g ^ 1][0][m], l_o = sh->ml[par][g ^ 1][1][m];
       if (ok) {
         tc_fence_after();
-        if (tr && it == p.trace_it) trace_mark(p, 2, 30);
+        if (tr && pend_it == p.trace_it) trace_mark(p, 2, 30);
         // Merge in an order fixed by the blocks' positions in the item (even ones first), not by which
         // group happened to get them: the result of a tile must not depend on the work that preceded it.
-        const bool mine_even = ((gbase & 1u) == (uint32_t)g);
-        const float m_e = mine_even ? m_used : m_o, m_d = mine_even ? m_o : m_used;
-        const float l_e = mine_even ? l : l_o, l_d = mine_even ? l_o : l;
-        const int cnt_e = mine_even ? cnt : cnt_other, cnt_d = mine_even ? cnt_other : cnt;
+        const bool mine_even = pend_even;
+        const float m_e = mine_even ? pend_m : m_o, m_d = mine_even ? m_o : pend_m;
+        const float l_e = mine_even ? pend_l : l_o, l_d = mine_even ? l_o : pend_l;
+        const int cnt_e = mine_even ? pend_cnt : pend_cnt_other, cnt_d = mine_even ? pend_cnt_other : pend_cnt;
         const float mm = fmaxf(m_e, m_d);
         const float w_e = (m_e == -INFINITY) ? 0.f : exp2f((m_e - mm) * c2);
         const float w_d = (m_d == -INFINITY) ? 0.f : exp2f((m_d - mm) * c2);
@@ -317,9 +339,23 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             }
           }
         }
-        if (q_in && g == 0) lse[(int64_t)bh * p.t_h * p.Wtok + tok] = mm * c2 + log2f(lt);
-        if (tr && it == p.trace_it) trace_mark(p, 2, 31);
+        if (q_in && g == 0) lse[(int64_t)e_bh * p.t_h * p.Wtok + tok] = mm * c2 + log2f(lt);
+        if (tr && pend_it == p.trace_it) trace_mark(p, 2, 31);
       }
+      }
+      }
+      if (j >= tp.nblk) break;
+      }
+      if (!have) break;
+      // this item's result becomes the pending one
+      pend = true;
+      pend_item = item;
+      pend_it = it;
+      pend_m = m_used;
+      pend_l = l;
+      pend_cnt = cnt;
+      pend_cnt_other = (int)((tp.nblk + (((gbase & 1u) == (uint32_t)(g ^ 1)) ? 1 : 0)) >> 1);
+      pend_even = ((gbase & 1u) == (uint32_t)g);
       gbase += tp.nblk;
     }
   } else {
