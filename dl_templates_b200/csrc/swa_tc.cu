@@ -114,7 +114,8 @@ bool make_plan_shape(const swa_geom_t* g, int which, int TH, int TW, uint32_t ta
     int nmax = which == 0 ? 128 : (512 - acc_cols) / (2 * nsb);
     nmax = nmax > 128 ? 128 : nmax;
     nmax = env_int("SWA_TC_NMAX", nmax);
-    for (int nxb = 2; nxb >= 1; --nxb) {
+    // the forward kernel always double-buffers its query tile
+    for (int nxb = which == 0 ? 2 : env_int("SWA_TC_NXB", 2); nxb >= (which == 0 ? 2 : 1); --nxb) {
       const uint32_t fixed = nxb * x_bytes + 128u * kXRowBytes + tab_bytes;
       long best_cost = -1;
       for (int KW = hw; KW <= 64; ++KW)

@@ -140,10 +140,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ C
 
   // Registers follow the work: the kernel starts with 128 per thread; the producer / issuer / RoPE
   // warpgroups (warps 0-3 and 12-15) give some back, the two compute warpgroups take them.
-  // (2 * 104 + 2 * 152) * 128 = 64 Ki.  Each setmaxnreg is the first instruction of its branch, so that the
+  // (2 * 104 + 2 * 152) * 128 = 64 Ki.  Not done in the variant whose RoPE warps keep cos/sin rows in registers.  Each setmaxnreg is the first instruction of its branch, so that the
   // whole branch is compiled for that budget.
   if (warp >= 4 && warp < 12) {
-    setmaxnreg_inc<152>();
+    if constexpr (TABS || NI == 0) setmaxnreg_inc<152>();
     // ------------------------------------------------------------------ P / dS, one thread per resident row and group
     const int lane = threadIdx.x & 31;
     const int g = (warp - 4) >> 2;
@@ -181,22 +181,37 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ C
         for (int e = 0; e < NP; ++e) cs[e] = __ldg(trow + e);
       }
     };
+    // Without RoPE the epilogue of an item is deferred until this thread has worked on its first block of
+    // the NEXT item: the last accumulating MMAs of an item complete long after a group has finished its
+    // own last block, and the score MMAs of the next item's first blocks have been issued by then.  (With
+    // RoPE the rotating warps set the pace and holding back the first accumulating MMA of the next item,
+    // which frees a stage of the ring, costs more than the tail; measured.)
+    constexpr bool kDefer = NI == 0;
+    bool pend = false;
+    int pend_item = 0, pend_it = 0;
 #pragma unroll 1
-    for (int it = 0, item = blockIdx.x; item < n_items; ++it, item += gridDim.x) {
-      const int bh = item / tiles_per_head, bi = bh / p.H, hi = bh - bi * p.H;
-      const TilePos tp = tile_pos(p, item - bh * tiles_per_head);
-      const int tr = tp.r0 + m / pl.TW, tx = tp.x0 + m % pl.TW;
-      const bool t_in = tr < p.t_h && tx < p.Wtok;
-      const int64_t tok = (int64_t)tr * p.Wtok + tx;
-      const int64_t vec_base = (int64_t)bh * p.t_h * p.Wtok;
+    for (int it = 0, item = blockIdx.x;; ++it, item += gridDim.x) {
+      const bool have = item < n_items;
+      TilePos tp;
+      tp.r0 = tp.x0 = tp.hx0 = tp.hr_first = tp.hr_last = 0;
+      tp.nblk = 0;
+      const int bh = have ? item / tiles_per_head : 0;
+      if (have) tp = tile_pos(p, item - bh * tiles_per_head);
       const int see_lo = tp.r0 + (quarter * 32) / pl.TW - p.wr, see_hi = tp.r0 + (quarter * 32 + 31) / pl.TW + p.wr;
       float my_nlse = -INFINITY, my_delta = 0.f;     // dQ: -lse and delta of this thread's query
-      if (!DKDV && t_in) {
-        my_nlse = -__ldg(lse + vec_base + tok);
-        my_delta = __ldg(delta + vec_base + tok);
+      if (!DKDV && have) {
+        const int tr = tp.r0 + m / pl.TW, tx = tp.x0 + m % pl.TW;
+        if (tr < p.t_h && tx < p.Wtok) {
+          const int64_t at = (int64_t)bh * p.t_h * p.Wtok + (int64_t)tr * p.Wtok + tx;
+          my_nlse = -__ldg(lse + at);
+          my_delta = __ldg(delta + at);
+        }
       }
+      int j = have ? (int)(own_next - gbase) : 0;
+      bool first = true;
 #pragma unroll 1
-      for (int j = (int)(own_next - gbase); j < tp.nblk; j += 2, own_next += 2) {
+      while (true) {
+      if (j < tp.nblk) {
         const uint32_t s_tm = lane_base + buf * 2 * N, d_tm = s_tm + N;
         uint64_t* const ds_bar = &sh->ds_full[buf];
         wait_spin(&sh->sd_full[buf], buf_par, 7);
@@ -209,7 +224,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ C
         if (stage >= pl.stages) { stage -= pl.stages; stage_par ^= 1; }
         const int blk_first = tp.hr_first + j * pl.KR, blk_last = blk_first + pl.KR - 1;
         const bool seen = !(blk_last < see_lo || blk_first > see_hi);
-        if (!ok) continue;
+        if (ok) {
         tc_fence_after();
         uint32_t sa[16], sb[16], da[16], db[16];
         if (!seen) {
@@ -273,9 +288,27 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ C
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(ds_bar);
+        }
         if (m == 0 && g == 0 && it == p.trace_it) trace_mark(p, 2, 2 + 2 * (j >> 1));
+        j += 2;
+        own_next += 2;
       }
-      // ---- the item ends: this group stores its half of the accumulator row(s)
+      const bool at_end = j >= tp.nblk;
+      if (kDefer ? first : at_end) {
+      first = false;
+      if (!kDefer && have) {                       // the item that has just ended
+        pend = true;
+        pend_item = item;
+        pend_it = it;
+      }
+      if (pend) {
+      pend = false;
+      // ---- the pending item: this group stores its half of the accumulator row(s)
+      const int e_bh = pend_item / tiles_per_head, bi = e_bh / p.H, hi = e_bh - bi * p.H;
+      const TilePos e_tp = tile_pos(p, pend_item - e_bh * tiles_per_head);
+      const int tr = e_tp.r0 + m / pl.TW, tx = e_tp.x0 + m % pl.TW;
+      const bool t_in = tr < p.t_h && tx < p.Wtok;
+      const int64_t tok = (int64_t)tr * p.Wtok + tx;
       // dQ / dK: columns [g W, g W + W), W = 32 qch; the partner of a rotated dim lies in the same half
       // Control flow below is warp-uniform (the tensor-memory loads are warp-collective): whether a
       // granule is rotated depends only on its dims; a thread whose token is outside the grid or has a
@@ -294,11 +327,11 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ C
           load_pairs(cs, seg >= 2, seg >= 2 ? icol : irow, base - seg * R);
         }
       }
-      if (m == 0 && g == 0 && it == p.trace_it) trace_mark(p, 2, 29);
-      wait_spin(&sh->acc_full, it & 1, 9);
+      if (m == 0 && g == 0 && pend_it == p.trace_it) trace_mark(p, 2, 29);
+      wait_spin(&sh->acc_full, pend_it & 1, 9);
       if (ok) {
         tc_fence_after();
-        if (m == 0 && g == 0 && it == p.trace_it) trace_mark(p, 2, 30);
+        if (m == 0 && g == 0 && pend_it == p.trace_it) trace_mark(p, 2, 30);
         T* qk_row = (T*)out_qk.ptr + bi * out_qk.s0 + hi * out_qk.s1 + tok * out_qk.s2;
         const uint32_t aqk = lane_base + acc_qk;
         const float scale = p.sm_scale;
@@ -348,12 +381,22 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ C
         }
         tc_fence_before();
         mbar_arrive(&sh->acc_free);
-        if (m == 0 && g == 0 && it == p.trace_it) trace_mark(p, 2, 31);
+        if (m == 0 && g == 0 && pend_it == p.trace_it) trace_mark(p, 2, 31);
+      }
+      }
+      }
+      if (at_end) break;
+      }
+      if (!have) break;
+      if (kDefer) {                                // this item's accumulators are stored during the next item
+        pend = true;
+        pend_item = item;
+        pend_it = it;
       }
       gbase += tp.nblk;
     }
   } else {
-    setmaxnreg_dec<104>();
+    if constexpr (TABS || NI == 0) setmaxnreg_dec<104>();
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (elect_one()) {

@@ -131,10 +131,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 
   // Registers follow the work: the kernel starts with 128 per thread; the producer / issuer / RoPE
   // warpgroups (warps 0-3 and 12-15) give some back, the two softmax warpgroups take them.
-  // (2 * 104 + 2 * 152) * 128 = 64 Ki.  Each setmaxnreg is the first instruction of its branch, so that the
+  // (2 * 104 + 2 * 152) * 128 = 64 Ki.  Not done in the variant whose RoPE warps keep cos/sin rows in registers.  Each setmaxnreg is the first instruction of its branch, so that the
   // whole branch is compiled for that budget.
   if (warp >= 4 && warp < 12) {
-    setmaxnreg_inc<152>();
+    if constexpr (TABS || NI == 0) setmaxnreg_inc<152>();
     // ------------------------------------------------------------------ softmax, one thread per query row and group
     const int lane = threadIdx.x & 31;
     const int g = (warp - 4) >> 2;                // group: takes the blocks whose stream position has parity g
@@ -359,7 +359,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       gbase += tp.nblk;
     }
   } else {
-    setmaxnreg_dec<104>();
+    if constexpr (TABS || NI == 0) setmaxnreg_dec<104>();
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (elect_one()) {
