@@ -140,12 +140,20 @@ bool make_plan_shape(const swa_geom_t* g, int which, int TH, int TW, uint32_t ta
       const int Wtok = g->t_width * g->b_size;
       pl.n_tiles_x = (Wtok + pl.TW - 1) / pl.TW;
       pl.n_tiles_y = (g->t_height + pl.TH - 1) / pl.TH;
-      pl.nsb = nsb;
       pl.nxb = nxb;
       pl.stages = min_stages;
       while (pl.stages < kMaxStages && fixed + (pl.stages + 1) * stage + kSmemSlack <= kSmemLimit) ++pl.stages;
       pl.stages = env_int("SWA_TC_STAGES", pl.stages);
       pl.smem_bytes = fixed + pl.stages * stage + kSmemSlack;
+      if (which == 0) {
+        // forward: score buffers = look-ahead of the score MMAs: 3 next to the two accumulators, 4 (packed at N-column
+        // strides) when tensor memory allows and the block ring is deep enough to feed them (measured)
+        int n = pl.stages >= 6 ? 4 : 3;
+        while (n > 2 && n * pl.N + 2 * 64 * vch > 512) --n;
+        pl.nsb = env_int("SWA_TC_NSB", n);
+      } else {
+        pl.nsb = nsb;
+      }
       *out = pl;
       return pl.smem_bytes <= kSmemLimit && pl.N % 16 == 0 && pl.N <= nmax && pl.stages >= 2;
     }

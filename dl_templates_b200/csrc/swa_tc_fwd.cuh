@@ -43,7 +43,7 @@ namespace tc {
 struct FwdShared {
   uint64_t q_full[2], q_ready[2], q_empty[2];
   uint64_t kv_full[kMaxStages], k_ready[kMaxStages], kv_empty[kMaxStages];
-  uint64_t s_full[3], p_full[3], pv_done[2], o_full, o_free;
+  uint64_t s_full[4], p_full[4], pv_done[2], o_full, o_free;
   float ml[2][2][2][128];   // [item parity][group][maximum | sum][row]: merged when an item ends
   PenaltyTables pen;        // window-mask penalty parts of the current item's halo rows / columns
   uint32_t tmem_base;
@@ -69,10 +69,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   const uint32_t k_stage = blk_bytes * p.qch, v_stage = blk_bytes * p.vch;
   const uint32_t kx_stage = (uint32_t)N * kXRowBytes;           // window-mask penalty rows of a streamed block
   const uint32_t o_cols = p.vch * 64u;                           // TMEM columns of one O accumulator
-  // three score buffers when the accumulators leave room (d_v = 64): the score MMAs then run three
-  // blocks ahead and a softmax group finds its next block ready when it has finished one
-  const int nsb = p.vch == 1 ? 3 : 2;
-  const uint32_t o_base = nsb * 128u;                            // score buffer b at column 128*b, O_g at o_base + g*d_v
+  // score buffers: the score MMAs run `nsb` blocks ahead, so that a softmax group finds its next block
+  // ready when it has finished one (2 to 4, chosen by the planner)
+  const int nsb = pl.nsb;
+  // score buffer b at column s_stride*b (128-column strides when they fit, else packed), O_g behind them
+  const uint32_t s_stride = (nsb * 128u + 2 * o_cols <= kFwdTmemCols) ? 128u : (uint32_t)N;
+  const uint32_t o_base = nsb * s_stride;
   uint8_t* q_smem = smem;                                        // two buffers
   uint8_t* qx_smem = q_smem + 2 * q_bytes;                      // window-mask indicator rows of a query tile
   uint8_t* k_smem = qx_smem + 128 * kXRowBytes;
@@ -91,7 +93,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       mbar_init(&sh->q_empty[s], 1);
       mbar_init(&sh->pv_done[s], 1);
     }
-    for (int s = 0; s < 3; ++s) {
+    for (int s = 0; s < 4; ++s) {
       mbar_init(&sh->s_full[s], 1);
       mbar_init(&sh->p_full[s], 128);   // per score buffer: a group may finish two blocks before the issuer looks
     }
@@ -173,7 +175,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 #pragma unroll 1
       while (true) {
       if (j < tp.nblk) {
-        const uint32_t s_tm = lane_base + sbuf * 128;
+        const uint32_t s_tm = lane_base + sbuf * s_stride;
         uint64_t* const p_bar = &sh->p_full[sbuf];
         wait_spin(&sh->s_full[sbuf], spar);
         sbuf += 2;                                // two positions on in the ring of nsb buffers
@@ -431,7 +433,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         if (ok) {
           tc_fence_after();
           if (elect_one()) {
-            const uint32_t pa = tmem + p_buf * 128, od = tmem + o_base + p_grp * o_cols;
+            const uint32_t pa = tmem + p_buf * s_stride, od = tmem + o_base + p_grp * o_cols;
             uint64_t vd = v_desc0 + (uint64_t)(p_stage * v_stage16);
             uint32_t acc = first ? 0u : 1u;
 #pragma unroll 1
@@ -462,7 +464,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         if (ok) {
           tc_fence_after();
           if (elect_one()) {
-            const uint32_t sd = tmem + s_buf * 128;
+            const uint32_t sd = tmem + s_buf * s_stride;
             uint64_t qd = q_desc0 + (uint64_t)(qb * (q_bytes >> 4)), kd = k_desc0 + (uint64_t)(s_stage * k_stage16);
             uint32_t acc = 0u;
 #pragma unroll 1
