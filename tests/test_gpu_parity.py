@@ -265,6 +265,47 @@ def test_ragged_grids_tensor_core_path(grid, w, dtype):
     assert_close(got, want, dtype, what=f"ragged {grid}")
 
 
+def test_random_shapes_tensor_core_vs_simt():
+    """48 seeded random shapes (grid, b_size, window, head dims, dtype, RoPE width, dropped indices): wherever
+    the tcgen05 kernels take the shape they must agree with the fp32-accumulate SIMT kernels (which the other
+    tests pin to the oracle) to within the 16-bit rounding of the outputs; nothing may hang or be non-finite."""
+    import random
+    rnd = random.Random(3)
+    n_tc = 0
+    for case in range(48):
+        th, tw = rnd.choice([5, 9, 16, 23, 31, 40, 47]), rnd.choice([6, 8, 13, 16, 24, 33, 50])
+        b = rnd.choice([1, 1, 1, 2, 4])
+        wr, wc = rnd.choice([0, 1, 2, 3, 6, 7, 12]), rnd.choice([0, 1, 2, 3, 6, 10])
+        dqk, dv = rnd.choice([64, 64, 128]), rnd.choice([64, 64, 128])
+        dtype = rnd.choice([torch.bfloat16, torch.float16])
+        H = rnd.choice([1, 2, 3])
+        R = rnd.choice([0, 8, 16, 32]) if dqk == 128 else rnd.choice([0, 8, 16])
+        N = th * tw * b
+        g = torch.Generator().manual_seed(100 + case)
+        q, k = (torch.randn(1, H, N, dqk, generator=g).to(dtype).to(DEV) for _ in range(2))
+        v, do = (torch.randn(1, H, N, dv, generator=g).to(dtype).to(DEV) for _ in range(2))
+        rope = None
+        if R:
+            idx = orc.encode_idx(th, tw * b)
+            idx[torch.rand(N, generator=g) < 0.05] = -1
+            rope = (idx.to(DEV), orc.make_cs_table(R, max(th, 2)).to(DEV), orc.make_cs_table(R, max(tw * b, 2)).to(DEV))
+        win, sc = (b, th, tw, wr, wc), dqk ** -0.5
+        what = f"case {case}: grid {th}x{tw} b{b} w({wr},{wc}) d{dqk}/{dv} {dtype} R{R}"
+        if swa.selected_impl(q, v, rope, *win, sc, which=2, impl="auto") != "tc":
+            continue
+        n_tc += 1
+        o1, l1 = swa.swa_forward(q, k, v, rope, *win, sc, impl="simt")
+        g1 = swa.swa_backward(q, k, v, o1, l1, do, rope, *win, sc, impl="simt")
+        o2, _ = swa.swa_forward(q, k, v, rope, *win, sc, impl="tc")
+        g2 = swa.swa_backward(q, k, v, o1, l1, do, rope, *win, sc, impl="tc")
+        swa.check_status()
+        for a, c, n in zip((o1, *g1), (o2, *g2), ("o", "dq", "dk", "dv")):
+            assert torch.isfinite(c.float()).all(), f"{what} {n}: non-finite"
+            err = (a.float() - c.float()).abs().max().item()
+            assert err < 4e-2, f"{what} {n}: max abs {err:.3e}"
+    assert n_tc >= 30
+
+
 def test_host_pipeline_matches_direct_calls():
     """Chunked, stream-pipelined host-buffer path (uneven last chunk, buffers reused) == direct calls, bitwise."""
     from dl_templates_b200.host_pipeline import HostPipeline
