@@ -110,11 +110,12 @@ bool make_plan_shape(const swa_geom_t* g, int which, int TH, int TW, uint32_t ta
   const uint32_t stage_extra = which == 0 ? 0u : 1024u;       // lse / delta slots of a streamed block
   const int acc_cols = which == 0 ? 0 : (which == 1 ? 64 * qch : 64 * (qch + vch));
   const int min_stages = 3;
-  for (int nsb = 2; nsb >= 1; --nsb) {
+  {
+    // backward: two (S, dP) pairs of 2N columns next to the accumulators (N = 64 always fits: 256 + 256 columns)
+    const int nsb = 2;
     int nmax = which == 0 ? 128 : (512 - acc_cols) / (2 * nsb);
     nmax = nmax > 128 ? 128 : nmax;
     nmax = env_int("SWA_TC_NMAX", nmax);
-    // the forward kernel always double-buffers its query tile
     for (int nxb = which == 0 ? 2 : env_int("SWA_TC_NXB", 2); nxb >= (which == 0 ? 2 : 1); --nxb) {
       const uint32_t fixed = nxb * x_bytes + 128u * kXRowBytes + tab_bytes;
       long best_cost = -1;
@@ -157,7 +158,6 @@ bool make_plan_shape(const swa_geom_t* g, int which, int TH, int TW, uint32_t ta
       *out = pl;
       return pl.smem_bytes <= kSmemLimit && pl.N % 16 == 0 && pl.N <= nmax && pl.stages >= 2;
     }
-    if (which == 0) break;
   }
   return false;
 }

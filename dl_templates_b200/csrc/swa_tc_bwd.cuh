@@ -75,7 +75,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ C
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const Plan& pl = p.pl;
-  const int N = pl.N, nsb = pl.nsb, nxb = pl.nxb;
+  const int N = pl.N, nxb = pl.nxb;
+  constexpr int nsb = 2;                                         // (S, dP) buffer pairs; the planner sizes N so that two fit
   const uint32_t blk_bytes = (uint32_t)N * 128u;               // one 64-wide chunk of a streamed block
   const uint32_t xqk_bytes = p.qch * 16384u, xv_bytes = p.vch * 16384u, x_bytes = xqk_bytes + xv_bytes;
   const uint32_t yqk_stage = blk_bytes * p.qch, yv_stage = blk_bytes * p.vch;
@@ -153,10 +154,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ C
     const float c2 = p.scale_log2;
     const int ng = N >> 4;
     uint32_t gbase = 0, own_next = g;
-    // this group's next block: buffer pair, its parity, stage of the ring and its parity
-    // (two pairs: group g owns pair g, every block flips its parity; one pair: both groups alternate
-    // on it, so the blocks of group g always wait for parity g)
-    int buf = nsb == 2 ? g : 0, buf_par = nsb == 2 ? 0 : g;
+    // this group's next block: buffer pair (group g owns pair g, every block flips its parity), stage of
+    // the ring and its parity
+    const int buf = g;
+    int buf_par = 0;
     int stage = g % pl.stages, stage_par = (g / pl.stages) & 1;
     using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
     // (cos, sin) of NP consecutive pairs starting at pair `first` of table row `pos` (row or column table):
@@ -219,7 +220,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ C
         const float* vec = vec_smem + stage * 256;
         if (DKDV) wait_spin(&sh->y_ready[stage], stage_par, 8);   // -lse / delta of the block's queries are staged
         // advance by two positions in the rings
-        if (nsb == 2) buf_par ^= 1;
+        buf_par ^= 1;
         stage += 2;
         if (stage >= pl.stages) { stage -= pl.stages; stage_par ^= 1; }
         const int blk_first = tp.hr_first + j * pl.KR, blk_last = blk_first + pl.KR - 1;
