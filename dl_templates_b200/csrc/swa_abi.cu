@@ -97,6 +97,15 @@ int swa_select_impl(const swa_geom_t* g, const swa_rope_t* rope, int32_t which) 
   return resolve_impl(g, rope, nullptr, 0, which);
 }
 
+int swa_describe_plan(const swa_geom_t* g, const swa_rope_t* rope, int32_t which, int32_t* out) {
+  if (int e = check_geom(g)) return e;
+  if (int e = check_rope(g, rope)) return e;
+  if (!out || which < 0 || which > 2) return fail(E_NULL, "swa_describe_plan: out is NULL or `which` not in 0..2");
+  if (swa::tc::unsupported_reason(g, rope, nullptr, 0, which) != nullptr || !swa::tc::describe_plan(g, rope, which, out))
+    return fail(E_SHAPE, "the tensor-core kernels do not take this shape");
+  return 0;
+}
+
 int swa_fwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
             const swa_tensor_t* v, const swa_tensor_t* o, float* lse, int32_t* status, void* stream) {
   if (int e = check_geom(g)) return e;

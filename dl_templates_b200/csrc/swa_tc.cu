@@ -250,6 +250,30 @@ const char* unsupported_reason(const swa_geom_t* g, const swa_rope_t* rope, cons
   return nullptr;
 }
 
+bool describe_plan(const swa_geom_t* g, const swa_rope_t* rope, int which, int32_t* out) {
+  Plan pl;
+  if (!make_plan(g, rope, which, &pl)) return false;
+  const uint32_t qch = g->d_qk / 64, vch = g->d_v / 64, N = pl.N;
+  uint32_t used = 1023, tmem = 0;   // worst-case pad to the 1024-byte alignment of the swizzled tiles
+  if (which == 0) {
+    used += 2 * qch * 16384u + 128u * kXRowBytes + pl.stages * N * ((qch + vch) * 128u + kXRowBytes);
+    used += ((uint32_t)sizeof(FwdShared) + 15u) & ~15u;
+    const uint32_t o_cols = vch * 64u;
+    const uint32_t stride = (pl.nsb * 128u + 2 * o_cols <= 512u) ? 128u : N;
+    tmem = pl.nsb * stride + 2 * o_cols;
+    if (stride < N) tmem = 1u << 30;   // a score buffer would not hold a block
+  } else {
+    used += pl.nxb * (qch + vch) * 16384u + 128u * kXRowBytes + pl.stages * (N * ((qch + vch) * 128u + kXRowBytes) + 1024u);
+    used += ((uint32_t)sizeof(BwdShared) + 15u) & ~15u;
+    tmem = 2 * 2 * N + 64u * qch + (which == 2 ? 64u * vch : 0u);
+  }
+  used += pl.tab_bytes;
+  const int32_t v[12] = {pl.TH, pl.TW, pl.KR, pl.KW, pl.N, pl.stages, which == 0 ? pl.nsb : 2, which == 0 ? 2 : pl.nxb,
+                         (int32_t)pl.tab_bytes, (int32_t)pl.smem_bytes, (int32_t)used, (int32_t)tmem};
+  for (int i = 0; i < 12; ++i) out[i] = v[i];
+  return true;
+}
+
 int launch_fwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
                const swa_tensor_t* v, const swa_tensor_t* o, float* lse, int32_t* status, cudaStream_t st) {
   Plan pl;

@@ -12,6 +12,12 @@ const char* unsupported_reason(const swa_geom_t* g, const swa_rope_t* rope, cons
                                int n_tensors, int which);
 const char* last_error();
 
+// Resource plan the tensor-core kernel `which` would run with (host-only, no GPU needed): out[0..11] =
+// TH, TW, KR, KW, N, stages, score buffers (forward) / buffer pairs (backward), resident-tile buffers,
+// staged-table bytes, dynamic shared memory requested, shared memory the kernel's layout really uses
+// (with the worst-case alignment pad), tensor-memory columns used.  Returns false when no plan fits.
+bool describe_plan(const swa_geom_t* g, const swa_rope_t* rope, int which, int32_t* out);
+
 int launch_fwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
                const swa_tensor_t* v, const swa_tensor_t* o, float* lse, int32_t* status, cudaStream_t st);
 int launch_dq(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,

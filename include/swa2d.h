@@ -127,6 +127,14 @@ int swa_bwd_noalloc(const swa_geom_t* g, const swa_rope_t* rope, const swa_tenso
  * geometry: SWA_IMPL_SIMT or SWA_IMPL_TC (negative = rejected). `which`: 0 fwd, 1 dq, 2 dkdv. */
 int swa_select_impl(const swa_geom_t* g, const swa_rope_t* rope, int32_t which);
 
+/* Resource plan of the tensor-core kernel `which` (0 fwd, 1 dq, 2 dkdv) for this geometry; host-only, needs no
+ * GPU.  A diagnostic without counterpart in the reference: tests use it to check that every plan stays inside
+ * 227 KB of shared memory and 512 tensor-memory columns.  out[12] = tile rows, tile columns, block rows, block
+ * columns, block tokens N, ring stages, score buffers (fwd) or (S, dP) pairs (bwd), resident-tile buffers,
+ * staged cos/sin table bytes, dynamic shared memory requested, shared memory used by the layout (worst-case
+ * alignment pad included), tensor-memory columns used.  Negative return: the shape runs on the SIMT kernels. */
+int swa_describe_plan(const swa_geom_t* g, const swa_rope_t* rope, int32_t which, int32_t* out);
+
 /* Number of kernel launches this library has enqueued from the calling process. */
 int64_t swa_launch_count(void);
 

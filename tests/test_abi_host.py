@@ -103,3 +103,55 @@ def test_bh_range_partitions():
     x = torch.arange(2 * 3 * 4 * 5).reshape(2, 3, 4, 5)
     parts = [shard_bh(x, r, 4) for r in range(4)]
     assert torch.equal(torch.cat([p.squeeze(0) for p in parts]), x.reshape(6, 4, 5))
+
+
+def _plan(g, r, which):
+    out = (C.c_int32 * 12)()
+    code = _lib.lib.swa_describe_plan(C.byref(g), None if r is None else C.byref(r), which, out)
+    return code, list(out)
+
+
+def test_every_tile_plan_fits_shared_and_tensor_memory():
+    """Sweep geometries through the planner (host only) and check the resource invariants the kernels rely on:
+    the layout fits the dynamic shared memory it asks for, that stays within 227 KB, tensor memory within its
+    512 columns, blocks are multiples of 16 tokens of at most 128, and the ring has at least two stages."""
+    idx = torch.zeros(16, dtype=torch.int32)
+    n_plans = 0
+    for d_qk, d_v in ((64, 64), (128, 64), (64, 128), (128, 128)):
+        for n_rdim, max_hw in ((0, 0), (8, 16), (16, 128), (32, 128), (32, 1024)):
+            if 4 * n_rdim > d_qk:
+                continue
+            r = None
+            if n_rdim:
+                tab = torch.zeros(max_hw, n_rdim, 2)
+                r = _lib.make_rope(idx, tab, tab)
+            for (th, tw, bs) in ((128, 128, 1), (32, 32, 1), (16, 16, 4), (24, 40, 1), (9, 7, 2), (64, 16, 2)):
+                for (rs, cs) in ((1, 1), (3, 3), (6, 6), (13, 13), (2, 9), (20, 4)):
+                    for dt in (torch.bfloat16, torch.float16):
+                        g = _geom(dtype=dt, b_size=bs, t_height=th, t_width=tw, row_size=rs, col_size=cs, d_qk=d_qk,
+                                  d_v=d_v)
+                        for which in (0, 1, 2):
+                            code, p = _plan(g, r, which)
+                            if code != 0:
+                                assert _lib.lib.swa_select_impl(C.byref(g), None if r is None else C.byref(r),
+                                                                which) != _lib.IMPL_TC
+                                continue
+                            th_, tw_, kr, kw, n, stages, nsb, nxb, tab_b, req, used, tmem = p
+                            what = (d_qk, d_v, n_rdim, max_hw, th, tw, bs, rs, cs, which, p)
+                            assert th_ * tw_ == 128 and th_ + tw_ <= 32, what
+                            assert n == kr * kw and n % 16 == 0 and 16 <= n <= 128, what
+                            assert 2 <= stages <= 8 and 2 <= nsb <= 4 and 1 <= nxb <= 2, what
+                            assert used <= req <= 227 * 1024, what
+                            assert tmem <= 512, what
+                            assert (tab_b > 0) <= (n_rdim > 0), what
+                            n_plans += 1
+    assert n_plans > 500
+
+
+def test_describe_plan_rejects_bad_arguments():
+    g = _geom()
+    assert _lib.lib.swa_describe_plan(C.byref(g), None, 0, None) < 0
+    out = (C.c_int32 * 12)()
+    assert _lib.lib.swa_describe_plan(C.byref(g), None, 3, out) < 0
+    g32 = _geom(dtype=torch.float32)
+    assert _lib.lib.swa_describe_plan(C.byref(g32), None, 0, out) < 0   # fp32 runs on the SIMT kernels
