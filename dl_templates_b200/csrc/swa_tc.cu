@@ -93,7 +93,7 @@ int halo_width(const swa_geom_t* g, int TW) {
 
 // Choose the resident tile, the streamed-block shape and the pipeline depths.  Tile shapes tried: 16 x 8 first -- a warp's 32 rows then span
 // 4 grid rows and skip 3 of the 7 streamed blocks of a 13-row window -- then 8 x 16.
-//   tensor memory (512 columns): forward  score buffers at 128-column strides + two O accumulators (N <= 128);
+//   tensor memory (512 columns): forward  score buffers at 128-column strides (packed when they do not fit) + two O accumulators;
 //                                backward nsb pairs (S, dP) of 2N columns + the accumulators
 //   shared memory:               nxb resident-tile buffers + indicator rows + stages x (block + penalty rows [+ lse, delta])
 bool make_plan_shape(const swa_geom_t* g, int which, int TH, int TW, uint32_t tab_bytes, Plan* out) {
@@ -156,7 +156,12 @@ bool make_plan_shape(const swa_geom_t* g, int which, int TH, int TW, uint32_t ta
         pl.nsb = nsb;
       }
       *out = pl;
-      return pl.smem_bytes <= kSmemLimit && pl.N % 16 == 0 && pl.N <= nmax && pl.stages >= 2;
+      // tensor-memory columns of the final plan (the environment overrides above included): a plan beyond the
+      // 512-column allocation is refused here, never launched
+      const uint32_t fwd_stride = (pl.N <= 128 && pl.nsb * 128 + 2 * 64 * vch <= 512) ? 128u : (uint32_t)pl.N;
+      const uint32_t tmem_cols = which == 0 ? pl.nsb * fwd_stride + 2u * 64u * vch : 2u * nsb * pl.N + (uint32_t)acc_cols;
+      return pl.smem_bytes <= kSmemLimit && pl.N % 16 == 0 && pl.N >= 16 && pl.N <= 256 && pl.N <= nmax && pl.stages >= 2 &&
+             pl.stages <= kMaxStages && pl.nsb >= 2 && pl.nsb <= 4 && tmem_cols <= 512u;
     }
   }
   return false;
@@ -259,7 +264,7 @@ bool describe_plan(const swa_geom_t* g, const swa_rope_t* rope, int which, int32
     used += 2 * qch * 16384u + 128u * kXRowBytes + pl.stages * N * ((qch + vch) * 128u + kXRowBytes);
     used += ((uint32_t)sizeof(FwdShared) + 15u) & ~15u;
     const uint32_t o_cols = vch * 64u;
-    const uint32_t stride = (pl.nsb * 128u + 2 * o_cols <= 512u) ? 128u : N;
+    const uint32_t stride = (N <= 128u && pl.nsb * 128u + 2 * o_cols <= 512u) ? 128u : N;
     tmem = pl.nsb * stride + 2 * o_cols;
     if (stride < N) tmem = 1u << 30;   // a score buffer would not hold a block
   } else {

@@ -73,7 +73,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   // ready when it has finished one (2 to 4, chosen by the planner)
   const int nsb = pl.nsb;
   // score buffer b at column s_stride*b (128-column strides when they fit, else packed), O_g behind them
-  const uint32_t s_stride = (nsb * 128u + 2 * o_cols <= kFwdTmemCols) ? 128u : (uint32_t)N;
+  const uint32_t s_stride = (N <= 128 && nsb * 128u + 2 * o_cols <= kFwdTmemCols) ? 128u : (uint32_t)N;
   const uint32_t o_base = nsb * s_stride;
   uint8_t* q_smem = smem;                                        // two buffers
   uint8_t* qx_smem = q_smem + 2 * q_bytes;                      // window-mask indicator rows of a query tile

@@ -155,3 +155,24 @@ def test_describe_plan_rejects_bad_arguments():
     assert _lib.lib.swa_describe_plan(C.byref(g), None, 3, out) < 0
     g32 = _geom(dtype=torch.float32)
     assert _lib.lib.swa_describe_plan(C.byref(g32), None, 0, out) < 0   # fp32 runs on the SIMT kernels
+
+
+def test_planner_refuses_overrides_beyond_tensor_memory(monkeypatch):
+    """The experiment knobs cannot produce a plan that overflows the 512 tensor-memory columns or the barrier
+    arrays: such a plan is refused on the host instead of being launched."""
+    g = _geom(t_height=128, t_width=128, row_size=6, col_size=6)
+    assert _plan(g, None, 1)[0] == 0
+    monkeypatch.setenv("SWA_TC_NMAX", "160")
+    monkeypatch.setenv("SWA_TC_KR", "8")
+    monkeypatch.setenv("SWA_TC_KW", "20")
+    monkeypatch.setenv("SWA_TC_TH", "16")
+    assert _plan(g, None, 1)[0] < 0 and _plan(g, None, 2)[0] < 0      # 2 pairs x 2 x 160 columns do not fit
+    monkeypatch.setenv("SWA_TC_NSB", "2")
+    code, p = _plan(g, None, 0)                                          # forward: 2 x 160 + 128 columns fit
+    assert code == 0 and p[4] == 160 and p[11] == 448
+    monkeypatch.setenv("SWA_TC_NSB", "3")
+    assert _plan(g, None, 0)[0] < 0
+    for k in ("SWA_TC_NMAX", "SWA_TC_KR", "SWA_TC_KW", "SWA_TC_NSB"):
+        monkeypatch.delenv(k)
+    monkeypatch.setenv("SWA_TC_STAGES", "9")
+    assert _plan(g, None, 0)[0] < 0
