@@ -207,6 +207,10 @@ def main():
     ap.add_argument("--bh-per-gpu", type=int, default=0, help="(batch*head) slices per GPU; 0 = the workload's B*H")
     ap.add_argument("--kernels", default="auto", choices=["auto", "simt", "tc"], help="kernel family to force")
     ap.add_argument("--rope-dims", type=int, default=-1, help="override the number of rotated q/k dims (0 = no RoPE)")
+    ap.add_argument("--layout", default="bhnd", choices=["bhnd", "packed"],
+                    help="bhnd: contiguous [B,H,N,d] tensors (the reference's layout, the default); packed: q,k,v as "
+                         "views of one [B,N,3,H,d] projection output, O and dO in [B,N,H*d], gradients into one "
+                         "packed buffer (kernel timing only, no e2e leg)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--e2e-chunk", type=int, default=32, help="(batch*head) slices per pipelined chunk of the e2e path")
@@ -258,6 +262,20 @@ def main():
     c = device_case(cfg, bh_local, device, seed=rank)
     q, k, v, do, rope, win, sm = c["q"], c["k"], c["v"], c["do"], c["rope"], c["win"], c["sm_scale"]
     impl = args.kernels
+    o_out = grads_out = None
+    if args.layout == "packed":
+        if cfg["d_qk"] != cfg["d_v"]:
+            raise SystemExit("--layout packed needs d_qk == d_v")
+        args.no_e2e = True
+        B_, H_, N_, d_ = q.shape
+        packed = torch.empty((B_, N_, 3, H_, d_), dtype=q.dtype, device=device)
+        for i, t in enumerate((q, k, v)):
+            packed[:, :, i].copy_(t.permute(0, 2, 1, 3))
+        q, k, v = (packed[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+        do = do.permute(0, 2, 1, 3).contiguous().permute(0, 2, 1, 3)
+        o_out = torch.empty((B_, N_, H_, d_), dtype=q.dtype, device=device).permute(0, 2, 1, 3)
+        dpacked = torch.empty_like(packed)
+        grads_out = tuple(dpacked[:, :, i].permute(0, 2, 1, 3) for i in range(3))
     fwd_f, bwd_f = windowed_flops(bh_local, cfg["grid"] ** 2, 1, half, half, cfg["d_qk"], cfg["d_v"])
     step_flops = fwd_f + (bwd_f if cfg["bwd"] else 0.0)
     stream = torch.cuda.current_stream(device)
@@ -269,11 +287,11 @@ def main():
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)] if record is not None else None
         if ev:
             ev[0].record(stream)
-        o, lse = swa.swa_forward(q, k, v, rope, *win, sm, impl=impl)
+        o, lse = swa.swa_forward(q, k, v, rope, *win, sm, impl=impl, out=o_out)
         if ev:
             ev[1].record(stream)
         if cfg["bwd"]:
-            out = swa_backward_timed(swa, _lib, q, k, v, o, lse, do, rope, win, sm, impl, ev, stream)
+            out = swa_backward_timed(swa, _lib, q, k, v, o, lse, do, rope, win, sm, impl, ev, stream, grads_out)
         else:
             out = (o,)
         if record is not None:
@@ -408,14 +426,14 @@ def main():
     return 0
 
 
-def swa_backward_timed(swa, _lib, q, k, v, o, lse, do, rope, win, sm, impl, ev, stream):
+def swa_backward_timed(swa, _lib, q, k, v, o, lse, do, rope, win, sm, impl, ev, stream, outs=None):
     """swa_backward with an event after each of its three launches (same calls, same order)."""
     if ev is None:
-        return (o,) + tuple(swa.swa_backward(q, k, v, o, lse, do, rope, *win, sm, impl=impl))
+        return (o,) + tuple(swa.swa_backward(q, k, v, o, lse, do, rope, *win, sm, impl=impl, out=outs))
     import ctypes as C
     from dl_templates_b200 import tiled_swa as ts
     B, H, N, _ = q.shape
-    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    dq, dk, dv = outs if outs is not None else (torch.empty_like(q), torch.empty_like(k), torch.empty_like(v))
     delta = torch.empty((B, H, N), dtype=torch.float32, device=q.device)
     g = ts._geom(q, v, *win, sm, impl)
     r = _lib.make_rope(*rope) if rope is not None else None
@@ -442,7 +460,9 @@ def workload_config(cfg, args, bh_local, world):
             "parallelism": f"batch*head sharded over {world} GPU(s), no collective",
             "l2": "inputs larger than L2 (no flush)" if bh_local * G * G * cfg["d_qk"] * 2 > 126e6 else
                   "inputs smaller than L2 (warm)",
-            "exact_pairs_per_head": exact_pairs(G, half), "counted_pairs_per_head": G * G * cfg["w"] ** 2}
+            "exact_pairs_per_head": exact_pairs(G, half), "counted_pairs_per_head": G * G * cfg["w"] ** 2,
+            "layout": "q,k,v views of [B,N,3,H,d]; O, dO [B,N,H*d]; packed gradient" if args.layout == "packed" else
+                      "[B,H,N,d] contiguous"}
 
 
 if __name__ == "__main__":

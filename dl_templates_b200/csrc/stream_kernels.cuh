@@ -35,10 +35,13 @@ __global__ void __launch_bounds__(256) delta_vec_kernel(View4 o, View4 d_o, floa
   if (row < total_rows && part == 0) delta[row] = acc;
 }
 
-// Same for fully contiguous o and do ([rows, d_v] row-major): no per-thread index decomposition.
-template <typename T>
+// Same for fully contiguous o and do: no per-thread index decomposition of the loads.  Head-major memory
+// ([B,H,N,d_v] row-major) writes delta[row]; TOKEN_MAJOR memory ([B,N,H,d_v] row-major, the layout next to an
+// output projection) is walked in memory order and row (b, n, h) writes delta[(b*H + h)*N + n].
+template <typename T, bool TOKEN_MAJOR = false>
 __global__ void __launch_bounds__(256) delta_flat_kernel(const T* __restrict__ o, const T* __restrict__ d_o,
-                                                         float* __restrict__ delta, int dv, int64_t total_rows) {
+                                                         float* __restrict__ delta, int dv, int64_t total_rows,
+                                                         int H = 1, int64_t N = 1) {
   const int tpr = dv >> 3;  // threads per row
   const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t row = gid / tpr;
@@ -52,7 +55,15 @@ __global__ void __launch_bounds__(256) delta_flat_kernel(const T* __restrict__ o
     for (int i = 0; i < 8; ++i) acc += to_f(pa[i]) * to_f(pb[i]);
   }
   for (int off = tpr >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-  if (row < total_rows && (gid - row * tpr) == 0) delta[row] = acc;
+  if (row < total_rows && (gid - row * tpr) == 0) {
+    if (TOKEN_MAJOR) {
+      const int64_t bn = row / H, h = row - bn * H;
+      const int64_t b = bn / N, n = bn - b * N;
+      delta[(b * H + h) * N + n] = acc;
+    } else {
+      delta[row] = acc;
+    }
+  }
 }
 
 // Element path: one warp per token, any dtype / stride / head dim.

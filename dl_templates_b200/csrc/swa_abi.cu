@@ -163,6 +163,18 @@ int swa_bwd_delta(const swa_geom_t* g, const swa_tensor_t* o, const swa_tensor_t
                                                                       (const __nv_bfloat16*)d_o->ptr, delta, dv, rows);
       return launch_ok("delta");
     }
+    auto token_major = [&](const swa_tensor_t* t) {   // [B,N,H,d_v] row-major seen as [B,H,N,d_v]
+      return t->stride[1] == dv && t->stride[2] == (int64_t)g->H * dv && (g->B == 1 || t->stride[0] == (int64_t)g->H * N * dv);
+    };
+    if (token_major(o) && token_major(d_o)) {
+      if (g->dtype == SWA_F16)
+        swa::delta_flat_kernel<__half, true><<<blocks, 256, 0, st>>>((const __half*)o->ptr, (const __half*)d_o->ptr, delta, dv,
+                                                                     rows, g->H, N);
+      else
+        swa::delta_flat_kernel<__nv_bfloat16, true><<<blocks, 256, 0, st>>>(
+            (const __nv_bfloat16*)o->ptr, (const __nv_bfloat16*)d_o->ptr, delta, dv, rows, g->H, N);
+      return launch_ok("delta");
+    }
     if (g->dtype == SWA_F16)
       swa::delta_vec_kernel<__half><<<blocks, 256, 0, st>>>(swa::make_view(o), swa::make_view(d_o), delta, g->H, N,
                                                             dv, rows);

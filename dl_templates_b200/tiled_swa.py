@@ -74,13 +74,24 @@ def _ref(x):
     return C.byref(x) if x is not None else None
 
 
-def swa_forward(q, k, v, rope, b_size, t_height, t_width, row_size, col_size, sm_scale, impl="auto"):
+def _check_out(t, shape, like, what):
+    if t.shape != shape or t.dtype != like.dtype or t.device != like.device:
+        raise ValueError(f"{what}: expected shape {tuple(shape)}, dtype {like.dtype} on {like.device}")
+
+
+def swa_forward(q, k, v, rope, b_size, t_height, t_width, row_size, col_size, sm_scale, impl="auto", out=None):
     """Launch the forward kernel; returns ``(o, lse)`` with ``lse`` fp32 ``[B,H,N]`` in
-    the base-2 domain.  ``rope`` is ``None`` or ``(idx, row_cs, col_cs)``."""
+    the base-2 domain.  ``rope`` is ``None`` or ``(idx, row_cs, col_cs)``.  ``out``: an
+    optional ``[B,H,N,d_v]`` tensor or strided view the kernel writes O into (e.g. a view
+    of a ``[B,N,H*d_v]`` buffer for the output projection)."""
     _check_inputs(q, k, v, b_size, t_height, t_width)
     B, H, N, _ = q.shape
     with torch.cuda.device(q.device):
-        o = torch.empty((B, H, N, v.shape[-1]), dtype=q.dtype, device=q.device)
+        if out is None:
+            o = torch.empty((B, H, N, v.shape[-1]), dtype=q.dtype, device=q.device)
+        else:
+            o = out
+            _check_out(o, (B, H, N, v.shape[-1]), q, "out")
         lse = torch.empty((B, H, N), dtype=torch.float32, device=q.device)
         g = _geom(q, v, b_size, t_height, t_width, row_size, col_size, sm_scale, impl)
         r = _lib.make_rope(*rope) if rope is not None else None
@@ -93,12 +104,20 @@ def swa_forward(q, k, v, rope, b_size, t_height, t_width, row_size, col_size, sm
     return o, lse
 
 
-def swa_backward(q, k, v, o, lse, do, rope, b_size, t_height, t_width, row_size, col_size, sm_scale, impl="auto"):
+def swa_backward(q, k, v, o, lse, do, rope, b_size, t_height, t_width, row_size, col_size, sm_scale, impl="auto",
+                 out=None):
     """Launch delta, dQ and dK/dV kernels; returns ``(dq, dk, dv)`` in the input dtype
-    (gradients of the un-rotated q and k when ``rope`` is given)."""
+    (gradients of the un-rotated q and k when ``rope`` is given).  ``out``: optional
+    ``(dq, dk, dv)`` tensors or strided views to write into (e.g. the three slices of one
+    packed ``[B,N,3,H,d]`` gradient buffer)."""
     B, H, N, _ = q.shape
     with torch.cuda.device(q.device):
-        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        if out is None:
+            dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        else:
+            dq, dk, dv = out
+            for t, like, what in ((dq, q, "dq"), (dk, k, "dk"), (dv, v, "dv")):
+                _check_out(t, like.shape, like, what)
         delta = torch.empty((B, H, N), dtype=torch.float32, device=q.device)
         g = _geom(q, v, b_size, t_height, t_width, row_size, col_size, sm_scale, impl)
         r = _lib.make_rope(*rope) if rope is not None else None
@@ -203,3 +222,49 @@ class TiledSwaRope2D(torch.autograd.Function):
         rope = tuple(saved[5:8]) if len(saved) == 8 else None
         dq, dk, dv = swa_backward(q, k, v, o, lse, do, rope, *ctx.win)
         return (dq, dk, dv) + (None,) * 9
+
+
+class TiledSwaPackedQKV(torch.autograd.Function):
+    """The op between a packed QKV projection and the output projection, without the
+    permute / contiguous copies either side of it.
+
+    ``TiledSwaPackedQKV.apply(qkv, idx, row_cs_buffer, col_cs_buffer, b_size, t_height,
+    t_width, row_size, col_size, sm_scale)`` takes ``qkv [B, N, 3, H, d]`` -- the output of
+    one ``Linear(C, 3*H*d)`` viewed, the layout the reference's RoPE self-test slices its
+    strided q and k from (src/fused_rope2d.py:259-262) -- and returns ``o [B, N, H*d]``,
+    the layout the output projection consumes.  The kernels read q, k, v through strided
+    tensor maps and write O, and in backward the three slices of one packed
+    ``[B, N, 3, H, d]`` gradient, in place; ``idx`` may be ``None`` (no rotation).
+    Same mathematics as ``TiledSwaRope2D`` on the permuted views.
+    """
+
+    @staticmethod
+    def forward(ctx, qkv, idx: Optional[torch.Tensor], row_cs_buffer, col_cs_buffer, b_size: int, t_height: int,
+                t_width: int, row_size: int, col_size: int, sm_scale: float):
+        if qkv.dim() != 5 or qkv.shape[2] != 3:
+            raise ValueError("expected qkv [B, N, 3, H, d]")
+        B, N, _, H, d = qkv.shape
+        q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+        rope = None if idx is None else (idx, row_cs_buffer, col_cs_buffer)
+        o_buf = torch.empty((B, N, H, d), dtype=qkv.dtype, device=qkv.device)
+        _, lse = swa_forward(q, k, v, rope, b_size, t_height, t_width, row_size, col_size, sm_scale,
+                             out=o_buf.permute(0, 2, 1, 3))
+        saved = (qkv, lse, o_buf) if rope is None else (qkv, lse, o_buf, idx, row_cs_buffer, col_cs_buffer)
+        ctx.save_for_backward(*saved)
+        ctx.win = (b_size, t_height, t_width, row_size, col_size, sm_scale)
+        return o_buf.view(B, N, H * d)
+
+    @staticmethod
+    def backward(ctx, do):
+        saved = ctx.saved_tensors
+        qkv, lse, o_buf = saved[:3]
+        rope = tuple(saved[3:6]) if len(saved) == 6 else None
+        B, N, _, H, d = qkv.shape
+        if do.stride(-1) != 1 or do.stride(1) % 8 or do.stride(0) % 8 or do.data_ptr() % 16:
+            do = do.contiguous()
+        do4 = do.view(B, N, H, d).permute(0, 2, 1, 3)
+        q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+        dqkv = torch.empty((B, N, 3, H, d), dtype=qkv.dtype, device=qkv.device)
+        outs = tuple(dqkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+        swa_backward(q, k, v, o_buf.permute(0, 2, 1, 3), lse, do4, rope, *ctx.win, out=outs)
+        return (dqkv,) + (None,) * 9

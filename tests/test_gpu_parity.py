@@ -321,3 +321,42 @@ def test_host_pipeline_matches_direct_calls():
     swa.check_status()
     for got, want in zip(outs, direct):
         assert torch.equal(got.float(), want)
+
+
+@pytest.mark.parametrize("with_rope", [True, False])
+def test_packed_qkv_entry(with_rope):
+    """qkv [B, N, 3, H, d] in, o [B, N, H*d] out, packed gradient back: against the oracle, and bit-identical to
+    the [B, H, N, d] entry on contiguous copies (same kernels, same arithmetic order)."""
+    torch.manual_seed(3)
+    B, H, TH, TW, d = 2, 3, 20, 24, 64
+    N = TH * TW
+    qkv = torch.randn(B, N, 3, H, d).to(torch.bfloat16)
+    do = torch.randn(B, N, H * d).to(torch.bfloat16)
+    win = (1, TH, TW, 3, 2)
+    rope_cpu = rope_dev = (None, None, None)
+    if with_rope:
+        idx = swa.FusedInplaceRotaryPositionEncoding2D.encode_idx(TH, TW)
+        idx[torch.rand(N) < 0.1] = -1
+        tr, tc = swa.make_cs_table(16, TH), swa.make_cs_table(16, TW)
+        rope_cpu = (idx, tr, tc)
+        rope_dev = tuple(t.to(DEV) for t in rope_cpu)
+    x = qkv.to(DEV).requires_grad_(True)
+    o = swa.TiledSwaPackedQKV.apply(x, *rope_dev, *win, 0.125)
+    assert o.shape == (B, N, H * d) and o.is_contiguous()
+    o.backward(do.to(DEV))
+    swa.check_status()
+    assert x.grad.shape == qkv.shape and x.grad.is_contiguous()
+    q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3).float() for i in range(3))
+    do4 = do.view(B, N, H, d).permute(0, 2, 1, 3).float()
+    want = orc.fused_ref(q, k, v, do4, *rope_cpu, *win, 0.125)
+    got = [o.detach().view(B, N, H, d).permute(0, 2, 1, 3).float().cpu()]
+    got += [x.grad[:, :, i].permute(0, 2, 1, 3).float().cpu() for i in range(3)]
+    assert_close(got, want, torch.bfloat16, what="packed qkv")
+    # the same problem through the [B, H, N, d] entry
+    qc, kc, vc = (qkv[:, :, i].permute(0, 2, 1, 3).contiguous().to(DEV).requires_grad_(True) for i in range(3))
+    assert swa.selected_impl(qc, vc, rope_dev if with_rope else None, *win) == "tc"
+    o2 = swa.TiledSwaRope2D.apply(qc, kc, vc, *rope_dev, *win, 0.125)
+    o2.backward(do.view(B, N, H, d).permute(0, 2, 1, 3).contiguous().to(DEV))
+    swa.check_status()
+    for a, b in zip(got, (o2.detach(), qc.grad, kc.grad, vc.grad)):
+        assert torch.equal(a, b.float().cpu())
