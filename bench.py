@@ -127,6 +127,29 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def bind_host_thread_near_gpu(cuda_index):
+    """Pin this process to the CPU cores NVML lists as local to the GPU, so that the pinned host buffers of
+    the end-to-end leg are allocated on the GPU's own NUMA node.  A setting of this process only (nothing on
+    the GPU changes); returns the number of cores bound to, or None when NVML or the topology says nothing."""
+    if os.environ.get("SWA_BENCH_NO_AFFINITY"):
+        return None
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        pr = torch.cuda.get_device_properties(cuda_index)
+        bus = f"{pr.pci_domain_id:08x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+        h = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        ideal = {64 * i + b for i, w in enumerate(words) for b in range(64) if (int(w) >> b) & 1}
+        cpus = ideal & os.sched_getaffinity(0)
+        if not cpus or cpus == os.sched_getaffinity(0):
+            return None
+        os.sched_setaffinity(0, cpus)
+        return len(cpus)
+    except Exception:
+        return None
+
+
 # --------------------------------------------------------------------------------------------
 # CPU arm: the oracle's SDPA form (the reference's own CPU path) on a bounded sample
 # --------------------------------------------------------------------------------------------
@@ -337,6 +360,7 @@ def main():
     e2e = None
     if not args.no_e2e:
         from dl_templates_b200.host_pipeline import HostPipeline
+        near_cpus = bind_host_thread_near_gpu(local_rank)
         host_in = [x.cpu().pin_memory() for x in (q, k, v, do)]
         n_out = 4 if cfg["bwd"] else 1
         host_out = [torch.empty_like(x, device="cpu").pin_memory() for x in ((v, q, k, v) if cfg["bwd"] else (v,))]
@@ -363,7 +387,7 @@ def main():
         e2e = {"value": step_flops * world / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
                "h2d_bytes_per_step": sum(x.numel() * x.element_size() for x in host_in),
                "d2h_bytes_per_step": sum(x.numel() * x.element_size() for x in host_out[:n_out]),
-               "ms_per_step": ms_e2e, "steps": e2e_steps}
+               "ms_per_step": ms_e2e, "steps": e2e_steps, "host_cpus_near_gpu": near_cpus}
         del host_in, host_out, pipe
 
     # ---------------------------------------------------------------- optional verification gather
