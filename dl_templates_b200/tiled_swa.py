@@ -74,6 +74,34 @@ def _ref(x):
     return C.byref(x) if x is not None else None
 
 
+def padded_head_dims(q, v, rope, b_size, t_height, t_width, row_size, col_size, sm_scale=1.0, impl="auto"):
+    """``(d_qk', d_v')`` if zero-padding the head dims to 64 or 128 moves this problem from the SIMT kernels to
+    the tensor-core kernels, else ``None``.  Padding q and k with zero columns leaves every score unchanged,
+    padding v adds zero columns to O; the reference's own test shape (d = 32, b_size = 16,
+    src/tiled_swa.py:736-746) is the case this exists for."""
+    if impl != "auto" or q.dtype == torch.float32 or os.environ.get("SWA_NO_HEAD_PAD"):
+        return None
+
+    def up(d):
+        return d if d in (64, 128) else 64 if d < 64 else 128 if d < 128 else None
+
+    d_qk, d_v = q.shape[-1], v.shape[-1]
+    p_qk, p_v = up(d_qk), up(d_v)
+    if p_qk is None or p_v is None or (p_qk == d_qk and p_v == d_v):
+        return None
+    B, H, _, _ = q.shape
+    g = _lib.make_geom(q.dtype, B, H, b_size, t_height, t_width, row_size, col_size, p_qk, p_v, sm_scale, "auto")
+    r = _lib.make_rope(*rope) if rope is not None else None
+    for which in (0, 1, 2):
+        if _lib.lib.swa_select_impl(C.byref(g), _ref(r), which) != _lib.IMPL_TC:
+            return None
+    return p_qk, p_v
+
+
+def _pad_last(t, d):
+    return t if t.shape[-1] == d else torch.nn.functional.pad(t, (0, d - t.shape[-1]))
+
+
 def _check_out(t, shape, like, what):
     if t.shape != shape or t.dtype != like.dtype or t.device != like.device:
         raise ValueError(f"{what}: expected shape {tuple(shape)}, dtype {like.dtype} on {like.device}")
@@ -86,6 +114,16 @@ def swa_forward(q, k, v, rope, b_size, t_height, t_width, row_size, col_size, sm
     of a ``[B,N,H*d_v]`` buffer for the output projection)."""
     _check_inputs(q, k, v, b_size, t_height, t_width)
     B, H, N, _ = q.shape
+    pad = padded_head_dims(q, v, rope, b_size, t_height, t_width, row_size, col_size, sm_scale, impl)
+    if pad is not None:
+        o_p, lse = swa_forward(_pad_last(q, pad[0]), _pad_last(k, pad[0]), _pad_last(v, pad[1]), rope, b_size, t_height,
+                               t_width, row_size, col_size, sm_scale, impl)
+        o_v = o_p[..., :v.shape[-1]]
+        if out is None:
+            return o_v.contiguous(), lse
+        _check_out(out, o_v.shape, q, "out")
+        out.copy_(o_v)
+        return out, lse
     with torch.cuda.device(q.device):
         if out is None:
             o = torch.empty((B, H, N, v.shape[-1]), dtype=q.dtype, device=q.device)
@@ -111,6 +149,17 @@ def swa_backward(q, k, v, o, lse, do, rope, b_size, t_height, t_width, row_size,
     ``(dq, dk, dv)`` tensors or strided views to write into (e.g. the three slices of one
     packed ``[B,N,3,H,d]`` gradient buffer)."""
     B, H, N, _ = q.shape
+    pad = padded_head_dims(q, v, rope, b_size, t_height, t_width, row_size, col_size, sm_scale, impl)
+    if pad is not None:
+        grads = swa_backward(_pad_last(q, pad[0]), _pad_last(k, pad[0]), _pad_last(v, pad[1]), _pad_last(o, pad[1]), lse,
+                             _pad_last(do, pad[1]), rope, b_size, t_height, t_width, row_size, col_size, sm_scale, impl)
+        grads = tuple(g[..., :like.shape[-1]] for g, like in zip(grads, (q, k, v)))
+        if out is None:
+            return tuple(g.contiguous() for g in grads)
+        for t, g, what in zip(out, grads, ("dq", "dk", "dv")):
+            _check_out(t, g.shape, q, what)
+            t.copy_(g)
+        return tuple(out)
     with torch.cuda.device(q.device):
         if out is None:
             dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)

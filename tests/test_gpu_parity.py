@@ -360,3 +360,27 @@ def test_packed_qkv_entry(with_rope):
     swa.check_status()
     for a, b in zip(got, (o2.detach(), qc.grad, kc.grad, vc.grad)):
         assert torch.equal(a, b.float().cpu())
+
+
+def test_reference_selftest_shape_runs_on_tensor_cores():
+    """The shape of the reference's own self-test (src/tiled_swa.py:736-746: fp16, d = 32, 4x4-pixel tiles so
+    b_size = 16, 16 x 16 tiles, one tile of reach) reaches the tensor-core kernels through zero-padded head dims;
+    results against the oracle and against the SIMT kernels on the unpadded tensors."""
+    torch.manual_seed(0)
+    B, H, d, bs, TH, TW = 1, 2, 32, 16, 16, 16
+    N = bs * TH * TW
+    q, k, v, do = (torch.randn(B, H, N, d).to(torch.float16) for _ in range(4))
+    win = (bs, TH, TW, 1, 1)
+    qd, kd, vd = (t.to(DEV).requires_grad_(True) for t in (q, k, v))
+    assert swa.padded_head_dims(qd, vd, None, *win, 1.0) == (64, 64)
+    assert swa.selected_impl(qd, vd, None, *win) == "simt"          # the unpadded problem itself is not eligible
+    o = swa.TiledSwa.apply(qd, kd, vd, *win, 1.0)
+    o.backward(do.to(DEV))
+    swa.check_status()
+    got = [t.detach().float().cpu() for t in (o, qd.grad, kd.grad, vd.grad)]
+    for t in got:
+        assert t.shape == q.shape
+    want = orc.fused_ref(q.float(), k.float(), v.float(), do.float(), None, None, None, *win, 1.0)
+    assert_close(got, want, torch.float16, what="self-test shape")
+    simt, _ = run_gpu(q, k, v, do, None, win, 1.0, impl="simt")
+    assert_close(got, simt, torch.float16, what="self-test shape vs simt")
