@@ -390,6 +390,43 @@ def main():
                "ms_per_step": ms_e2e, "steps": e2e_steps, "host_cpus_near_gpu": near_cpus}
         del host_in, host_out, pipe
 
+    # ---------------------------------------------------------------- the un-fused composition, for comparison
+    # What the reference does (src/fused_rope2d.py:126-168 then src/tiled_swa.py:604): rotate q and k in place with
+    # the stand-alone kernel, attention without RoPE, inverse rotation of dq and dk in place.  Runs last because it
+    # overwrites q and k (rotating them again each step, which keeps their scale).
+    prerot = None
+    if rope is not None and args.layout == "bhnd" and not os.environ.get("SWA_BENCH_NO_VARIANTS"):
+        def flat(x):
+            return x.view(-1, x.shape[2], x.shape[3])
+
+        def prerot_step():
+            swa.rope2d_apply_(flat(q), *rope)
+            swa.rope2d_apply_(flat(k), *rope)
+            o, lse = swa.swa_forward(q, k, v, None, *win, sm, impl=impl)
+            if cfg["bwd"]:
+                dq, dk, _ = swa.swa_backward(q, k, v, o, lse, do, None, *win, sm, impl=impl)
+                swa.rope2d_apply_(flat(dq), *rope, inverse=True)
+                swa.rope2d_apply_(flat(dk), *rope, inverse=True)
+
+        v_steps = max(2, min(args.steps, 10))
+        for _ in range(3):
+            prerot_step()
+        barrier()
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        p0.record(stream)
+        for _ in range(v_steps):
+            prerot_step()
+        p1.record(stream)
+        barrier()
+        tp = torch.tensor([p0.elapsed_time(p1)], device=device, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(tp, op=dist.ReduceOp.MAX)
+        ms_p = tp.item() / v_steps
+        prerot = {"what": "stand-alone RoPE kernel in place on q, k; attention without RoPE; inverse RoPE on dq, dk",
+                  "ms_per_step": ms_p, "value": step_flops * world / (ms_p * 1e-3) / 1e12, "unit": "TFLOP/s",
+                  "steps": v_steps}
+        swa.check_status()
+
     # ---------------------------------------------------------------- optional verification gather
     verified = None
     if args.verify and world > 1:
@@ -442,6 +479,8 @@ def main():
         "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": int(launches),
         "clocks": clocks,
     }
+    if prerot is not None:
+        line["unfused_composition"] = prerot
     if verified is not None:
         line["verified_gather"] = verified
     print(json.dumps(line))

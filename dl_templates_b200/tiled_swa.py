@@ -240,6 +240,29 @@ class TiledSwa(torch.autograd.Function):
         return dq, dk, dv, None, None, None, None, None, None
 
 
+_rope_mode = os.environ.get("SWA_ROPE_MODE", "fused")
+
+
+def set_rope_mode(mode: str) -> str:
+    """How ``TiledSwaRope2D`` applies the rotation; returns the previous mode.
+
+    ``"fused"`` (default): q and k are rotated on chip inside the attention kernels; no temporaries, but every
+    streamed row is rotated once per tile whose window contains it.  ``"prerotate"``: the stand-alone kernel
+    rotates copies of q and k once (src/fused_rope2d.py:126-168 followed by src/tiled_swa.py:604, the reference's
+    own composition), the attention kernels run without RoPE on the copies, which replace q and k among the saved
+    tensors, and dq, dk are rotated back in place; two extra passes over q and k, each row rotated once.
+    A module-level switch like the reference's ``use_fused_na()`` / ``use_autotuner()`` toggles."""
+    global _rope_mode
+    if mode not in ("fused", "prerotate"):
+        raise ValueError("rope mode must be 'fused' or 'prerotate'")
+    prev, _rope_mode = _rope_mode, mode
+    return prev
+
+
+def _flat3(x):
+    return x.view(-1, x.shape[2], x.shape[3])
+
+
 class TiledSwaRope2D(torch.autograd.Function):
     """RoPE-2D on q and k fused into the attention kernels.
 
@@ -256,7 +279,15 @@ class TiledSwaRope2D(torch.autograd.Function):
         if rope is not None:
             assert idx.shape[0] == q.shape[2]
             assert row_cs_buffer.shape[1] == col_cs_buffer.shape[1]
-        o, lse = swa_forward(q, k, v, rope, b_size, t_height, t_width, row_size, col_size, sm_scale)
+        ctx.prerotated = rope is not None and _rope_mode == "prerotate"
+        if ctx.prerotated:
+            from .fused_rope2d import rope2d_apply_
+            q, k = (t.clone(memory_format=torch.contiguous_format) for t in (q, k))
+            rope2d_apply_(_flat3(q), *rope)
+            rope2d_apply_(_flat3(k), *rope)
+            o, lse = swa_forward(q, k, v, None, b_size, t_height, t_width, row_size, col_size, sm_scale)
+        else:
+            o, lse = swa_forward(q, k, v, rope, b_size, t_height, t_width, row_size, col_size, sm_scale)
         if rope is None:
             ctx.save_for_backward(q, k, v, lse, o)
         else:
@@ -269,7 +300,14 @@ class TiledSwaRope2D(torch.autograd.Function):
         saved = ctx.saved_tensors
         q, k, v, lse, o = saved[:5]
         rope = tuple(saved[5:8]) if len(saved) == 8 else None
-        dq, dk, dv = swa_backward(q, k, v, o, lse, do, rope, *ctx.win)
+        if ctx.prerotated:     # q, k are the rotated copies
+            from .fused_rope2d import rope2d_apply_
+            dq, dk, dv = swa_backward(q, k, v, o, lse, do, None, *ctx.win)
+            dq, dk = (t if t.is_contiguous() else t.contiguous() for t in (dq, dk))
+            rope2d_apply_(_flat3(dq), *rope, inverse=True)
+            rope2d_apply_(_flat3(dk), *rope, inverse=True)
+        else:
+            dq, dk, dv = swa_backward(q, k, v, o, lse, do, rope, *ctx.win)
         return (dq, dk, dv) + (None,) * 9
 
 

@@ -384,3 +384,26 @@ def test_reference_selftest_shape_runs_on_tensor_cores():
     assert_close(got, want, torch.float16, what="self-test shape")
     simt, _ = run_gpu(q, k, v, do, None, win, 1.0, impl="simt")
     assert_close(got, simt, torch.float16, what="self-test shape vs simt")
+
+
+def test_prerotate_mode_matches_fused_mode():
+    """``set_rope_mode('prerotate')`` (stand-alone rotation of copies, attention without RoPE, gradients rotated
+    back) against the oracle and against the fused mode; q and k stay unmodified in both."""
+    c = make_case(CONFIGS["cfg3"], B=1, H=2)
+    rope = tuple(t.to(DEV) for t in (c["idx"], c["row_cs"], c["col_cs"]))
+    want = orc.fused_ref(c["q"].float(), c["k"].float(), c["v"].float(), c["do"].float(), c["idx"], c["row_cs"],
+                         c["col_cs"], *c["win"], c["sm_scale"])
+    results = {}
+    for mode in ("prerotate", "fused"):
+        prev = swa.set_rope_mode(mode)
+        try:
+            q, k, v = (c[n].to(DEV).requires_grad_(True) for n in ("q", "k", "v"))
+            o = swa.TiledSwaRope2D.apply(q, k, v, *rope, *c["win"], c["sm_scale"])
+            o.backward(c["do"].to(DEV))
+            swa.check_status()
+        finally:
+            swa.set_rope_mode(prev)
+        assert torch.equal(q.detach().cpu(), c["q"]) and torch.equal(k.detach().cpu(), c["k"])
+        results[mode] = [t.detach().float().cpu() for t in (o, q.grad, k.grad, v.grad)]
+        assert_close(results[mode], want, c["q"].dtype, what=mode)
+    assert_close(results["prerotate"], results["fused"], c["q"].dtype, what="prerotate vs fused")
