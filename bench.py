@@ -189,10 +189,13 @@ def run_cpu_reference(cfg, steps, warmup):
     for _ in range(warmup):
         cpu_sample_step(case, cfg, n_slices)
     t0 = time.perf_counter()
-    for _ in range(steps):
+    done = 0
+    # steps = None: a bounded sample of about ten seconds of CPU work (at least 3, at most 64 steps)
+    while (done < steps) if steps is not None else (done < 3 or (time.perf_counter() - t0 < 10.0 and done < 64)):
         cpu_sample_step(case, cfg, n_slices)
-    dt = (time.perf_counter() - t0) / max(1, steps)
-    return flops / dt / 1e12, dt * 1e3, cores, n_slices
+        done += 1
+    dt = (time.perf_counter() - t0) / max(1, done)
+    return flops / dt / 1e12, dt * 1e3, cores, n_slices, done
 
 
 # --------------------------------------------------------------------------------------------
@@ -254,7 +257,7 @@ def main():
         if rank != 0:
             return 0
         steps, warmup = max(1, min(args.steps, 10)), max(1, min(args.warmup, 2))
-        tf, ms, cores, n_slices = run_cpu_reference(cfg, steps, warmup)
+        tf, ms, cores, n_slices, _ = run_cpu_reference(cfg, steps, warmup)
         sample = (f"{n_slices} (batch,head) slice(s) of {args.workload} per step, dense [N,N] mask + SDPA + autograd, "
                   f"fp32, {steps} steps")
         print(json.dumps({
@@ -465,10 +468,10 @@ def main():
 
     cpu_baseline = None
     if world == 1 and not args.no_cpu_baseline:
-        tf, ms, cores, n_slices = run_cpu_reference(cfg, steps=3, warmup=1)
+        tf, ms, cores, n_slices, n_cpu_steps = run_cpu_reference(cfg, steps=None, warmup=1)
         cpu_baseline = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
                         "sample": f"{n_slices} (batch,head) slice(s) of {args.workload} per step, dense [N,N] mask + "
-                                  f"SDPA + autograd, fp32, 3 steps, {ms:.0f} ms/step"}
+                                  f"SDPA + autograd, fp32, {n_cpu_steps} steps, {ms:.0f} ms/step"}
 
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
