@@ -239,6 +239,7 @@ def main():
                          "packed buffer (kernel timing only, no e2e leg)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-variants", action="store_true", help="skip the un-fused composition leg after the timed region")
     ap.add_argument("--e2e-chunk", type=int, default=32, help="(batch*head) slices per pipelined chunk of the e2e path")
     ap.add_argument("--verify", action="store_true", help="gather outputs over NCCL and compare rank slices")
     args = ap.parse_args()
@@ -398,7 +399,7 @@ def main():
     # the stand-alone kernel, attention without RoPE, inverse rotation of dq and dk in place.  Runs last because it
     # overwrites q and k (rotating them again each step, which keeps their scale).
     prerot = None
-    if rope is not None and args.layout == "bhnd" and not os.environ.get("SWA_BENCH_NO_VARIANTS"):
+    if rope is not None and args.layout == "bhnd" and not args.no_variants:
         def flat(x):
             return x.view(-1, x.shape[2], x.shape[3])
 
