@@ -38,9 +38,9 @@ sys.path.insert(0, ROOT)
 # DRAM bytes (read + write) per launch and per (batch, head) slice, from one `ncu --set full` capture at
 # B*H = 64 (profiles/ncu_full_target_bh64_all_kernels.md); traffic grows in proportion to B*H.
 TRAFFIC_BYTES_PER_BH = {
-    "target:fwd": (402.8e6 + 118.0e6) / 64,
-    "target:dq": (545.4e6 + 121.6e6) / 64,
-    "target:dkdv": (545.4e6 + 239.8e6) / 64,
+    "target:fwd": (402.9e6 + 118.2e6) / 64,
+    "target:dq": (545.9e6 + 118.9e6) / 64,
+    "target:dkdv": (545.5e6 + 237.3e6) / 64,
 }
 
 METRIC = "2D-SWA fwd+bwd TFLOP/s (windowed FLOPs, whole job)"
