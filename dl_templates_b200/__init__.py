@@ -4,11 +4,11 @@ Python call surface of the reference's ``src/tiled_swa.py`` and
 ``src/fused_rope2d.py`` over a C-ABI CUDA library built for sm_100a.
 """
 from .fused_rope2d import (FusedInplaceRotaryPositionEncoding2D, FusedRotaryPositionEncodingContext, RotaryPE2D,
-                           make_cs_table, rope2d_apply_)
+                           make_cs_table, rope2d_apply_, rope2d_apply_to)
 from .host_pipeline import HostPipeline
 from .tiled_swa import (TiledSwa, TiledSwaPackedQKV, TiledSwaRope2D, check_status, padded_head_dims, selected_impl,
                         set_rope_mode, swa_backward, swa_backward_noalloc, swa_forward, tiled_swa_fwd)
 
 __all__ = ["HostPipeline", "TiledSwa", "TiledSwaRope2D", "TiledSwaPackedQKV", "tiled_swa_fwd", "swa_forward", "swa_backward",
            "swa_backward_noalloc", "selected_impl", "padded_head_dims", "set_rope_mode", "check_status", "RotaryPE2D", "FusedInplaceRotaryPositionEncoding2D",
-           "FusedRotaryPositionEncodingContext", "make_cs_table", "rope2d_apply_"]
+           "FusedRotaryPositionEncodingContext", "make_cs_table", "rope2d_apply_", "rope2d_apply_to"]

@@ -36,7 +36,7 @@ class Rope(C.Structure):
 
 
 EXPORTS = ("swa_fwd", "swa_bwd_delta", "swa_bwd_dq", "swa_bwd_dkdv", "swa_bwd_noalloc", "rope2d_apply",
-           "swa_select_impl", "swa_describe_plan", "swa_launch_count", "swa_last_error", "swa_version")
+           "rope2d_apply_to", "swa_select_impl", "swa_describe_plan", "swa_launch_count", "swa_last_error", "swa_version")
 
 
 def _load() -> C.CDLL:
@@ -57,10 +57,12 @@ def _load() -> C.CDLL:
                                     C.c_void_p, P(Tensor4), P(Tensor4), P(Tensor4), C.c_void_p, C.c_void_p]
     lib.rope2d_apply.argtypes = [C.c_int32, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, P(C.c_int64), P(Rope),
                                  C.c_int32, C.c_void_p]
+    lib.rope2d_apply_to.argtypes = [C.c_int32, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, P(C.c_int64),
+                                    P(C.c_int64), P(Rope), C.c_int32, C.c_void_p]
     lib.swa_select_impl.argtypes = [P(Geom), P(Rope), C.c_int32]
     lib.swa_describe_plan.argtypes = [P(Geom), P(Rope), C.c_int32, P(C.c_int32)]
     for name in ("swa_fwd", "swa_bwd_delta", "swa_bwd_dq", "swa_bwd_dkdv", "swa_bwd_noalloc", "rope2d_apply",
-                 "swa_select_impl", "swa_describe_plan", "swa_version"):
+                 "rope2d_apply_to", "swa_select_impl", "swa_describe_plan", "swa_version"):
         getattr(lib, name).restype = C.c_int
     lib.swa_launch_count.restype = C.c_int64
     lib.swa_last_error.restype = C.c_char_p

@@ -132,4 +132,45 @@ __global__ void __launch_bounds__(256) rope2d_kernel(T* __restrict__ x, int64_t 
   }
 }
 
+// Out-of-place form for 16-bit types: y = rope(x), x untouched.  One thread per 16-byte unit of a token row
+// (8 elements): units outside the rotated dims, or of a half whose index is negative, are copied; a rotated unit
+// reads its partner unit (R elements away, same row, so the same DRAM sectors another thread reads) and writes
+// its own half of the pair.  Needs R % 8 == 0, C % 8 == 0, unit last strides and 16-byte aligned rows.
+template <typename T>
+__global__ void __launch_bounds__(256) rope2d_copy_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows,
+                                                          int64_t N, int C, int64_t xs0, int64_t xs1, int64_t ys0,
+                                                          int64_t ys1, RopeDev rp, float sign) {
+  const int upr = C >> 3;
+  const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t row = gid / upr;
+  if (row >= rows) return;
+  const int u = (int)(gid - row * upr);
+  const int64_t bi = row / N, tok = row - bi * N;
+  const T* src = x + bi * xs0 + tok * xs1 + u * 8;
+  uint4 own = *reinterpret_cast<const uint4*>(src);
+  const int e0 = u * 8;
+  if (e0 < 4 * rp.R) {
+    const int seg = e0 / rp.R, half = seg >> 1, second = seg & 1, i0 = e0 - seg * rp.R;
+    int irow, icol;
+    decode_idx(rp.idx[tok], rp.max_h, rp.max_w, irow, icol);
+    const int pos = half ? icol : irow;
+    if (pos >= 0) {
+      const uint4 oth = *reinterpret_cast<const uint4*>(second ? src - rp.R : src + rp.R);
+      const float* tab = (half ? rp.col_cs : rp.row_cs) + ((int64_t)pos * rp.R + i0) * 2;
+      float cs[16];
+#pragma unroll
+      for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(cs + j) = *reinterpret_cast<const float4*>(tab + j);
+      T* eo = reinterpret_cast<T*>(&own);
+      const T* ep = reinterpret_cast<const T*>(&oth);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float c = cs[2 * j], sn = cs[2 * j + 1] * sign;
+        const float a = second ? to_f(ep[j]) : to_f(eo[j]), b = second ? to_f(eo[j]) : to_f(ep[j]);
+        eo[j] = from_f<T>(second ? a * sn + b * c : a * c - b * sn);
+      }
+    }
+  }
+  *reinterpret_cast<uint4*>(y + bi * ys0 + tok * ys1 + u * 8) = own;
+}
+
 }  // namespace swa

@@ -330,4 +330,33 @@ int rope2d_apply(int32_t dtype, void* x, int64_t batch, int64_t n_tokens, int32_
   return launch_ok("rope2d");
 }
 
+int rope2d_apply_to(int32_t dtype, const void* x, void* y, int64_t batch, int64_t n_tokens, int32_t n_dim,
+                    const int64_t* xs, const int64_t* ys, const swa_rope_t* rope, int32_t inverse, void* stream) {
+  if (dtype != SWA_F16 && dtype != SWA_BF16) return fail(E_DTYPE, "rope2d_apply_to takes fp16 / bf16 (dtype %d)", dtype);
+  if (!x || !y || !xs || !ys) return fail(E_NULL, "x / y / strides are NULL");
+  if (x == y) return fail(E_SHAPE, "rope2d_apply_to is out of place; use rope2d_apply for x == y");
+  if (!rope || !rope->idx || !rope->row_cs || !rope->col_cs) return fail(E_ROPE, "rope index / tables are NULL");
+  if (rope->n_rdim <= 0 || 4 * rope->n_rdim > n_dim)
+    return fail(E_ROPE, "4*n_rdim (%d) must be in [4, n_dim=%d]", 4 * rope->n_rdim, n_dim);
+  if (rope->max_h <= 0 || rope->max_w <= 0) return fail(E_ROPE, "rope table lengths must be positive");
+  if (batch <= 0 || n_tokens <= 0) return fail(E_SHAPE, "batch and n_tokens must be positive");
+  const swa::RopeDev rp = swa::make_rope(rope);
+  auto rows16 = [](const void* p, const int64_t* st) {
+    return st[2] == 1 && ((uintptr_t)p % 16) == 0 && st[0] % 8 == 0 && st[1] % 8 == 0;
+  };
+  if (rp.R % 8 || n_dim % 8 || !rows16(x, xs) || !rows16(y, ys) || ((uintptr_t)rp.row_cs % 16) || ((uintptr_t)rp.col_cs % 16))
+    return fail(E_SHAPE, "rope2d_apply_to needs n_rdim %% 8 == 0, n_dim %% 8 == 0, unit last strides and 16-byte aligned rows");
+  const int64_t rows = batch * n_tokens, threads = rows * (n_dim / 8);
+  const unsigned blocks = (unsigned)((threads + 255) / 256);
+  const float sign = inverse ? -1.f : 1.f;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == SWA_F16)
+    swa::rope2d_copy_kernel<__half><<<blocks, 256, 0, st>>>((const __half*)x, (__half*)y, rows, n_tokens, n_dim, xs[0], xs[1],
+                                                            ys[0], ys[1], rp, sign);
+  else
+    swa::rope2d_copy_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, rows, n_tokens,
+                                                                   n_dim, xs[0], xs[1], ys[0], ys[1], rp, sign);
+  return launch_ok("rope2d_copy");
+}
+
 }  // extern "C"

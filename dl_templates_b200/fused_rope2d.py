@@ -60,6 +60,30 @@ def rope2d_apply_(x: torch.Tensor, idx: torch.Tensor, row_cs: torch.Tensor, col_
     return x
 
 
+def rope2d_apply_to(x: torch.Tensor, idx: torch.Tensor, row_cs: torch.Tensor, col_cs: torch.Tensor,
+                    inverse: bool = False) -> torch.Tensor:
+    """``rope(x)`` (or the inverse rotation) of ``x [batch, N, C]`` in a new contiguous tensor, ``x`` untouched:
+    one pass when the layout allows (fp16 / bf16, ``n_rdim % 8 == 0``, ``C % 8 == 0``, unit last stride, 16-byte
+    aligned rows), else a copy followed by the in-place kernel."""
+    if not x.is_cuda:
+        raise RuntimeError("dl_templates_b200 runs on CUDA tensors only (sm_100a); there is no CPU path")
+    B, N, n_dim = x.shape
+    assert row_cs.shape[1] == col_cs.shape[1] and idx.shape[0] == N
+    y = torch.empty((B, N, n_dim), dtype=x.dtype, device=x.device)
+    rows16 = x.stride(2) == 1 and x.data_ptr() % 16 == 0 and x.stride(0) % 8 == 0 and x.stride(1) % 8 == 0
+    if x.dtype in (torch.float16, torch.bfloat16) and row_cs.shape[1] % 8 == 0 and n_dim % 8 == 0 and rows16:
+        with torch.cuda.device(x.device):
+            rope = _lib.make_rope(idx, row_cs, col_cs)
+            xs = (C.c_int64 * 3)(x.stride(0), x.stride(1), x.stride(2))
+            ys = (C.c_int64 * 3)(y.stride(0), y.stride(1), y.stride(2))
+            code = _lib.lib.rope2d_apply_to(_lib.dtype_code(x.dtype), x.data_ptr(), y.data_ptr(), B, N, n_dim, xs, ys,
+                                            C.byref(rope), 1 if inverse else 0, _lib.stream_ptr(x.device))
+        _lib.check(code, "rope2d_apply_to")
+        return y
+    y.copy_(x)
+    return rope2d_apply_(y, idx, row_cs, col_cs, inverse)
+
+
 class RotaryPE2D(torch.autograd.Function):
     """``RotaryPE2D.apply(x, idx, row_cs_buffer, col_cs_buffer)``: rotates ``x [B,N,C]`` in
     place and returns it; backward applies the inverse rotation to a copy of the
@@ -76,8 +100,7 @@ class RotaryPE2D(torch.autograd.Function):
     @torch.autograd.function.once_differentiable
     def backward(ctx, do):
         idx, row_cs_buffer, col_cs_buffer = ctx.saved_tensors
-        dx = do.clone()
-        rope2d_apply_(dx, idx, row_cs_buffer, col_cs_buffer, inverse=True)
+        dx = rope2d_apply_to(do, idx, row_cs_buffer, col_cs_buffer, inverse=True)   # clone + inverse rotation in one pass
         return dx, None, None, None
 
 

@@ -281,10 +281,9 @@ class TiledSwaRope2D(torch.autograd.Function):
             assert row_cs_buffer.shape[1] == col_cs_buffer.shape[1]
         ctx.prerotated = rope is not None and _rope_mode == "prerotate"
         if ctx.prerotated:
-            from .fused_rope2d import rope2d_apply_
-            q, k = (t.clone(memory_format=torch.contiguous_format) for t in (q, k))
-            rope2d_apply_(_flat3(q), *rope)
-            rope2d_apply_(_flat3(k), *rope)
+            from .fused_rope2d import rope2d_apply_to
+            q, k = (rope2d_apply_to(t.reshape(-1, t.shape[2], t.shape[3]) if t.is_contiguous() else
+                                    t.contiguous().view(-1, t.shape[2], t.shape[3]), *rope).view(t.shape) for t in (q, k))
             o, lse = swa_forward(q, k, v, None, b_size, t_height, t_width, row_size, col_size, sm_scale)
         else:
             o, lse = swa_forward(q, k, v, rope, b_size, t_height, t_width, row_size, col_size, sm_scale)

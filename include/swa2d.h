@@ -100,6 +100,14 @@ int swa_bwd_dkdv(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t
 int rope2d_apply(int32_t dtype, void* x, int64_t batch, int64_t n_tokens, int32_t n_dim, const int64_t* xs,
                  const swa_rope_t* rope, int32_t inverse, void* stream);
 
+/* Out-of-place form for fp16 / bf16: y = rope(x) (or the inverse rotation), x untouched, dims beyond 4*n_rdim and
+ * tokens with a negative index half copied.  The reference's RotaryPE2D rotates in place and its backward clones
+ * the incoming gradient first (src/fused_rope2d.py:143,151); this entry does clone + rotate in one pass.
+ * Needs n_rdim % 8 == 0, n_dim % 8 == 0, unit last strides and 16-byte aligned rows (negative return otherwise:
+ * copy, then rope2d_apply). */
+int rope2d_apply_to(int32_t dtype, const void* x, void* y, int64_t batch, int64_t n_tokens, int32_t n_dim,
+                    const int64_t* xs, const int64_t* ys, const swa_rope_t* rope, int32_t inverse, void* stream);
+
 /* Whole backward pass (delta, then dq, then dk/dv) for callers that must not allocate.
  * This entry point has no counterpart in the reference; it exists for hosts that cannot call
  * cudaMalloc around the op: a plugin running inside a runtime that has already handed all device

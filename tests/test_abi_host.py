@@ -17,7 +17,7 @@ from dl_templates_b200.sharding import bh_range, shard_bh
 def header_symbols():
     text = open(os.path.join(ROOT, "include", "swa2d.h")).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(swa_[a-z_0-9]+|rope2d_apply)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(swa_[a-z_0-9]+|rope2d_[a-z_0-9]+)\s*\(", text)))
 
 
 def test_library_exports_every_declared_symbol():

@@ -67,3 +67,36 @@ def test_module_forward_4d():
                           m.col_buffer.cs_components.cpu()).reshape(B, H, G * G, C)
     y = m(x, idx)
     assert orc.max_abs(y.cpu(), want) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("R,C", [(8, 32), (16, 64), (8, 64), (3, 20), (32, 128)])
+def test_out_of_place_form(dtype, R, C):
+    """``rope2d_apply_to``: same values as clone + in-place rotation (one-pass kernel for 16-bit types with
+    n_rdim % 8 == 0, the two-step path otherwise), input untouched, strided input rows, inverse included."""
+    torch.manual_seed(2)
+    Gh, Gw, B = 7, 12, 4
+    N = Gh * Gw + 2
+    idx = torch.cat([orc.encode_idx(Gh, Gw), torch.full((2,), -1, dtype=torch.int32)])
+    idx[torch.rand(N) < 0.2] = -1
+    idx[5] = int(idx[5]) | 0xFFFF if int(idx[5]) >= 0 else idx[5]
+    idx[8] = -65536 | (int(idx[8]) & 0xFFFF)
+    rt, ct = orc.make_cs_table(R, Gh), orc.make_cs_table(R, Gw)
+    packed = torch.randn(B, N, 3, C).to(dtype).to(DEV)
+    x = packed[:, :, 1]                                   # rows of C elements at a stride of 3*C
+    keep = packed.clone()
+    dev = [t.to(DEV) for t in (idx, rt, ct)]
+    for inverse in (False, True):
+        y = swa.rope2d_apply_to(x, *dev, inverse=inverse)
+        assert y.is_contiguous() and torch.equal(packed, keep)
+        ref = swa.rope2d_apply_(x.clone(), *dev, inverse=inverse)
+        if dtype == torch.float32:
+            assert torch.equal(y, ref)
+        else:
+            assert orc.max_abs(y.float().cpu(), ref.float().cpu()) <= 2 ** -6 * float(ref.float().abs().max())
+            want = orc.rope2d_ref(x.float().cpu(), idx, rt, ct) if not inverse else None
+            if want is not None:
+                assert orc.max_abs(y.float().cpu(), want) < 3e-2
+        none = (idx == -1)
+        assert torch.equal(y[:, none.to(DEV)], x[:, none.to(DEV)])
+        assert torch.equal(y[..., 4 * R:], x[..., 4 * R:])
