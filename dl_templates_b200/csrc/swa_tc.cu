@@ -96,7 +96,7 @@ int halo_width(const swa_geom_t* g, int TW) {
 //   tensor memory (512 columns): forward  score buffers at 128-column strides (packed when they do not fit) + two O accumulators;
 //                                backward nsb pairs (S, dP) of 2N columns + the accumulators
 //   shared memory:               nxb resident-tile buffers + indicator rows + stages x (block + penalty rows [+ lse, delta])
-bool make_plan_shape(const swa_geom_t* g, int which, int TH, int TW, uint32_t tab_bytes, Plan* out) {
+bool make_plan_shape(const swa_geom_t* g, int which, int TH, int TW, uint32_t tab_bytes, Plan* out, long* cost_out = nullptr) {
   Plan pl;
   pl.tab_bytes = tab_bytes;
   pl.TH = TH;
@@ -156,6 +156,7 @@ bool make_plan_shape(const swa_geom_t* g, int which, int TH, int TW, uint32_t ta
         pl.nsb = nsb;
       }
       *out = pl;
+      if (cost_out) *cost_out = best_cost;
       // tensor-memory columns of the final plan (the environment overrides above included): a plan beyond the
       // 512-column allocation is refused here, never launched
       const uint32_t fwd_stride = (pl.N <= 128 && pl.nsb * 128 + 2 * 64 * vch <= 512) ? 128u : (uint32_t)pl.N;
@@ -183,6 +184,20 @@ bool make_plan(const swa_geom_t* g, const swa_rope_t* rope, int which, Plan* out
     else {
       // measured at the 13 x 13 window: with fused RoPE 16 x 8 wins (80-token blocks, every block row shared by
       // two rotating threads), without it 8 x 16 wins for the forward and dQ kernels (fewer, wider blocks)
+      if (which == 2) {
+        // dK/dV (K tile resident, Q blocks streamed; its accumulators leave the narrowest blocks): the shape whose
+        // blocks cost less by the planner's own measure -- 16 x 8 at the 13 x 13 window with d = 64, 8 x 16 once
+        // d_v = 128 or the window grows (measured: 10 % and 13 % faster at 15 x 15 / d_v = 128 and 31 x 31 / d = 128)
+        Plan a, b;
+        long ca = 0, cb = 0;
+        const bool oa = make_plan_shape(g, which, 16, 8, tab, &a, &ca), ob = make_plan_shape(g, which, 8, 16, tab, &b, &cb);
+        if (oa || ob) {
+          *out = (oa && (!ob || ca <= cb)) ? a : b;
+          return true;
+        }
+        if (tab == 0) return false;
+        continue;
+      }
       const bool wide_first = which != 2 && !(rope && rope->idx);
       if (wide_first ? (make_plan_shape(g, which, 8, 16, tab, out) || make_plan_shape(g, which, 16, 8, tab, out))
                      : (make_plan_shape(g, which, 16, 8, tab, out) || make_plan_shape(g, which, 8, 16, tab, out)))
