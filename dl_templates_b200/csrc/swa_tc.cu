@@ -175,36 +175,46 @@ uint32_t rope_table_bytes(const swa_rope_t* rope) {
   return b <= 48 * 1024 && !getenv("SWA_TC_NO_TABS") ? (uint32_t)((b + 15) & ~15ull) : 0;
 }
 
-bool make_plan(const swa_geom_t* g, const swa_rope_t* rope, int which, Plan* out) {
+// Tile shape for one choice of staged-table bytes; *cost = the planner's block cost of the plan taken.
+static bool make_plan_tab(const swa_geom_t* g, const swa_rope_t* rope, int which, uint32_t tab, Plan* out, long* cost) {
   const char* th_names[3] = {"SWA_TC_TH_FWD", "SWA_TC_TH_DQ", "SWA_TC_TH_DKDV"};
   const int th = env_int(th_names[which], env_int("SWA_TC_TH", 0));
-  for (uint32_t tab = rope_table_bytes(rope);; tab = 0) {   // with the staged tables if a plan fits, else without
-    if (th == 8) { if (make_plan_shape(g, which, 8, 16, tab, out)) return true; }
-    else if (th == 16) { if (make_plan_shape(g, which, 16, 8, tab, out)) return true; }
-    else {
-      // measured at the 13 x 13 window: with fused RoPE 16 x 8 wins (80-token blocks, every block row shared by
-      // two rotating threads), without it 8 x 16 wins for the forward and dQ kernels (fewer, wider blocks)
-      if (which == 2) {
-        // dK/dV (K tile resident, Q blocks streamed; its accumulators leave the narrowest blocks): the shape whose
-        // blocks cost less by the planner's own measure -- 16 x 8 at the 13 x 13 window with d = 64, 8 x 16 once
-        // d_v = 128 or the window grows (measured: 10 % and 13 % faster at 15 x 15 / d_v = 128 and 31 x 31 / d = 128)
-        Plan a, b;
-        long ca = 0, cb = 0;
-        const bool oa = make_plan_shape(g, which, 16, 8, tab, &a, &ca), ob = make_plan_shape(g, which, 8, 16, tab, &b, &cb);
-        if (oa || ob) {
-          *out = (oa && (!ob || ca <= cb)) ? a : b;
-          return true;
-        }
-        if (tab == 0) return false;
-        continue;
-      }
-      const bool wide_first = which != 2 && !(rope && rope->idx);
-      if (wide_first ? (make_plan_shape(g, which, 8, 16, tab, out) || make_plan_shape(g, which, 16, 8, tab, out))
-                     : (make_plan_shape(g, which, 16, 8, tab, out) || make_plan_shape(g, which, 8, 16, tab, out)))
-        return true;
-    }
-    if (tab == 0) return false;
+  if (th == 8) return make_plan_shape(g, which, 8, 16, tab, out, cost);
+  if (th == 16) return make_plan_shape(g, which, 16, 8, tab, out, cost);
+  if (which == 2) {
+    // dK/dV (K tile resident, Q blocks streamed; its accumulators leave the narrowest blocks): the shape whose
+    // blocks cost less by the planner's own measure -- 16 x 8 at the 13 x 13 window with d = 64, 8 x 16 once
+    // d_v = 128 or the window grows (measured: 10 % and 13 % faster at 15 x 15 / d_v = 128 and 31 x 31 / d = 128)
+    Plan a, b;
+    long ca = 0, cb = 0;
+    const bool oa = make_plan_shape(g, which, 16, 8, tab, &a, &ca), ob = make_plan_shape(g, which, 8, 16, tab, &b, &cb);
+    if (!oa && !ob) return false;
+    const bool take_a = oa && (!ob || ca <= cb);
+    *out = take_a ? a : b;
+    *cost = take_a ? ca : cb;
+    return true;
   }
+  // measured at the 13 x 13 window: with fused RoPE 16 x 8 wins (80-token blocks, every block row shared by
+  // two rotating threads), without it 8 x 16 wins for the forward and dQ kernels (fewer, wider blocks)
+  const bool wide_first = !(rope && rope->idx);
+  return wide_first ? (make_plan_shape(g, which, 8, 16, tab, out, cost) || make_plan_shape(g, which, 16, 8, tab, out, cost))
+                    : (make_plan_shape(g, which, 16, 8, tab, out, cost) || make_plan_shape(g, which, 8, 16, tab, out, cost));
+}
+
+// The cos/sin tables are staged in shared memory when that does not cost block size: a plan with the tables is
+// taken only if its blocks are as cheap as those of the plan without them (40 KB of tables beside d = 128 tiles
+// would force 48-token instead of 80-token blocks, measured 1.5x slower in the forward kernel).
+bool make_plan(const swa_geom_t* g, const swa_rope_t* rope, int which, Plan* out) {
+  const uint32_t tab = rope_table_bytes(rope);
+  Plan with, without;
+  long cw = 0, cn = 0;
+  const bool ok_n = make_plan_tab(g, rope, which, 0, &without, &cn);
+  if (tab && make_plan_tab(g, rope, which, tab, &with, &cw) && (!ok_n || cw <= cn)) {
+    *out = with;
+    return true;
+  }
+  if (ok_n) *out = without;
+  return ok_n;
 }
 
 // Indicator value a and penalty b (powers of two, exact in fp16 and bf16) of the window mask that
