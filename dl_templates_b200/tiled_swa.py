@@ -251,12 +251,26 @@ def set_rope_mode(mode: str) -> str:
     rotates copies of q and k once (src/fused_rope2d.py:126-168 followed by src/tiled_swa.py:604, the reference's
     own composition), the attention kernels run without RoPE on the copies, which replace q and k among the saved
     tensors, and dq, dk are rotated back in place; two extra passes over q and k, each row rotated once.
+    ``"auto"``: ``"prerotate"`` for problems whose cos/sin tables the fused kernels cannot stage in shared
+    memory (e.g. 256 x 256 positions with 128 rotated dims, where fusing was measured 1.7x slower), else ``"fused"``.
     A module-level switch like the reference's ``use_fused_na()`` / ``use_autotuner()`` toggles."""
     global _rope_mode
-    if mode not in ("fused", "prerotate"):
-        raise ValueError("rope mode must be 'fused' or 'prerotate'")
+    if mode not in ("fused", "prerotate", "auto"):
+        raise ValueError("rope mode must be 'fused', 'prerotate' or 'auto'")
     prev, _rope_mode = _rope_mode, mode
     return prev
+
+
+def _prerotate_wanted(q, v, rope, win) -> bool:
+    if rope is None or _rope_mode == "fused":
+        return False
+    if _rope_mode == "prerotate":
+        return True
+    g = _geom(q, v, *win, "auto")
+    r = _lib.make_rope(*rope)
+    plan = (C.c_int32 * 12)()
+    # tensor-core forward plan without staged tables (plan[8] == 0): the rotating warps would fetch from L2
+    return _lib.lib.swa_describe_plan(C.byref(g), C.byref(r), 0, plan) == 0 and plan[8] == 0
 
 
 def _flat3(x):
@@ -279,7 +293,7 @@ class TiledSwaRope2D(torch.autograd.Function):
         if rope is not None:
             assert idx.shape[0] == q.shape[2]
             assert row_cs_buffer.shape[1] == col_cs_buffer.shape[1]
-        ctx.prerotated = rope is not None and _rope_mode == "prerotate"
+        ctx.prerotated = _prerotate_wanted(q, v, rope, (b_size, t_height, t_width, row_size, col_size, sm_scale))
         if ctx.prerotated:
             from .fused_rope2d import rope2d_apply_to
             q, k = (rope2d_apply_to(t.reshape(-1, t.shape[2], t.shape[3]) if t.is_contiguous() else

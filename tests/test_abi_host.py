@@ -176,3 +176,19 @@ def test_planner_refuses_overrides_beyond_tensor_memory(monkeypatch):
         monkeypatch.delenv(k)
     monkeypatch.setenv("SWA_TC_STAGES", "9")
     assert _plan(g, None, 0)[0] < 0
+
+
+def test_auto_rope_mode_follows_table_staging():
+    """'auto' pre-rotates exactly when the fused forward plan cannot stage the cos/sin tables (host-only check)."""
+    from dl_templates_b200 import tiled_swa as ts
+    prev = swa.set_rope_mode("auto")
+    try:
+        for grid, d, R, half, want in ((256, 128, 32, 15, True), (128, 64, 16, 6, False), (64, 64, 8, 3, False)):
+            q = torch.zeros(1, 1, grid * grid, d, dtype=torch.bfloat16)
+            rope = (torch.zeros(grid * grid, dtype=torch.int32), torch.zeros(grid, R, 2), torch.zeros(grid, R, 2))
+            assert ts._prerotate_wanted(q, q, rope, (1, grid, grid, half, half, 0.1)) is want
+        assert ts._prerotate_wanted(q, q, None, (1, grid, grid, half, half, 0.1)) is False
+    finally:
+        swa.set_rope_mode(prev)
+    with pytest.raises(ValueError):
+        swa.set_rope_mode("sometimes")

@@ -394,7 +394,7 @@ def test_prerotate_mode_matches_fused_mode():
     want = orc.fused_ref(c["q"].float(), c["k"].float(), c["v"].float(), c["do"].float(), c["idx"], c["row_cs"],
                          c["col_cs"], *c["win"], c["sm_scale"])
     results = {}
-    for mode in ("prerotate", "fused"):
+    for mode in ("prerotate", "fused", "auto"):
         prev = swa.set_rope_mode(mode)
         try:
             q, k, v = (c[n].to(DEV).requires_grad_(True) for n in ("q", "k", "v"))
