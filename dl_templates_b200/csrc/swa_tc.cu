@@ -196,7 +196,9 @@ static bool make_plan_tab(const swa_geom_t* g, const swa_rope_t* rope, int which
   }
   // measured at the 13 x 13 window: with fused RoPE 16 x 8 wins (80-token blocks, every block row shared by
   // two rotating threads), without it 8 x 16 wins for the forward and dQ kernels (fewer, wider blocks)
-  const bool wide_first = !(rope && rope->idx);
+  // ... and for the dQ kernel also when at most 32 of 64 q/k dims are rotated (measured 12 % faster at d_v = 128
+  // with a 15 x 15 window and 3 % at the 13 x 13 window; at d_qk = 128 the 16 x 8 tile stays 27 % ahead)
+  const bool wide_first = !(rope && rope->idx) || (which == 1 && rope->n_rdim <= 8 && g->d_qk == 64);
   return wide_first ? (make_plan_shape(g, which, 8, 16, tab, out, cost) || make_plan_shape(g, which, 16, 8, tab, out, cost))
                     : (make_plan_shape(g, which, 16, 8, tab, out, cost) || make_plan_shape(g, which, 8, 16, tab, out, cost));
 }
