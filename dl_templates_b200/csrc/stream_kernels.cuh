@@ -57,9 +57,15 @@ __global__ void __launch_bounds__(256) delta_flat_kernel(const T* __restrict__ o
   for (int off = tpr >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
   if (row < total_rows && (gid - row * tpr) == 0) {
     if (TOKEN_MAJOR) {
-      const int64_t bn = row / H, h = row - bn * H;
-      const int64_t b = bn / N, n = bn - b * N;
-      delta[(b * H + h) * N + n] = acc;
+      if (total_rows < (int64_t(1) << 31)) {   // 32-bit index arithmetic: two 64-bit divisions per row are not free here
+        const uint32_t r = (uint32_t)row, uh = (uint32_t)H, un = (uint32_t)N;
+        const uint32_t bn = r / uh, h = r - bn * uh, b = bn / un, n = bn - b * un;
+        delta[((int64_t)b * H + h) * N + n] = acc;
+      } else {
+        const int64_t bn = row / H, h = row - bn * H;
+        const int64_t b = bn / N, n = bn - b * N;
+        delta[(b * H + h) * N + n] = acc;
+      }
     } else {
       delta[row] = acc;
     }
