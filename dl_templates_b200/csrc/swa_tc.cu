@@ -19,7 +19,6 @@ namespace {
 
 thread_local char g_tc_err[256] = "";
 constexpr uint32_t kSmemLimit = 227 * 1024;
-constexpr uint32_t kSmemSlack = 14336;  // 1 KiB alignment + lse/delta staging + barriers, exchange buffers, penalty tables
 
 PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
   static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
@@ -102,7 +101,7 @@ bool make_plan_shape(const swa_geom_t* g, int which, int TH, int TW, uint32_t ta
   pl.TH = TH;
   pl.TW = TW;
   const int hw = halo_width(g, pl.TW);
-  if (hw > 64) return false;
+  if (hw > kPenCols) return false;
   const int halo_rows = pl.TH + 2 * g->row_size;
   const int qch = g->d_qk / 64, vch = g->d_v / 64;
   const uint32_t x_bytes = (which == 0 ? qch : qch + vch) * 16384u;
@@ -110,6 +109,8 @@ bool make_plan_shape(const swa_geom_t* g, int which, int TH, int TW, uint32_t ta
   const uint32_t stage_extra = which == 0 ? 0u : 1024u;       // lse / delta slots of a streamed block
   const int acc_cols = which == 0 ? 0 : (which == 1 ? 64 * qch : 64 * (qch + vch));
   const int min_stages = 3;
+  // alignment pad of the swizzled tiles + the kernel's barrier / exchange / penalty-table block behind the ring
+  const uint32_t kSmemSlack = 1024u + (((which == 0 ? (uint32_t)sizeof(FwdShared) : (uint32_t)sizeof(BwdShared)) + 15u) & ~15u);
   {
     // backward: two (S, dP) pairs of 2N columns next to the accumulators (N = 64 always fits: 256 + 256 columns)
     const int nsb = 2;
@@ -119,7 +120,7 @@ bool make_plan_shape(const swa_geom_t* g, int which, int TH, int TW, uint32_t ta
     for (int nxb = which == 0 ? 2 : env_int("SWA_TC_NXB", 2); nxb >= (which == 0 ? 2 : 1); --nxb) {
       const uint32_t fixed = nxb * x_bytes + 128u * kXRowBytes + tab_bytes;
       long best_cost = -1;
-      for (int KW = hw; KW <= 64; ++KW)
+      for (int KW = hw; KW <= kPenCols; ++KW)
         for (int KR = 1; KR <= 16; ++KR) {
           const int N = KW * KR;
           if (N > nmax || N % 16) continue;

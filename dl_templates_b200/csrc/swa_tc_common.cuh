@@ -136,9 +136,10 @@ __device__ __forceinline__ void write_indicator_row(uint8_t* tile, int row, int 
 // the row part depends only on the token's halo row, the column part only on its halo column.  Both
 // are tabulated once per resident tile; per block a thread only copies 16-byte units.
 constexpr int kPenRows = 160;   // >= TH + 2*wr + KR halo rows (wr <= 64)
+constexpr int kPenCols = 128;   // >= KW, the widest streamed block (halo width in token columns)
 struct PenaltyTables {
   uint4 row[kPenRows][2];       // [halo row - hr_first][tile rows 0-7 | 8-15]
-  uint4 col[64][2];             // [halo column - hx0][tile columns 0-7 | 8-15]
+  uint4 col[kPenCols][2];       // [halo column - hx0][tile columns 0-7 | 8-15]
 };
 
 template <bool BF16>
@@ -163,8 +164,9 @@ __device__ __forceinline__ void build_penalty_tables(PenaltyTables* tab, int t, 
     tab->row[hr][0] = penalty_unit<BF16>(lo, hi, nb);
     tab->row[hr][1] = penalty_unit<BF16>(lo - 8, hi - 8, nb);
   }
-  if (t < 64) {
-    const int yx = tp.hx0 + t;
+#pragma unroll 1
+  for (int jc = t; jc < kPenCols; jc += nthreads) {
+    const int yx = tp.hx0 + jc;
     const bool in = yx >= 0 && yx < p.Wtok;
     int lo = 1, hi = 0;
     if (in) {
@@ -172,8 +174,8 @@ __device__ __forceinline__ void build_penalty_tables(PenaltyTables* tab, int t, 
       lo = (yc - p.wc) * p.b - tp.x0;                       // allowed tile columns, inclusive
       hi = (yc + p.wc + 1) * p.b - tp.x0 - 1;
     }
-    tab->col[t][0] = penalty_unit<BF16>(lo, hi, nb);
-    tab->col[t][1] = penalty_unit<BF16>(lo - 8, hi - 8, nb);
+    tab->col[jc][0] = penalty_unit<BF16>(lo, hi, nb);
+    tab->col[jc][1] = penalty_unit<BF16>(lo - 8, hi - 8, nb);
   }
 }
 

@@ -407,3 +407,23 @@ def test_prerotate_mode_matches_fused_mode():
         results[mode] = [t.detach().float().cpu() for t in (o, q.grad, k.grad, v.grad)]
         assert_close(results[mode], want, c["q"].dtype, what=mode)
     assert_close(results["prerotate"], results["fused"], c["q"].dtype, what="prerotate vs fused")
+
+
+@pytest.mark.parametrize("bs,th,tw,rs,cs", [(16, 6, 6, 1, 2), (32, 4, 5, 2, 1), (8, 7, 9, 1, 5), (16, 5, 12, 0, 2)])
+def test_wide_halo_runs_on_tensor_cores(bs, th, tw, rs, cs):
+    """Windows whose halo is 65 to 96 token columns wide (the dK/dV kernel fits blocks of up to 96 tokens at d = 64) (tiles of 8 to 32 tokens with several tile columns of
+    reach -- the regime of the reference's own self-test, b_size = 16) take the tensor-core kernels."""
+    torch.manual_seed(bs + cs)
+    B, H, d = 1, 2, 64
+    N = bs * th * tw
+    q, k, v, do = (torch.randn(B, H, N, d).to(torch.bfloat16) for _ in range(4))
+    win = (bs, th, tw, rs, cs)
+    idx = torch.arange(N, dtype=torch.int32) // bs          # every token of a tile shares the tile's position
+    idx = ((idx // tw) << 16) | (idx % tw)
+    rope = (idx.to(torch.int32), swa.make_cs_table(16, th), swa.make_cs_table(16, tw))
+    rope_dev = tuple(t.to(DEV) for t in rope)
+    for which in (0, 1, 2):
+        assert swa.selected_impl(q.to(DEV), v.to(DEV), rope_dev, *win, 0.125, which=which) == "tc"
+    got, _ = run_gpu(q, k, v, do, rope, win, 0.125)
+    want = orc.fused_ref(q.float(), k.float(), v.float(), do.float(), *rope, *win, 0.125)
+    assert_close(got, want, torch.bfloat16, what=f"wide halo b={bs} col={cs}")
