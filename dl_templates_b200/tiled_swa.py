@@ -149,6 +149,8 @@ def swa_backward(q, k, v, o, lse, do, rope, b_size, t_height, t_width, row_size,
     ``(dq, dk, dv)`` tensors or strided views to write into (e.g. the three slices of one
     packed ``[B,N,3,H,d]`` gradient buffer)."""
     B, H, N, _ = q.shape
+    if do.stride(-1) != 1 or min(do.stride()[:3]) <= 0 or any(st % 8 for st in do.stride()[:3]) or do.data_ptr() % 16:
+        do = do.contiguous()     # e.g. the expanded gradient of ``o.sum()``: keep the tensor-core kernels eligible
     pad = padded_head_dims(q, v, rope, b_size, t_height, t_width, row_size, col_size, sm_scale, impl)
     if pad is not None:
         grads = swa_backward(_pad_last(q, pad[0]), _pad_last(k, pad[0]), _pad_last(v, pad[1]), _pad_last(o, pad[1]), lse,

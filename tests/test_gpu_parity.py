@@ -427,3 +427,20 @@ def test_wide_halo_runs_on_tensor_cores(bs, th, tw, rs, cs):
     got, _ = run_gpu(q, k, v, do, rope, win, 0.125)
     want = orc.fused_ref(q.float(), k.float(), v.float(), do.float(), *rope, *win, 0.125)
     assert_close(got, want, torch.bfloat16, what=f"wide halo b={bs} col={cs}")
+
+
+def test_expanded_gradient_keeps_tensor_core_path():
+    """``o.sum().backward()`` hands backward a stride-0 gradient; it is materialised once instead of pushing the
+    whole backward pass onto the SIMT kernels, and the result matches an explicit tensor of ones."""
+    torch.manual_seed(5)
+    q, k, v = (torch.randn(1, 2, 32 * 32, 64, device=DEV).to(torch.bfloat16).requires_grad_(True) for _ in range(3))
+    win = (1, 32, 32, 3, 3)
+    swa.TiledSwa.apply(q, k, v, *win, 0.125).sum().backward()
+    got = [t.grad.clone() for t in (q, k, v)]
+    for t in (q, k, v):
+        t.grad = None
+    o = swa.TiledSwa.apply(q, k, v, *win, 0.125)
+    o.backward(torch.ones_like(o))
+    swa.check_status()
+    for a, t in zip(got, (q, k, v)):
+        assert torch.equal(a, t.grad)
