@@ -102,6 +102,19 @@ def _pad_last(t, d):
     return t if t.shape[-1] == d else torch.nn.functional.pad(t, (0, d - t.shape[-1]))
 
 
+def _tc_addressable(t) -> bool:
+    """Unit last stride, positive strides that are multiples of 8 elements, 16-byte aligned base: what a tensor map
+    of the tensor-core kernels can describe (fp32 runs on the SIMT kernels, which take any strides)."""
+    st = t.stride()
+    return st[-1] == 1 and min(st[:3]) > 0 and not any(x % 8 for x in st[:3]) and t.data_ptr() % 16 == 0
+
+
+def _materialise(*tensors):
+    """16-bit tensors the tensor-core kernels cannot address are copied once rather than sending the call to
+    the SIMT kernels (two orders of magnitude slower); everything else is passed through untouched."""
+    return tuple(t if t.dtype == torch.float32 or _tc_addressable(t) else t.contiguous() for t in tensors)
+
+
 def _check_out(t, shape, like, what):
     if t.shape != shape or t.dtype != like.dtype or t.device != like.device:
         raise ValueError(f"{what}: expected shape {tuple(shape)}, dtype {like.dtype} on {like.device}")
@@ -114,6 +127,7 @@ def swa_forward(q, k, v, rope, b_size, t_height, t_width, row_size, col_size, sm
     of a ``[B,N,H*d_v]`` buffer for the output projection)."""
     _check_inputs(q, k, v, b_size, t_height, t_width)
     B, H, N, _ = q.shape
+    q, k, v = _materialise(q, k, v)
     pad = padded_head_dims(q, v, rope, b_size, t_height, t_width, row_size, col_size, sm_scale, impl)
     if pad is not None:
         o_p, lse = swa_forward(_pad_last(q, pad[0]), _pad_last(k, pad[0]), _pad_last(v, pad[1]), rope, b_size, t_height,
@@ -149,8 +163,7 @@ def swa_backward(q, k, v, o, lse, do, rope, b_size, t_height, t_width, row_size,
     ``(dq, dk, dv)`` tensors or strided views to write into (e.g. the three slices of one
     packed ``[B,N,3,H,d]`` gradient buffer)."""
     B, H, N, _ = q.shape
-    if do.stride(-1) != 1 or min(do.stride()[:3]) <= 0 or any(st % 8 for st in do.stride()[:3]) or do.data_ptr() % 16:
-        do = do.contiguous()     # e.g. the expanded gradient of ``o.sum()``: keep the tensor-core kernels eligible
+    q, k, v, o, do = _materialise(q, k, v, o, do)   # e.g. the expanded (stride-0) gradient of ``o.sum()``
     pad = padded_head_dims(q, v, rope, b_size, t_height, t_width, row_size, col_size, sm_scale, impl)
     if pad is not None:
         grads = swa_backward(_pad_last(q, pad[0]), _pad_last(k, pad[0]), _pad_last(v, pad[1]), _pad_last(o, pad[1]), lse,

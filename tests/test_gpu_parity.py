@@ -444,3 +444,21 @@ def test_expanded_gradient_keeps_tensor_core_path():
     swa.check_status()
     for a, t in zip(got, (q, k, v)):
         assert torch.equal(a, t.grad)
+
+
+def test_unaddressable_inputs_are_copied_not_demoted():
+    """q, k, v with a non-unit last stride (a transposed [B,H,d,N] buffer): same result as contiguous copies."""
+    torch.manual_seed(6)
+    base = [torch.randn(1, 2, 64, 24 * 24, device=DEV).to(torch.bfloat16) for _ in range(3)]
+    q, k, v = (t.transpose(-1, -2) for t in base)
+    assert q.stride(-1) != 1
+    win = (1, 24, 24, 2, 2)
+    o1, l1 = swa.swa_forward(q, k, v, None, *win, 0.125)
+    o2, l2 = swa.swa_forward(q.contiguous(), k.contiguous(), v.contiguous(), None, *win, 0.125)
+    do = torch.randn_like(o2)
+    g1 = swa.swa_backward(q, k, v, o1, l1, do, None, *win, 0.125)
+    g2 = swa.swa_backward(q.contiguous(), k.contiguous(), v.contiguous(), o2, l2, do, None, *win, 0.125)
+    swa.check_status()
+    assert torch.equal(o1, o2) and torch.equal(l1, l2)
+    for a, b in zip(g1, g2):
+        assert torch.equal(a, b)
