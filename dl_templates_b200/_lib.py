@@ -35,7 +35,8 @@ class Rope(C.Structure):
                 ("n_rdim", C.c_int32), ("max_h", C.c_int32), ("max_w", C.c_int32)]
 
 
-EXPORTS = ("swa_fwd", "swa_bwd_delta", "swa_bwd_dq", "swa_bwd_dkdv", "swa_bwd_noalloc", "rope2d_apply",
+EXPORTS = ("swa_fwd", "swa_bwd_delta", "swa_bwd_dq", "swa_bwd_dkdv", "swa_fwd_rot", "swa_bwd_dq_rot", "swa_bwd_dkdv_rot",
+           "swa_bwd_noalloc", "rope2d_apply",
            "rope2d_apply_to", "swa_select_impl", "swa_describe_plan", "swa_launch_count", "swa_last_error", "swa_version")
 
 
@@ -53,6 +54,10 @@ def _load() -> C.CDLL:
                                C.c_void_p, P(Tensor4), C.c_void_p, C.c_void_p]
     lib.swa_bwd_dkdv.argtypes = [P(Geom), P(Rope), P(Tensor4), P(Tensor4), P(Tensor4), P(Tensor4), C.c_void_p,
                                  C.c_void_p, P(Tensor4), P(Tensor4), C.c_void_p, C.c_void_p]
+    lib.swa_fwd_rot.argtypes = [P(Geom), P(Rope), P(Tensor4), P(Tensor4), P(Tensor4), P(Tensor4), C.c_void_p, P(Tensor4),
+                                P(Tensor4), C.c_void_p, C.c_void_p]
+    lib.swa_bwd_dq_rot.argtypes = lib.swa_bwd_dq.argtypes
+    lib.swa_bwd_dkdv_rot.argtypes = lib.swa_bwd_dkdv.argtypes
     lib.swa_bwd_noalloc.argtypes = [P(Geom), P(Rope), P(Tensor4), P(Tensor4), P(Tensor4), P(Tensor4), P(Tensor4),
                                     C.c_void_p, P(Tensor4), P(Tensor4), P(Tensor4), C.c_void_p, C.c_void_p]
     lib.rope2d_apply.argtypes = [C.c_int32, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, P(C.c_int64), P(Rope),
@@ -61,7 +66,8 @@ def _load() -> C.CDLL:
                                     P(C.c_int64), P(Rope), C.c_int32, C.c_void_p]
     lib.swa_select_impl.argtypes = [P(Geom), P(Rope), C.c_int32]
     lib.swa_describe_plan.argtypes = [P(Geom), P(Rope), C.c_int32, P(C.c_int32)]
-    for name in ("swa_fwd", "swa_bwd_delta", "swa_bwd_dq", "swa_bwd_dkdv", "swa_bwd_noalloc", "rope2d_apply",
+    for name in ("swa_fwd", "swa_bwd_delta", "swa_bwd_dq", "swa_bwd_dkdv", "swa_fwd_rot", "swa_bwd_dq_rot",
+                 "swa_bwd_dkdv_rot", "swa_bwd_noalloc", "rope2d_apply",
                  "rope2d_apply_to", "swa_select_impl", "swa_describe_plan", "swa_version"):
         getattr(lib, name).restype = C.c_int
     lib.swa_launch_count.restype = C.c_int64

@@ -179,4 +179,77 @@ __global__ void __launch_bounds__(256) rope2d_copy_kernel(const T* __restrict__ 
   *reinterpret_cast<uint4*>(y + bi * ys0 + tok * ys1 + u * 8) = own;
 }
 
+// The same one-pass clone + rotate for a strided [B, H, N, C] tensor (both tensors described by four element
+// strides): bh = b * H + h is decomposed per thread, so packed projection outputs need no flattening copy.
+template <typename T>
+__global__ void __launch_bounds__(256) rope2d_copy4_kernel(View4 x, View4 y, int64_t rows, int H, int64_t N, int C,
+                                                           RopeDev rp, float sign) {
+  const int upr = C >> 3;
+  const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t row = gid / upr;
+  if (row >= rows) return;
+  const int u = (int)(gid - row * upr);
+  const int64_t bh = row / N, tok = row - bh * N;
+  const int64_t b = bh / H, h = bh - b * H;
+  const T* src = (const T*)x.ptr + b * x.s0 + h * x.s1 + tok * x.s2 + u * 8;
+  uint4 own = *reinterpret_cast<const uint4*>(src);
+  const int e0 = u * 8;
+  if (e0 < 4 * rp.R) {
+    const int seg = e0 / rp.R, half = seg >> 1, second = seg & 1, i0 = e0 - seg * rp.R;
+    int irow, icol;
+    decode_idx(rp.idx[tok], rp.max_h, rp.max_w, irow, icol);
+    const int pos = half ? icol : irow;
+    if (pos >= 0) {
+      const uint4 oth = *reinterpret_cast<const uint4*>(second ? src - rp.R : src + rp.R);
+      const float* tab = (half ? rp.col_cs : rp.row_cs) + ((int64_t)pos * rp.R + i0) * 2;
+      float cs[16];
+#pragma unroll
+      for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(cs + j) = *reinterpret_cast<const float4*>(tab + j);
+      T* eo = reinterpret_cast<T*>(&own);
+      const T* ep = reinterpret_cast<const T*>(&oth);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float c = cs[2 * j], sn = cs[2 * j + 1] * sign;
+        const float a = second ? to_f(ep[j]) : to_f(eo[j]), bb = second ? to_f(eo[j]) : to_f(ep[j]);
+        eo[j] = from_f<T>(second ? a * sn + bb * c : a * c - bb * sn);
+      }
+    }
+  }
+  *reinterpret_cast<uint4*>((T*)y.ptr + b * y.s0 + h * y.s1 + tok * y.s2 + u * 8) = own;
+}
+
+// Element path of the same operation for any dtype and any strides; x == y (in place) is allowed.  One thread
+// per (token row, rotated pair): it reads both elements of its pair and writes both, and copies its share of the
+// dims beyond 4 * n_rdim when the operation is out of place.
+template <typename T>
+__global__ void __launch_bounds__(256) rope2d_generic4_kernel(View4 x, View4 y, int64_t rows, int H, int64_t N, int C,
+                                                              RopeDev rp, float sign) {
+  const int ppr = 2 * rp.R;   // pairs per row
+  const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t row = gid / ppr;
+  if (row >= rows) return;
+  const int pi = (int)(gid - row * ppr);
+  const int64_t bh = row / N, tok = row - bh * N;
+  const int64_t b = bh / H, h = bh - b * H;
+  const T* src = (const T*)x.ptr + b * x.s0 + h * x.s1 + tok * x.s2;
+  T* dst = (T*)y.ptr + b * y.s0 + h * y.s1 + tok * y.s2;
+  const int half = pi / rp.R, i = pi - half * rp.R;
+  const int d0 = 2 * half * rp.R + i, d1 = d0 + rp.R;
+  int irow, icol;
+  decode_idx(rp.idx[tok], rp.max_h, rp.max_w, irow, icol);
+  const int pos = half ? icol : irow;
+  float a = to_f(src[d0 * x.s3]), bb = to_f(src[d1 * x.s3]);
+  if (pos >= 0) {
+    const float* tab = (half ? rp.col_cs : rp.row_cs) + ((int64_t)pos * rp.R + i) * 2;
+    const float c = tab[0], sn = tab[1] * sign;
+    const float ra = a * c - bb * sn, rb = a * sn + bb * c;
+    a = ra;
+    bb = rb;
+  }
+  dst[d0 * y.s3] = from_f<T>(a);
+  dst[d1 * y.s3] = from_f<T>(bb);
+  if (src != dst || x.s3 != y.s3)
+    for (int d = 4 * rp.R + pi; d < C; d += ppr) dst[d * y.s3] = src[d * x.s3];
+}
+
 }  // namespace swa

@@ -75,8 +75,8 @@ int launch_ok(const char* what) {
 
 // Resolve AUTO / reject TC requests the tensor-core kernels cannot serve.
 int resolve_impl(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* const* tensors, int n_tensors,
-                 int which) {
-  const char* why = swa::tc::unsupported_reason(g, rope, tensors, n_tensors, which);
+                 int which, bool prerotated = false) {
+  const char* why = swa::tc::unsupported_reason(g, rope, tensors, n_tensors, which, prerotated);
   if (g->impl == SWA_IMPL_SIMT) return SWA_IMPL_SIMT;
   if (why == nullptr) return SWA_IMPL_TC;
   if (g->impl == SWA_IMPL_TC) return fail(E_IMPL, "tensor-core path unavailable: %s", why);
@@ -250,6 +250,147 @@ int swa_bwd_dkdv(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t
   return launch_ok("simt dkdv");
 }
 
+// ---- rotation handed on between the kernels ---------------------------------------------------
+namespace {
+
+// y = rope(x) (inverse: the transposed rotation) for a strided [B, H, N, C] tensor; x == y rotates in place.
+int launch_rope4(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* x, const swa_tensor_t* y, bool inverse,
+                 cudaStream_t st) {
+  const swa::RopeDev rp = swa::make_rope(rope);
+  const int64_t N = (int64_t)g->t_height * g->t_width * g->b_size;
+  const int64_t rows = N * g->B * g->H;
+  const int C = g->d_qk;
+  const float sign = inverse ? -1.f : 1.f;
+  auto rows16 = [](const swa_tensor_t* t) {
+    return t->stride[3] == 1 && ((uintptr_t)t->ptr % 16) == 0 && t->stride[0] % 8 == 0 && t->stride[1] % 8 == 0 &&
+           t->stride[2] % 8 == 0;
+  };
+  const bool vec = g->dtype != SWA_F32 && x->ptr != y->ptr && rp.R % 8 == 0 && C % 8 == 0 && rows16(x) && rows16(y) &&
+                   ((uintptr_t)rp.row_cs % 16) == 0 && ((uintptr_t)rp.col_cs % 16) == 0;
+  if (vec) {
+    const int64_t threads = rows * (C / 8);
+    const unsigned blocks = (unsigned)((threads + 255) / 256);
+    if (g->dtype == SWA_F16)
+      swa::rope2d_copy4_kernel<__half><<<blocks, 256, 0, st>>>(swa::make_view(x), swa::make_view(y), rows, g->H, N, C, rp, sign);
+    else
+      swa::rope2d_copy4_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(swa::make_view(x), swa::make_view(y), rows, g->H, N, C, rp, sign);
+  } else {
+    const int64_t threads = rows * 2 * rp.R;
+    const unsigned blocks = (unsigned)((threads + 255) / 256);
+    SWA_DISPATCH_DTYPE(g->dtype, swa::rope2d_generic4_kernel<T><<<blocks, 256, 0, st>>>(swa::make_view(x), swa::make_view(y),
+                                                                                      rows, g->H, N, C, rp, sign));
+  }
+  return launch_ok("rope2d (4-D)");
+}
+
+int require_rope(const swa_rope_t* rope, const char* who) {
+  if (!rope || !rope->idx) return fail(E_ROPE, "%s needs a RoPE description (idx and tables); without RoPE use the plain entry point", who);
+  return 0;
+}
+
+}  // namespace
+
+int swa_fwd_rot(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
+                const swa_tensor_t* v, const swa_tensor_t* o, float* lse, const swa_tensor_t* q_rot,
+                const swa_tensor_t* k_rot, int32_t* status, void* stream) {
+  if (int e = check_geom(g)) return e;
+  if (int e = require_rope(rope, "swa_fwd_rot")) return e;
+  if (int e = check_rope(g, rope)) return e;
+  if (int e = check_tensor(q, "q")) return e;
+  if (int e = check_tensor(k, "k")) return e;
+  if (int e = check_tensor(v, "v")) return e;
+  if (int e = check_tensor(o, "o")) return e;
+  if (int e = check_tensor(q_rot, "q_rot")) return e;
+  if (int e = check_tensor(k_rot, "k_rot")) return e;
+  if (!lse) return fail(E_NULL, "lse is NULL");
+  if (q_rot->ptr == q->ptr || k_rot->ptr == k->ptr) return fail(E_SHAPE, "q_rot / k_rot must not alias q / k");
+  const swa_tensor_t* ts[] = {q, k, v, o, q_rot, k_rot};
+  const int impl = resolve_impl(g, rope, ts, 6, 0, true);
+  if (impl < 0) return impl;
+  cudaStream_t st = (cudaStream_t)stream;
+  // every key row is rotated exactly once, by a streaming pass; the attention kernel streams the rotated rows
+  if (int e = launch_rope4(g, rope, k, k_rot, false, st)) return e;
+  if (impl == SWA_IMPL_TC) {
+    int e = swa::tc::launch_fwd2(g, rope, q, k_rot, v, o, lse, q_rot, status, st);
+    if (e) return fail(E_LAUNCH, "tcgen05 forward: %s", swa::tc::last_error());
+    return launch_ok("tcgen05 forward (rotation handed on)");
+  }
+  if (int e = launch_rope4(g, rope, q, q_rot, false, st)) return e;
+  const swa::Geom gg = swa::make_geom(g);
+  const swa::RopeDev none = swa::make_rope(nullptr);
+  const int N = g->t_height * g->t_width * g->b_size;
+  dim3 grid((N + 7) / 8, g->B * g->H), block(256);
+  SWA_DISPATCH_DTYPE(g->dtype, swa::simt_fwd_kernel<T><<<grid, block, 0, st>>>(
+                                   gg, none, swa::make_view(q_rot), swa::make_view(k_rot), swa::make_view(v),
+                                   swa::make_view(o), lse));
+  return launch_ok("simt forward");
+}
+
+int swa_bwd_dq_rot(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q_rot, const swa_tensor_t* k_rot,
+                   const swa_tensor_t* v, const swa_tensor_t* d_o, const float* lse, const float* delta,
+                   const swa_tensor_t* dq, int32_t* status, void* stream) {
+  if (int e = check_geom(g)) return e;
+  if (int e = require_rope(rope, "swa_bwd_dq_rot")) return e;
+  if (int e = check_rope(g, rope)) return e;
+  if (int e = check_tensor(q_rot, "q_rot")) return e;
+  if (int e = check_tensor(k_rot, "k_rot")) return e;
+  if (int e = check_tensor(v, "v")) return e;
+  if (int e = check_tensor(d_o, "do")) return e;
+  if (int e = check_tensor(dq, "dq")) return e;
+  if (!lse || !delta) return fail(E_NULL, "lse/delta is NULL");
+  const swa_tensor_t* ts[] = {q_rot, k_rot, v, d_o, dq};
+  const int impl = resolve_impl(g, rope, ts, 5, 1, true);
+  if (impl < 0) return impl;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (impl == SWA_IMPL_TC) {
+    int e = swa::tc::launch_dq(g, rope, q_rot, k_rot, v, d_o, lse, delta, dq, status, st, true);
+    if (e) return fail(E_LAUNCH, "tcgen05 dq: %s", swa::tc::last_error());
+    return launch_ok("tcgen05 dq (inputs rotated)");
+  }
+  const swa::Geom gg = swa::make_geom(g);
+  const swa::RopeDev none = swa::make_rope(nullptr);
+  const int N = g->t_height * g->t_width * g->b_size;
+  dim3 grid((N + 7) / 8, g->B * g->H), block(256);
+  SWA_DISPATCH_DTYPE(g->dtype, swa::simt_dq_kernel<T><<<grid, block, 0, st>>>(
+                                   gg, none, swa::make_view(q_rot), swa::make_view(k_rot), swa::make_view(v),
+                                   swa::make_view(d_o), lse, delta, swa::make_view(dq)));
+  if (int e = launch_ok("simt dq")) return e;
+  return launch_rope4(g, rope, dq, dq, true, st);
+}
+
+int swa_bwd_dkdv_rot(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q_rot, const swa_tensor_t* k_rot,
+                     const swa_tensor_t* v, const swa_tensor_t* d_o, const float* lse, const float* delta,
+                     const swa_tensor_t* dk, const swa_tensor_t* dv, int32_t* status, void* stream) {
+  if (int e = check_geom(g)) return e;
+  if (int e = require_rope(rope, "swa_bwd_dkdv_rot")) return e;
+  if (int e = check_rope(g, rope)) return e;
+  if (int e = check_tensor(q_rot, "q_rot")) return e;
+  if (int e = check_tensor(k_rot, "k_rot")) return e;
+  if (int e = check_tensor(v, "v")) return e;
+  if (int e = check_tensor(d_o, "do")) return e;
+  if (int e = check_tensor(dk, "dk")) return e;
+  if (int e = check_tensor(dv, "dv")) return e;
+  if (!lse || !delta) return fail(E_NULL, "lse/delta is NULL");
+  const swa_tensor_t* ts[] = {q_rot, k_rot, v, d_o, dk, dv};
+  const int impl = resolve_impl(g, rope, ts, 6, 2, true);
+  if (impl < 0) return impl;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (impl == SWA_IMPL_TC) {
+    int e = swa::tc::launch_dkdv(g, rope, q_rot, k_rot, v, d_o, lse, delta, dk, dv, status, st, true);
+    if (e) return fail(E_LAUNCH, "tcgen05 dkdv: %s", swa::tc::last_error());
+    return launch_ok("tcgen05 dkdv (inputs rotated)");
+  }
+  const swa::Geom gg = swa::make_geom(g);
+  const swa::RopeDev none = swa::make_rope(nullptr);
+  const int N = g->t_height * g->t_width * g->b_size;
+  dim3 grid((N + 7) / 8, g->B * g->H), block(256);
+  SWA_DISPATCH_DTYPE(g->dtype, swa::simt_dkdv_kernel<T><<<grid, block, 0, st>>>(
+                                   gg, none, swa::make_view(q_rot), swa::make_view(k_rot), swa::make_view(v),
+                                   swa::make_view(d_o), lse, delta, swa::make_view(dk), swa::make_view(dv)));
+  if (int e = launch_ok("simt dkdv")) return e;
+  return launch_rope4(g, rope, dk, dk, true, st);
+}
+
 // ---- backward without allocation ------------------------------------------------------------
 // Scratch for the softmax delta of swa_bwd_noalloc.  In host code this name is only a handle of
 // the symbol, not a device address: the address is looked up once per device below.
@@ -288,6 +429,23 @@ int swa_bwd_noalloc(const swa_geom_t* g, const swa_rope_t* rope, const swa_tenso
   if (rows > (int64_t)SWA_NOALLOC_MAX_ROWS)
     return fail(E_SHAPE, "swa_bwd_noalloc: B*H*N = %lld exceeds the built-in scratch of %d rows; use swa_bwd_delta/"
                 "swa_bwd_dq/swa_bwd_dkdv with a caller-provided delta buffer", (long long)rows, SWA_NOALLOC_MAX_ROWS);
+  // every rejection the three launches below could raise is raised here, before the first of them
+  if (int e = check_rope(g, rope)) return e;
+  if (int e = check_tensor(q, "q")) return e;
+  if (int e = check_tensor(k, "k")) return e;
+  if (int e = check_tensor(v, "v")) return e;
+  if (int e = check_tensor(o, "o")) return e;
+  if (int e = check_tensor(d_o, "do")) return e;
+  if (int e = check_tensor(dq, "dq")) return e;
+  if (int e = check_tensor(dk, "dk")) return e;
+  if (int e = check_tensor(dv, "dv")) return e;
+  if (!lse) return fail(E_NULL, "lse is NULL");
+  {
+    const swa_tensor_t* t1[] = {q, k, v, d_o, dq};
+    const swa_tensor_t* t2[] = {q, k, v, d_o, dk, dv};
+    if (int e = resolve_impl(g, rope, t1, 5, 1); e < 0) return e;
+    if (int e = resolve_impl(g, rope, t2, 6, 2); e < 0) return e;
+  }
   float* delta = nullptr;
   if (int e = noalloc_scratch(&delta)) return e;
   if (int e = swa_bwd_delta(g, o, d_o, delta, stream)) return e;

@@ -10,7 +10,9 @@
 
 #include "swa_tc.cuh"
 #include "swa_tc_bwd.cuh"
+#include "swa_tc_bwd2.cuh"
 #include "swa_tc_fwd.cuh"
+#include "swa_tc_fwd2.cuh"
 
 namespace swa {
 namespace tc {
@@ -110,7 +112,7 @@ bool make_plan_shape(const swa_geom_t* g, int which, int TH, int TW, uint32_t ta
   const int acc_cols = which == 0 ? 0 : (which == 1 ? 64 * qch : 64 * (qch + vch));
   const int min_stages = 3;
   // alignment pad of the swizzled tiles + the kernel's barrier / exchange / penalty-table block behind the ring
-  const uint32_t kSmemSlack = 1024u + (((which == 0 ? (uint32_t)sizeof(FwdShared) : (uint32_t)sizeof(BwdShared)) + 15u) & ~15u);
+  const uint32_t kSmemSlack = 1024u + (((which == 0 ? (uint32_t)sizeof(FwdShared) + 64u : (uint32_t)sizeof(BwdShared)) + 15u) & ~15u);
   {
     // backward: two (S, dP) pairs of 2N columns next to the accumulators (N = 64 always fits: 256 + 256 columns)
     const int nsb = 2;
@@ -264,7 +266,7 @@ bool tensor_ok(const swa_tensor_t* t) {
 const char* last_error() { return g_tc_err; }
 
 const char* unsupported_reason(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* const* tensors,
-                               int n_tensors, int which) {
+                               int n_tensors, int which, bool prerotated) {
   if (getenv("SWA_TC_DISABLE")) return "disabled by SWA_TC_DISABLE";
   if (g->dtype != SWA_F16 && g->dtype != SWA_BF16) return "fp32 runs on the SIMT kernels";
   if ((g->d_qk != 64 && g->d_qk != 128) || (g->d_v != 64 && g->d_v != 128)) return "head dims must be 64 or 128";
@@ -276,7 +278,7 @@ const char* unsupported_reason(const swa_geom_t* g, const swa_rope_t* rope, cons
   if (g->row_size > 64) return "row window too tall for the penalty tables";
   if ((int64_t)g->t_height * g->t_width * g->b_size > (1 << 30)) return "grid too large";
   Plan pl;
-  if (!make_plan(g, rope, which, &pl))
+  if (!make_plan(g, prerotated ? nullptr : rope, which, &pl))
     return "no tile plan fits (window too wide for one streamed block)";
   for (int i = 0; i < n_tensors; ++i)
     if (!tensor_ok(tensors[i])) return "tensors need unit last stride and 16-byte aligned rows";
@@ -290,7 +292,7 @@ bool describe_plan(const swa_geom_t* g, const swa_rope_t* rope, int which, int32
   uint32_t used = 1023, tmem = 0;   // worst-case pad to the 1024-byte alignment of the swizzled tiles
   if (which == 0) {
     used += 2 * qch * 16384u + 128u * kXRowBytes + pl.stages * N * ((qch + vch) * 128u + kXRowBytes);
-    used += ((uint32_t)sizeof(FwdShared) + 15u) & ~15u;
+    used += ((uint32_t)sizeof(FwdShared) + 64u + 15u) & ~15u;   // the larger of the two forward kernels' blocks
     const uint32_t o_cols = vch * 64u;
     const uint32_t stride = (N <= 128u && pl.nsb * 128u + 2 * o_cols <= 512u) ? 128u : N;
     tmem = pl.nsb * stride + 2 * o_cols;
@@ -309,6 +311,7 @@ bool describe_plan(const swa_geom_t* g, const swa_rope_t* rope, int which, int32
 
 int launch_fwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
                const swa_tensor_t* v, const swa_tensor_t* o, float* lse, int32_t* status, cudaStream_t st) {
+  if (!(rope && rope->idx)) return launch_fwd2(g, nullptr, q, k, v, o, lse, nullptr, status, st);
   Plan pl;
   if (!make_plan(g, rope, 0, &pl)) {
     snprintf(g_tc_err, sizeof(g_tc_err), "no tile plan");
@@ -349,14 +352,54 @@ int launch_fwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* 
   return 0;
 }
 
+int launch_fwd2(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
+                const swa_tensor_t* v, const swa_tensor_t* o, float* lse, const swa_tensor_t* q_rot, int32_t* status,
+                cudaStream_t st) {
+  Plan pl;
+  if (!make_plan(g, nullptr, 0, &pl)) {      // no streamed row is rotated: the plan of the problem without RoPE
+    snprintf(g_tc_err, sizeof(g_tc_err), "no tile plan");
+    return -1;
+  }
+  CUtensorMap tq, tk, tv;
+  if (!make_map(&tq, q, g, g->d_qk, pl.TW, pl.TH) || !make_map(&tk, k, g, g->d_qk, pl.KW, pl.KR) ||
+      !make_map(&tv, v, g, g->d_v, pl.KW, pl.KR))
+    return -1;
+  const KParams p = make_params(g, rope, pl, status);
+  const int sms = sm_count();
+  dim3 grid(p.n_items < sms ? p.n_items : sms), block(kFwdThreads);   // persistent: one CTA per SM walks the items
+  using Fwd2Kernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, KParams, View4, float*, View4);
+  // [dtype][n_rdim / 8 of the query rotation]
+  static const Fwd2Kernel table[2][5] = {
+      {fwd2_kernel<false, 0>, fwd2_kernel<false, 1>, fwd2_kernel<false, 2>, nullptr, fwd2_kernel<false, 4>},
+      {fwd2_kernel<true, 0>, fwd2_kernel<true, 1>, fwd2_kernel<true, 2>, nullptr, fwd2_kernel<true, 4>}};
+  const int ni = (rope && rope->idx) ? rope->n_rdim / 8 : 0;
+  Fwd2Kernel kern = table[g->dtype == SWA_BF16 ? 1 : 0][ni];
+  if (kern == nullptr) {
+    snprintf(g_tc_err, sizeof(g_tc_err), "n_rdim %d has no tensor-core kernel", rope ? rope->n_rdim : 0);
+    return -1;
+  }
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem_bytes);
+  if (e != cudaSuccess) {
+    snprintf(g_tc_err, sizeof(g_tc_err), "cudaFuncSetAttribute(%u bytes): %s", pl.smem_bytes, cudaGetErrorString(e));
+    return -1;
+  }
+  if (getenv("SWA_TC_VERBOSE"))
+    fprintf(stderr, "[swa2d] fwd2 plan: tile %dx%d, block %dx%d (N=%d), stages %d, score buffers %d, smem %u, %d items on %u CTAs\n",
+            pl.TH, pl.TW, pl.KR, pl.KW, pl.N, pl.stages, pl.nsb, pl.smem_bytes, p.n_items, grid.x);
+  kern<<<grid, block, pl.smem_bytes, st>>>(tq, tk, tv, p, make_view(o), lse, q_rot ? make_view(q_rot) : View4{nullptr, 0, 0, 0, 0});
+  return 0;
+}
+
 namespace {
 
+// `prerotated`: q and k are rotated copies made by an earlier kernel (the forward kernel of swa_fwd_rot); the
+// kernels then run in their no-RoPE structure and only rotate dQ / dK back in the epilogue.
 template <bool DKDV>
-int launch_bwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* xqk, const swa_tensor_t* xv,
+int launch_bwd(const swa_geom_t* g, const swa_rope_t* rope, bool prerotated, const swa_tensor_t* xqk, const swa_tensor_t* xv,
                const swa_tensor_t* yqk, const swa_tensor_t* yv, const float* lse, const float* delta,
                const swa_tensor_t* out_qk, const swa_tensor_t* out_v, int32_t* status, cudaStream_t st) {
   Plan pl;
-  if (!make_plan(g, rope, DKDV ? 2 : 1, &pl)) {
+  if (!make_plan(g, prerotated ? nullptr : rope, DKDV ? 2 : 1, &pl)) {
     snprintf(g_tc_err, sizeof(g_tc_err), "no tile plan");
     return -1;
   }
@@ -369,17 +412,19 @@ int launch_bwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* 
   dim3 grid(p.n_items < sms ? p.n_items : sms), block(kBwdThreads);   // persistent: one CTA per SM walks the items
   using BwdKernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, KParams, const float*,
                              const float*, View4, View4);
-  static const BwdKernel bwd_table[2][2][5] = {
-      {{bwd_kernel<false, DKDV, 0, false>, bwd_kernel<false, DKDV, 1, false>, bwd_kernel<false, DKDV, 2, false>, nullptr,
-        bwd_kernel<false, DKDV, 4, false>},
-       {bwd_kernel<false, DKDV, 0, false>, bwd_kernel<false, DKDV, 1, true>, bwd_kernel<false, DKDV, 2, true>, nullptr,
-        bwd_kernel<false, DKDV, 4, true>}},
-      {{bwd_kernel<true, DKDV, 0, false>, bwd_kernel<true, DKDV, 1, false>, bwd_kernel<true, DKDV, 2, false>, nullptr,
-        bwd_kernel<true, DKDV, 4, false>},
-       {bwd_kernel<true, DKDV, 0, false>, bwd_kernel<true, DKDV, 1, true>, bwd_kernel<true, DKDV, 2, true>, nullptr,
-        bwd_kernel<true, DKDV, 4, true>}}};
+  // [dtype][tables staged][n_rdim / 8]: q / k rotated in shared memory, dQ / dK rotated back in the epilogue
+  static const BwdKernel fused_table[2][2][5] = {
+      {{nullptr, bwd_kernel<false, DKDV, 1, false>, bwd_kernel<false, DKDV, 2, false>, nullptr, bwd_kernel<false, DKDV, 4, false>},
+       {nullptr, bwd_kernel<false, DKDV, 1, true>, bwd_kernel<false, DKDV, 2, true>, nullptr, bwd_kernel<false, DKDV, 4, true>}},
+      {{nullptr, bwd_kernel<true, DKDV, 1, false>, bwd_kernel<true, DKDV, 2, false>, nullptr, bwd_kernel<true, DKDV, 4, false>},
+       {nullptr, bwd_kernel<true, DKDV, 1, true>, bwd_kernel<true, DKDV, 2, true>, nullptr, bwd_kernel<true, DKDV, 4, true>}}};
+  // [dtype][n_rdim / 8]: no RoPE, or inputs already rotated and only the epilogue rotation
+  static const BwdKernel prerot_table[2][5] = {
+      {bwd2_kernel<false, DKDV, 0>, bwd2_kernel<false, DKDV, 1>, bwd2_kernel<false, DKDV, 2>, nullptr, bwd2_kernel<false, DKDV, 4>},
+      {bwd2_kernel<true, DKDV, 0>, bwd2_kernel<true, DKDV, 1>, bwd2_kernel<true, DKDV, 2>, nullptr, bwd2_kernel<true, DKDV, 4>}};
   const int ni = (rope && rope->idx) ? rope->n_rdim / 8 : 0;
-  BwdKernel kern = bwd_table[g->dtype == SWA_BF16 ? 1 : 0][pl.tab_bytes ? 1 : 0][ni];
+  const int bf = g->dtype == SWA_BF16 ? 1 : 0;
+  BwdKernel kern = (prerotated || ni == 0) ? prerot_table[bf][ni] : fused_table[bf][pl.tab_bytes ? 1 : 0][ni];
   if (kern == nullptr) {
     snprintf(g_tc_err, sizeof(g_tc_err), "n_rdim %d has no tensor-core kernel", rope ? rope->n_rdim : 0);
     return -1;
@@ -401,14 +446,14 @@ int launch_bwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* 
 
 int launch_dq(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
               const swa_tensor_t* v, const swa_tensor_t* d_o, const float* lse, const float* delta,
-              const swa_tensor_t* dq, int32_t* status, cudaStream_t st) {
-  return launch_bwd<false>(g, rope, q, d_o, k, v, lse, delta, dq, nullptr, status, st);
+              const swa_tensor_t* dq, int32_t* status, cudaStream_t st, bool prerotated) {
+  return launch_bwd<false>(g, rope, prerotated, q, d_o, k, v, lse, delta, dq, nullptr, status, st);
 }
 
 int launch_dkdv(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
                 const swa_tensor_t* v, const swa_tensor_t* d_o, const float* lse, const float* delta,
-                const swa_tensor_t* dk, const swa_tensor_t* dv, int32_t* status, cudaStream_t st) {
-  return launch_bwd<true>(g, rope, k, v, q, d_o, lse, delta, dk, dv, status, st);
+                const swa_tensor_t* dk, const swa_tensor_t* dv, int32_t* status, cudaStream_t st, bool prerotated) {
+  return launch_bwd<true>(g, rope, prerotated, k, v, q, d_o, lse, delta, dk, dv, status, st);
 }
 
 }  // namespace tc

@@ -8,8 +8,10 @@ namespace tc {
 
 // nullptr when the tensor-core kernels cover this call, else the reason they do not.
 // `which`: 0 forward, 1 dQ, 2 dK/dV.  `tensors` may be null (shape-only query).
+// `prerotated`: the call hands rotated copies of q / k between the kernels (swa_fwd_rot and the *_rot backward
+// entries), so no kernel rotates streamed rows and the plan is the one without RoPE.
 const char* unsupported_reason(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* const* tensors,
-                               int n_tensors, int which);
+                               int n_tensors, int which, bool prerotated = false);
 const char* last_error();
 
 // Resource plan the tensor-core kernel `which` would run with (host-only, no GPU needed): out[0..11] =
@@ -20,12 +22,17 @@ bool describe_plan(const swa_geom_t* g, const swa_rope_t* rope, int which, int32
 
 int launch_fwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
                const swa_tensor_t* v, const swa_tensor_t* o, float* lse, int32_t* status, cudaStream_t st);
+// Forward with the keys already rotated (or no RoPE at all: rope == nullptr): the query tile is rotated on chip
+// and, when q_rot != nullptr, the rotated rows are stored there.
+int launch_fwd2(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
+                const swa_tensor_t* v, const swa_tensor_t* o, float* lse, const swa_tensor_t* q_rot, int32_t* status,
+                cudaStream_t st);
 int launch_dq(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
               const swa_tensor_t* v, const swa_tensor_t* d_o, const float* lse, const float* delta,
-              const swa_tensor_t* dq, int32_t* status, cudaStream_t st);
+              const swa_tensor_t* dq, int32_t* status, cudaStream_t st, bool prerotated = false);
 int launch_dkdv(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
                 const swa_tensor_t* v, const swa_tensor_t* d_o, const float* lse, const float* delta,
-                const swa_tensor_t* dk, const swa_tensor_t* dv, int32_t* status, cudaStream_t st);
+                const swa_tensor_t* dk, const swa_tensor_t* dv, int32_t* status, cudaStream_t st, bool prerotated = false);
 
 }  // namespace tc
 }  // namespace swa

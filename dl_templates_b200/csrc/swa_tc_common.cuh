@@ -398,6 +398,14 @@ __device__ __forceinline__ void trace_mark(const KParams& p, int role, int k) {
 #endif
 }
 
+// Event log of one CTA (performance debugging, -DSWA_TC_TRACE only): one designated thread of a role
+// appends (clock << 8 | tag) to that role's row of 256 entries; `n` is the thread's own cursor.
+__device__ __forceinline__ void trace_ev(const KParams& p, int role, int& n, bool on, int tag) {
+#ifdef SWA_TC_TRACE
+  if (on && p.trace != nullptr && blockIdx.x == 37 && n < 256) p.trace[128 + role * 256 + n++] = (clock64() << 8) | (long long)(tag & 255);
+#endif
+}
+
 // Record a timed-out wait (first one wins) so the host can report it.
 __device__ __forceinline__ void report_abort(int32_t* status, int code, int where) {
   if (status != nullptr && atomicCAS(status, 0, code) == 0) {

@@ -147,7 +147,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     const uint32_t o_tm = lane_base + o_base + g * o_cols, o_other = lane_base + o_base + (g ^ 1) * o_cols;
     const float c2 = p.scale_log2;
     const int ng = N >> 4;                        // 16-column granules of a row
-    const bool tr = (m == 0 && g == 0);
+    const bool tr = (m == 0);
+    const int trole = g ? 0 : 2;              // trace rows: group 0 -> 2, group 1 -> 0
     uint32_t gbase = 0;                           // stream position of the current item's block 0
     // this group's next block: stream position, its score buffer and that buffer's barrier parity
     uint32_t own_next = g, n_own = 0;
@@ -169,7 +170,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       const int see_lo = tp.r0 + (quarter * 32) / pl.TW - p.wr, see_hi = tp.r0 + (quarter * 32 + 31) / pl.TW + p.wr;
       float m_used = -INFINITY, l = 0.f;
       int cnt = 0;                                // blocks of this item this group has handed to the PV MMA
-      if (tr && it == p.trace_it) trace_mark(p, 2, 29);
+      if (tr && it == p.trace_it) trace_mark(p, trole, 29);
       int j = have ? (int)(own_next - gbase) : 0;
       bool first = true;
 #pragma unroll 1
@@ -182,7 +183,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         if (sbuf >= nsb) { sbuf -= nsb; spar ^= 1; }
         const int blk_first = tp.hr_first + j * pl.KR, blk_last = blk_first + pl.KR - 1;
         const bool seen = !(blk_last < see_lo || blk_first > see_hi);
-        if (tr && it == p.trace_it) trace_mark(p, 2, 1 + 4 * (j >> 1));
+        if (tr && it == p.trace_it) trace_mark(p, trole, 1 + 4 * (j >> 1));
         if (ok) {
         tc_fence_after();
         uint32_t ra[16], rb[16];
@@ -213,7 +214,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           tmem_ld16(s_tm, ra);                            // first granule of pass 2, in flight during the bookkeeping
           float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
           if (mx < none_thresh) mx = -INFINITY;
-          if (tr && it == p.trace_it) trace_mark(p, 2, 2 + 4 * (j >> 1));
+          if (tr && it == p.trace_it) trace_mark(p, trole, 2 + 4 * (j >> 1));
           // running max with lazy rescale: keep scaling by m_used until the true max exceeds it by 2^8
           bool need = false;
           float m_new = m_used;
@@ -273,7 +274,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         tc_fence_before();
         mbar_arrive(p_bar);
         }
-        if (tr && it == p.trace_it) trace_mark(p, 2, 4 + 4 * (j >> 1));
+        if (tr && it == p.trace_it) trace_mark(p, trole, 4 + 4 * (j >> 1));
         j += 2;
         own_next += 2;
         ++n_own;
@@ -296,7 +297,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       const float m_o = sh->ml[par][g ^ 1][0][m], l_o = sh->ml[par][g ^ 1][1][m];
       if (ok) {
         tc_fence_after();
-        if (tr && pend_it == p.trace_it) trace_mark(p, 2, 30);
+        if (tr && pend_it == p.trace_it) trace_mark(p, trole, 30);
         // Merge in an order fixed by the blocks' positions in the item (even ones first), not by which
         // group happened to get them: the result of a tile must not depend on the work that preceded it.
         const bool mine_even = pend_even;
@@ -342,7 +343,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           }
         }
         if (q_in && g == 0) lse[(int64_t)e_bh * p.t_h * p.Wtok + tok] = mm * c2 + log2f(lt);
-        if (tr && pend_it == p.trace_it) trace_mark(p, 2, 31);
+        if (tr && pend_it == p.trace_it) trace_mark(p, trole, 31);
       }
       }
       }

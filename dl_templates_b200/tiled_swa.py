@@ -199,6 +199,69 @@ def swa_backward(q, k, v, o, lse, do, rope, b_size, t_height, t_width, row_size,
     return dq, dk, dv
 
 
+def swa_forward_rot(q, k, v, rope, b_size, t_height, t_width, row_size, col_size, sm_scale, impl="auto", out=None):
+    """Forward with the rotation handed on (``swa_fwd_rot``): returns ``(o, lse, q_rot, k_rot)``.
+
+    Every key row is rotated once by a streaming pass into ``k_rot``, every query tile is rotated on chip by the
+    attention kernel, which stores the rotated rows to ``q_rot``; ``q`` and ``k`` stay untouched.  ``q_rot`` and
+    ``k_rot`` are what ``swa_backward_rot`` takes in place of ``q`` and ``k`` -- the tensors the reference keeps for
+    backward as well, since its RoPE rotates q and k in place (src/fused_rope2d.py:143-145).  ``rope`` =
+    ``(idx, row_cs, col_cs)`` is required; ``out`` as in ``swa_forward``."""
+    _check_inputs(q, k, v, b_size, t_height, t_width)
+    B, H, N, _ = q.shape
+    q, k, v = _materialise(q, k, v)
+    with torch.cuda.device(q.device):
+        if out is None:
+            o = torch.empty((B, H, N, v.shape[-1]), dtype=q.dtype, device=q.device)
+        else:
+            o = out
+            _check_out(o, (B, H, N, v.shape[-1]), q, "out")
+        lse = torch.empty((B, H, N), dtype=torch.float32, device=q.device)
+        q_rot = torch.empty((B, H, N, q.shape[-1]), dtype=q.dtype, device=q.device)
+        k_rot = torch.empty_like(q_rot)
+        g = _geom(q, v, b_size, t_height, t_width, row_size, col_size, sm_scale, impl)
+        r = _lib.make_rope(*rope)
+        tq, tk, tv, to, tqr, tkr = (_lib.tensor4(t) for t in (q, k, v, o, q_rot, k_rot))
+        code = _lib.lib.swa_fwd_rot(C.byref(g), C.byref(r), C.byref(tq), C.byref(tk), C.byref(tv), C.byref(to),
+                                    lse.data_ptr(), C.byref(tqr), C.byref(tkr), _status(q.device).data_ptr(),
+                                    _lib.stream_ptr(q.device))
+    _lib.check(code, "swa_fwd_rot")
+    if os.environ.get("SWA_DEBUG_SYNC"):
+        check_status()
+    return o, lse, q_rot, k_rot
+
+
+def swa_backward_rot(q_rot, k_rot, v, o, lse, do, rope, b_size, t_height, t_width, row_size, col_size, sm_scale,
+                     impl="auto", out=None):
+    """Backward pass on the rotated copies ``swa_forward_rot`` left behind: delta, ``swa_bwd_dq_rot``,
+    ``swa_bwd_dkdv_rot``.  Returns ``(dq, dk, dv)``, gradients of the UN-rotated q and k (the kernels rotate dq and
+    dk back in their epilogues).  ``out`` as in ``swa_backward``."""
+    B, H, N, _ = q_rot.shape
+    q_rot, k_rot, v, o, do = _materialise(q_rot, k_rot, v, o, do)
+    with torch.cuda.device(q_rot.device):
+        if out is None:
+            dq, dk, dv = torch.empty_like(q_rot), torch.empty_like(k_rot), torch.empty_like(v)
+        else:
+            dq, dk, dv = out
+            for t, like, what in ((dq, q_rot, "dq"), (dk, k_rot, "dk"), (dv, v, "dv")):
+                _check_out(t, like.shape, like, what)
+        delta = torch.empty((B, H, N), dtype=torch.float32, device=q_rot.device)
+        g = _geom(q_rot, v, b_size, t_height, t_width, row_size, col_size, sm_scale, impl)
+        r = _lib.make_rope(*rope)
+        tq, tk, tv, to, tdo, tdq, tdk, tdv = (_lib.tensor4(t) for t in (q_rot, k_rot, v, o, do, dq, dk, dv))
+        st, status = _lib.stream_ptr(q_rot.device), _status(q_rot.device).data_ptr()
+        _lib.check(_lib.lib.swa_bwd_delta(C.byref(g), C.byref(to), C.byref(tdo), delta.data_ptr(), st),
+                   "swa_bwd_delta")
+        _lib.check(_lib.lib.swa_bwd_dq_rot(C.byref(g), C.byref(r), C.byref(tq), C.byref(tk), C.byref(tv), C.byref(tdo),
+                                           lse.data_ptr(), delta.data_ptr(), C.byref(tdq), status, st), "swa_bwd_dq_rot")
+        _lib.check(_lib.lib.swa_bwd_dkdv_rot(C.byref(g), C.byref(r), C.byref(tq), C.byref(tk), C.byref(tv),
+                                             C.byref(tdo), lse.data_ptr(), delta.data_ptr(), C.byref(tdk),
+                                             C.byref(tdv), status, st), "swa_bwd_dkdv_rot")
+    if os.environ.get("SWA_DEBUG_SYNC"):
+        check_status()
+    return dq, dk, dv
+
+
 def swa_backward_noalloc(q, k, v, o, lse, do, rope, b_size, t_height, t_width, row_size, col_size, sm_scale, dq, dk,
                          dv, impl="auto"):
     """Backward pass into caller-provided ``dq, dk, dv`` through ``swa_bwd_noalloc``: the library

@@ -93,6 +93,30 @@ int swa_bwd_dkdv(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t
                  const swa_tensor_t* v, const swa_tensor_t* d_o, const float* lse, const float* delta,
                  const swa_tensor_t* dk, const swa_tensor_t* dv, int32_t* status, void* stream);
 
+/* The same three steps with the rotation handed on from kernel to kernel, so that every q and k row is rotated
+ * exactly once on chip (swa_fwd / swa_bwd_* with rope != NULL rotate a streamed row once per tile whose window
+ * holds it).  q_rot and k_rot are caller-provided tensors of the shapes of q and k; q and k stay untouched.
+ *   swa_fwd_rot     - a streaming pass writes rope(k) to k_rot, then the attention kernel rotates each query tile
+ *                     in shared memory before its MMAs, stores the rotated rows to q_rot, and streams k_rot.
+ *                     Same o and lse as swa_fwd(rope).  Replaces the same launches as swa_fwd (two
+ *                     rope2d_fwd_kernel launches, src/fused_rope2d.py:138, and the forward kernel,
+ *                     src/tiled_swa.py:611-637); what the reference leaves behind by rotating q and k in place
+ *                     (src/fused_rope2d.py:143-145) is what q_rot / k_rot hold here.
+ *   swa_bwd_dq_rot, swa_bwd_dkdv_rot - take q_rot / k_rot where swa_bwd_dq / swa_bwd_dkdv take q / k; no row
+ *                     is rotated before the MMAs, dq / dk are rotated back in the epilogue registers, i.e. they
+ *                     are the gradients of the UN-rotated q and k (the rope2d_bwd_kernel launches,
+ *                     src/fused_rope2d.py:163, stay fused).  delta comes from swa_bwd_delta as before.
+ * rope must not be NULL (without RoPE the plain entry points do the same work). */
+int swa_fwd_rot(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
+                const swa_tensor_t* v, const swa_tensor_t* o, float* lse, const swa_tensor_t* q_rot,
+                const swa_tensor_t* k_rot, int32_t* status, void* stream);
+int swa_bwd_dq_rot(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q_rot, const swa_tensor_t* k_rot,
+                   const swa_tensor_t* v, const swa_tensor_t* d_o, const float* lse, const float* delta,
+                   const swa_tensor_t* dq, int32_t* status, void* stream);
+int swa_bwd_dkdv_rot(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q_rot, const swa_tensor_t* k_rot,
+                     const swa_tensor_t* v, const swa_tensor_t* d_o, const float* lse, const float* delta,
+                     const swa_tensor_t* dk, const swa_tensor_t* dv, int32_t* status, void* stream);
+
 /* Stand-alone in-place RoPE-2D on x [batch, N, C] (element strides xs[3]).
  * inverse = 0 replaces rope2d_fwd_kernel (src/fused_rope2d.py:24-72), inverse = 1
  * replaces rope2d_bwd_kernel (src/fused_rope2d.py:74-122).  A negative index half
