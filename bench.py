@@ -237,6 +237,10 @@ def main():
                     help="bhnd: contiguous [B,H,N,d] tensors (the reference's layout, the default); packed: q,k,v as "
                          "views of one [B,N,3,H,d] projection output, O and dO in [B,N,H*d], gradients into one "
                          "packed buffer (kernel timing only, no e2e leg)")
+    ap.add_argument("--rope-mode", default="handoff", choices=["handoff", "fused"],
+                    help="handoff (default): every q / k row rotated once on chip, the rotated copies handed from the "
+                         "forward to the backward kernels (swa_fwd_rot, swa_bwd_*_rot); fused: every kernel rotates the "
+                         "rows it streams (swa_fwd, swa_bwd_* with rope)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-variants", action="store_true", help="skip the un-fused composition leg after the timed region")
@@ -307,6 +311,7 @@ def main():
     step_flops = fwd_f + (bwd_f if cfg["bwd"] else 0.0)
     stream = torch.cuda.current_stream(device)
 
+    handoff = rope is not None and args.rope_mode == "handoff"
     names = ["fwd", "delta", "dq", "dkdv"] if cfg["bwd"] else ["fwd"]
     kernel_ms = {n: [] for n in names}
 
@@ -314,11 +319,15 @@ def main():
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)] if record is not None else None
         if ev:
             ev[0].record(stream)
-        o, lse = swa.swa_forward(q, k, v, rope, *win, sm, impl=impl, out=o_out)
+        if handoff:
+            o, lse, q_in, k_in = swa.swa_forward_rot(q, k, v, rope, *win, sm, impl=impl, out=o_out)
+        else:
+            (o, lse), q_in, k_in = swa.swa_forward(q, k, v, rope, *win, sm, impl=impl, out=o_out), q, k
         if ev:
             ev[1].record(stream)
         if cfg["bwd"]:
-            out = swa_backward_timed(swa, _lib, q, k, v, o, lse, do, rope, win, sm, impl, ev, stream, grads_out)
+            out = swa_backward_timed(swa, _lib, q_in, k_in, v, o, lse, do, rope, win, sm, impl, ev, stream, grads_out,
+                                     handoff)
         else:
             out = (o,)
         if record is not None:
@@ -493,10 +502,12 @@ def main():
     return 0
 
 
-def swa_backward_timed(swa, _lib, q, k, v, o, lse, do, rope, win, sm, impl, ev, stream, outs=None):
-    """swa_backward with an event after each of its three launches (same calls, same order)."""
+def swa_backward_timed(swa, _lib, q, k, v, o, lse, do, rope, win, sm, impl, ev, stream, outs=None, handoff=False):
+    """swa_backward / swa_backward_rot with an event after each of its three launches (same calls, same order);
+    with `handoff`, q and k are the rotated copies the forward left behind."""
     if ev is None:
-        return (o,) + tuple(swa.swa_backward(q, k, v, o, lse, do, rope, *win, sm, impl=impl, out=outs))
+        fn = swa.swa_backward_rot if handoff else swa.swa_backward
+        return (o,) + tuple(fn(q, k, v, o, lse, do, rope, *win, sm, impl=impl, out=outs))
     import ctypes as C
     from dl_templates_b200 import tiled_swa as ts
     B, H, N, _ = q.shape
@@ -508,10 +519,11 @@ def swa_backward_timed(swa, _lib, q, k, v, o, lse, do, rope, win, sm, impl, ev, 
     st, status = _lib.stream_ptr(q.device), ts._status(q.device).data_ptr()
     _lib.check(_lib.lib.swa_bwd_delta(C.byref(g), C.byref(to), C.byref(tdo), delta.data_ptr(), st), "delta")
     ev[2].record(stream)
-    _lib.check(_lib.lib.swa_bwd_dq(C.byref(g), ts._ref(r), C.byref(tq), C.byref(tk), C.byref(tv), C.byref(tdo),
+    dq_fn, dkdv_fn = (_lib.lib.swa_bwd_dq_rot, _lib.lib.swa_bwd_dkdv_rot) if handoff else (_lib.lib.swa_bwd_dq, _lib.lib.swa_bwd_dkdv)
+    _lib.check(dq_fn(C.byref(g), ts._ref(r), C.byref(tq), C.byref(tk), C.byref(tv), C.byref(tdo),
                                    lse.data_ptr(), delta.data_ptr(), C.byref(tdq), status, st), "dq")
     ev[3].record(stream)
-    _lib.check(_lib.lib.swa_bwd_dkdv(C.byref(g), ts._ref(r), C.byref(tq), C.byref(tk), C.byref(tv), C.byref(tdo),
+    _lib.check(dkdv_fn(C.byref(g), ts._ref(r), C.byref(tq), C.byref(tk), C.byref(tv), C.byref(tdo),
                                      lse.data_ptr(), delta.data_ptr(), C.byref(tdk), C.byref(tdv), status, st), "dkdv")
     ev[4].record(stream)
     return o, dq, dk, dv

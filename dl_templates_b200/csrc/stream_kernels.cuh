@@ -179,43 +179,53 @@ __global__ void __launch_bounds__(256) rope2d_copy_kernel(const T* __restrict__ 
   *reinterpret_cast<uint4*>(y + bi * ys0 + tok * ys1 + u * 8) = own;
 }
 
-// The same one-pass clone + rotate for a strided [B, H, N, C] tensor (both tensors described by four element
-// strides): bh = b * H + h is decomposed per thread, so packed projection outputs need no flattening copy.
+// One-pass clone + rotate for a strided [B, H, N, C] 16-bit tensor (both tensors described by four element
+// strides, so packed projection outputs need no flattening copy).  One thread per "slot" of a token row: a slot of
+// the rotated dims is a 16-byte unit together with its partner unit R elements further (both halves of eight
+// pairs: two 16-byte loads, one set of cos/sin values, two 16-byte stores, nothing read twice); a slot of the dims
+// beyond 4R is two consecutive units that are copied.  grid = (slots of one (batch, head) slice / 256, B * H).
 template <typename T>
-__global__ void __launch_bounds__(256) rope2d_copy4_kernel(View4 x, View4 y, int64_t rows, int H, int64_t N, int C,
-                                                           RopeDev rp, float sign) {
-  const int upr = C >> 3;
-  const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int64_t row = gid / upr;
-  if (row >= rows) return;
-  const int u = (int)(gid - row * upr);
-  const int64_t bh = row / N, tok = row - bh * N;
-  const int64_t b = bh / H, h = bh - b * H;
-  const T* src = (const T*)x.ptr + b * x.s0 + h * x.s1 + tok * x.s2 + u * 8;
-  uint4 own = *reinterpret_cast<const uint4*>(src);
-  const int e0 = u * 8;
-  if (e0 < 4 * rp.R) {
-    const int seg = e0 / rp.R, half = seg >> 1, second = seg & 1, i0 = e0 - seg * rp.R;
+__global__ void __launch_bounds__(256) rope2d_copy4_kernel(View4 x, View4 y, int H, int N, int C, RopeDev rp, float sign) {
+  const uint32_t rot_slots = (uint32_t)rp.R >> 2;                       // 4R / 8 units, two per slot
+  const uint32_t spr = rot_slots + ((((uint32_t)C >> 3) - 2 * rot_slots + 1) >> 1);   // slots per row
+  const uint32_t gid = blockIdx.x * blockDim.x + threadIdx.x;
+  const uint32_t tok = gid / spr;
+  if (tok >= (uint32_t)N) return;
+  const uint32_t sl = gid - tok * spr;
+  const uint32_t bh = blockIdx.y;
+  const int64_t b = bh / (uint32_t)H, h = bh - (uint32_t)b * (uint32_t)H;
+  const T* src = (const T*)x.ptr + b * x.s0 + h * x.s1 + (int64_t)tok * x.s2;
+  T* dst = (T*)y.ptr + b * y.s0 + h * y.s1 + (int64_t)tok * y.s2;
+  if (sl < rot_slots) {
+    const uint32_t per_half = (uint32_t)rp.R >> 3;                      // slots of the row-angle half
+    const uint32_t half = sl / per_half, i0 = (sl - half * per_half) * 8;
+    const uint32_t e0 = half * 2 * rp.R + i0, e1 = e0 + rp.R;
+    uint4 va = *reinterpret_cast<const uint4*>(src + e0), vb = *reinterpret_cast<const uint4*>(src + e1);
     int irow, icol;
-    decode_idx(rp.idx[tok], rp.max_h, rp.max_w, irow, icol);
+    decode_idx(__ldg(rp.idx + tok), rp.max_h, rp.max_w, irow, icol);
     const int pos = half ? icol : irow;
     if (pos >= 0) {
-      const uint4 oth = *reinterpret_cast<const uint4*>(second ? src - rp.R : src + rp.R);
-      const float* tab = (half ? rp.col_cs : rp.row_cs) + ((int64_t)pos * rp.R + i0) * 2;
-      float cs[16];
+      const float4* tab = reinterpret_cast<const float4*>((half ? rp.col_cs : rp.row_cs) + ((int64_t)pos * rp.R + i0) * 2);
+      T* ea = reinterpret_cast<T*>(&va);
+      T* eb = reinterpret_cast<T*>(&vb);
 #pragma unroll
-      for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(cs + j) = *reinterpret_cast<const float4*>(tab + j);
-      T* eo = reinterpret_cast<T*>(&own);
-      const T* ep = reinterpret_cast<const T*>(&oth);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float c = cs[2 * j], sn = cs[2 * j + 1] * sign;
-        const float a = second ? to_f(ep[j]) : to_f(eo[j]), bb = second ? to_f(eo[j]) : to_f(ep[j]);
-        eo[j] = from_f<T>(second ? a * sn + bb * c : a * c - bb * sn);
+      for (int j = 0; j < 8; j += 2) {
+        const float4 cs = __ldg(tab + (j >> 1));                        // (cos, sin) of pairs j and j + 1
+        const float a0 = to_f(ea[j]), b0 = to_f(eb[j]), a1 = to_f(ea[j + 1]), b1 = to_f(eb[j + 1]);
+        const float s0 = cs.y * sign, s1 = cs.w * sign;
+        ea[j] = from_f<T>(a0 * cs.x - b0 * s0);
+        eb[j] = from_f<T>(a0 * s0 + b0 * cs.x);
+        ea[j + 1] = from_f<T>(a1 * cs.z - b1 * s1);
+        eb[j + 1] = from_f<T>(a1 * s1 + b1 * cs.z);
       }
     }
+    *reinterpret_cast<uint4*>(dst + e0) = va;
+    *reinterpret_cast<uint4*>(dst + e1) = vb;
+  } else {
+    const uint32_t e0 = 4 * rp.R + (sl - rot_slots) * 16;
+    *reinterpret_cast<uint4*>(dst + e0) = *reinterpret_cast<const uint4*>(src + e0);
+    if (e0 + 8 < (uint32_t)C) *reinterpret_cast<uint4*>(dst + e0 + 8) = *reinterpret_cast<const uint4*>(src + e0 + 8);
   }
-  *reinterpret_cast<uint4*>((T*)y.ptr + b * y.s0 + h * y.s1 + tok * y.s2 + u * 8) = own;
 }
 
 // Element path of the same operation for any dtype and any strides; x == y (in place) is allowed.  One thread

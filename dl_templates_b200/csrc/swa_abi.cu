@@ -268,12 +268,12 @@ int launch_rope4(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t
   const bool vec = g->dtype != SWA_F32 && x->ptr != y->ptr && rp.R % 8 == 0 && C % 8 == 0 && rows16(x) && rows16(y) &&
                    ((uintptr_t)rp.row_cs % 16) == 0 && ((uintptr_t)rp.col_cs % 16) == 0;
   if (vec) {
-    const int64_t threads = rows * (C / 8);
-    const unsigned blocks = (unsigned)((threads + 255) / 256);
+    const int64_t slots = rp.R / 4 + ((C / 8 - rp.R / 2) + 1) / 2;   // per token row (see the kernel)
+    dim3 grid((unsigned)((N * slots + 255) / 256), (unsigned)(g->B * g->H));
     if (g->dtype == SWA_F16)
-      swa::rope2d_copy4_kernel<__half><<<blocks, 256, 0, st>>>(swa::make_view(x), swa::make_view(y), rows, g->H, N, C, rp, sign);
+      swa::rope2d_copy4_kernel<__half><<<grid, 256, 0, st>>>(swa::make_view(x), swa::make_view(y), g->H, (int)N, C, rp, sign);
     else
-      swa::rope2d_copy4_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(swa::make_view(x), swa::make_view(y), rows, g->H, N, C, rp, sign);
+      swa::rope2d_copy4_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(swa::make_view(x), swa::make_view(y), g->H, (int)N, C, rp, sign);
   } else {
     const int64_t threads = rows * 2 * rp.R;
     const unsigned blocks = (unsigned)((threads + 255) / 256);
@@ -308,14 +308,14 @@ int swa_fwd_rot(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t*
   const int impl = resolve_impl(g, rope, ts, 6, 0, true);
   if (impl < 0) return impl;
   cudaStream_t st = (cudaStream_t)stream;
-  // every key row is rotated exactly once, by a streaming pass; the attention kernel streams the rotated rows
+  // every q and k row is rotated exactly once, by a streaming pass; the attention kernels read the rotated rows
+  if (int e = launch_rope4(g, rope, q, q_rot, false, st)) return e;
   if (int e = launch_rope4(g, rope, k, k_rot, false, st)) return e;
   if (impl == SWA_IMPL_TC) {
-    int e = swa::tc::launch_fwd2(g, rope, q, k_rot, v, o, lse, q_rot, status, st);
+    int e = swa::tc::launch_fwd2(g, q_rot, k_rot, v, o, lse, status, st);
     if (e) return fail(E_LAUNCH, "tcgen05 forward: %s", swa::tc::last_error());
     return launch_ok("tcgen05 forward (rotation handed on)");
   }
-  if (int e = launch_rope4(g, rope, q, q_rot, false, st)) return e;
   const swa::Geom gg = swa::make_geom(g);
   const swa::RopeDev none = swa::make_rope(nullptr);
   const int N = g->t_height * g->t_width * g->b_size;

@@ -112,7 +112,8 @@ bool make_plan_shape(const swa_geom_t* g, int which, int TH, int TW, uint32_t ta
   const int acc_cols = which == 0 ? 0 : (which == 1 ? 64 * qch : 64 * (qch + vch));
   const int min_stages = 3;
   // alignment pad of the swizzled tiles + the kernel's barrier / exchange / penalty-table block behind the ring
-  const uint32_t kSmemSlack = 1024u + (((which == 0 ? (uint32_t)sizeof(FwdShared) + 64u : (uint32_t)sizeof(BwdShared)) + 15u) & ~15u);
+  // (the kernels without streamed rotation have a few more barriers, and two more lse / delta slots in backward)
+  const uint32_t kSmemSlack = 1024u + (((which == 0 ? (uint32_t)sizeof(FwdShared) + 128u : (uint32_t)sizeof(BwdShared) + 64u + 2048u) + 15u) & ~15u);
   {
     // backward: two (S, dP) pairs of 2N columns next to the accumulators (N = 64 always fits: 256 + 256 columns)
     const int nsb = 2;
@@ -222,6 +223,23 @@ bool make_plan(const swa_geom_t* g, const swa_rope_t* rope, int which, Plan* out
   return ok_n;
 }
 
+// Plan of the kernels that rotate no streamed row (rotation handed on between the kernels, or no RoPE): the
+// tile shape of the problem without RoPE; the tables (needed once per item only) are staged when that costs
+// neither block size nor a stage of the ring.
+bool make_plan_prerot(const swa_geom_t* g, const swa_rope_t* rope, int which, Plan* out) {
+  const uint32_t tab = rope_table_bytes(rope);
+  Plan with, without;
+  long cw = 0, cn = 0;
+  const bool ok_n = make_plan_tab(g, nullptr, which, 0, &without, &cn);
+  if (ok_n && tab && make_plan_tab(g, nullptr, which, tab, &with, &cw) && cw <= cn && with.stages >= without.stages &&
+      with.TH == without.TH) {
+    *out = with;
+    return true;
+  }
+  if (ok_n) *out = without;
+  return ok_n;
+}
+
 // Indicator value a and penalty b (powers of two, exact in fp16 and bf16) of the window mask that
 // rides on the score MMA: a*b*scale*log2(e) >= 4000, so exp2 of a masked score is exactly 0.
 bool mask_constants(float sm_scale, float* a, float* b) {
@@ -278,7 +296,7 @@ const char* unsupported_reason(const swa_geom_t* g, const swa_rope_t* rope, cons
   if (g->row_size > 64) return "row window too tall for the penalty tables";
   if ((int64_t)g->t_height * g->t_width * g->b_size > (1 << 30)) return "grid too large";
   Plan pl;
-  if (!make_plan(g, prerotated ? nullptr : rope, which, &pl))
+  if (!(prerotated ? make_plan_prerot(g, which == 0 ? nullptr : rope, which, &pl) : make_plan(g, rope, which, &pl)))
     return "no tile plan fits (window too wide for one streamed block)";
   for (int i = 0; i < n_tensors; ++i)
     if (!tensor_ok(tensors[i])) return "tensors need unit last stride and 16-byte aligned rows";
@@ -292,14 +310,14 @@ bool describe_plan(const swa_geom_t* g, const swa_rope_t* rope, int which, int32
   uint32_t used = 1023, tmem = 0;   // worst-case pad to the 1024-byte alignment of the swizzled tiles
   if (which == 0) {
     used += 2 * qch * 16384u + 128u * kXRowBytes + pl.stages * N * ((qch + vch) * 128u + kXRowBytes);
-    used += ((uint32_t)sizeof(FwdShared) + 64u + 15u) & ~15u;   // the larger of the two forward kernels' blocks
+    used += ((uint32_t)sizeof(FwdShared) + 128u + 15u) & ~15u;   // the larger of the two forward kernels' blocks
     const uint32_t o_cols = vch * 64u;
     const uint32_t stride = (N <= 128u && pl.nsb * 128u + 2 * o_cols <= 512u) ? 128u : N;
     tmem = pl.nsb * stride + 2 * o_cols;
     if (stride < N) tmem = 1u << 30;   // a score buffer would not hold a block
   } else {
     used += pl.nxb * (qch + vch) * 16384u + 128u * kXRowBytes + pl.stages * (N * ((qch + vch) * 128u + kXRowBytes) + 1024u);
-    used += ((uint32_t)sizeof(BwdShared) + 15u) & ~15u;
+    used += ((uint32_t)sizeof(BwdShared) + 64u + 2048u + 15u) & ~15u;   // the larger of the two backward kernels' blocks
     tmem = 2 * 2 * N + 64u * qch + (which == 2 ? 64u * vch : 0u);
   }
   used += pl.tab_bytes;
@@ -311,7 +329,7 @@ bool describe_plan(const swa_geom_t* g, const swa_rope_t* rope, int which, int32
 
 int launch_fwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
                const swa_tensor_t* v, const swa_tensor_t* o, float* lse, int32_t* status, cudaStream_t st) {
-  if (!(rope && rope->idx)) return launch_fwd2(g, nullptr, q, k, v, o, lse, nullptr, status, st);
+  if (!(rope && rope->idx)) return launch_fwd2(g, q, k, v, o, lse, status, st);
   Plan pl;
   if (!make_plan(g, rope, 0, &pl)) {
     snprintf(g_tc_err, sizeof(g_tc_err), "no tile plan");
@@ -352,11 +370,10 @@ int launch_fwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* 
   return 0;
 }
 
-int launch_fwd2(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
-                const swa_tensor_t* v, const swa_tensor_t* o, float* lse, const swa_tensor_t* q_rot, int32_t* status,
-                cudaStream_t st) {
+int launch_fwd2(const swa_geom_t* g, const swa_tensor_t* q, const swa_tensor_t* k, const swa_tensor_t* v,
+                const swa_tensor_t* o, float* lse, int32_t* status, cudaStream_t st) {
   Plan pl;
-  if (!make_plan(g, nullptr, 0, &pl)) {      // no streamed row is rotated: the plan of the problem without RoPE
+  if (!make_plan(g, nullptr, 0, &pl)) {      // nothing is rotated: the plan of the problem without RoPE
     snprintf(g_tc_err, sizeof(g_tc_err), "no tile plan");
     return -1;
   }
@@ -364,20 +381,10 @@ int launch_fwd2(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t*
   if (!make_map(&tq, q, g, g->d_qk, pl.TW, pl.TH) || !make_map(&tk, k, g, g->d_qk, pl.KW, pl.KR) ||
       !make_map(&tv, v, g, g->d_v, pl.KW, pl.KR))
     return -1;
-  const KParams p = make_params(g, rope, pl, status);
+  const KParams p = make_params(g, nullptr, pl, status);
   const int sms = sm_count();
   dim3 grid(p.n_items < sms ? p.n_items : sms), block(kFwdThreads);   // persistent: one CTA per SM walks the items
-  using Fwd2Kernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, KParams, View4, float*, View4);
-  // [dtype][n_rdim / 8 of the query rotation]
-  static const Fwd2Kernel table[2][5] = {
-      {fwd2_kernel<false, 0>, fwd2_kernel<false, 1>, fwd2_kernel<false, 2>, nullptr, fwd2_kernel<false, 4>},
-      {fwd2_kernel<true, 0>, fwd2_kernel<true, 1>, fwd2_kernel<true, 2>, nullptr, fwd2_kernel<true, 4>}};
-  const int ni = (rope && rope->idx) ? rope->n_rdim / 8 : 0;
-  Fwd2Kernel kern = table[g->dtype == SWA_BF16 ? 1 : 0][ni];
-  if (kern == nullptr) {
-    snprintf(g_tc_err, sizeof(g_tc_err), "n_rdim %d has no tensor-core kernel", rope ? rope->n_rdim : 0);
-    return -1;
-  }
+  auto kern = g->dtype == SWA_BF16 ? fwd2_kernel<true> : fwd2_kernel<false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem_bytes);
   if (e != cudaSuccess) {
     snprintf(g_tc_err, sizeof(g_tc_err), "cudaFuncSetAttribute(%u bytes): %s", pl.smem_bytes, cudaGetErrorString(e));
@@ -386,7 +393,7 @@ int launch_fwd2(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t*
   if (getenv("SWA_TC_VERBOSE"))
     fprintf(stderr, "[swa2d] fwd2 plan: tile %dx%d, block %dx%d (N=%d), stages %d, score buffers %d, smem %u, %d items on %u CTAs\n",
             pl.TH, pl.TW, pl.KR, pl.KW, pl.N, pl.stages, pl.nsb, pl.smem_bytes, p.n_items, grid.x);
-  kern<<<grid, block, pl.smem_bytes, st>>>(tq, tk, tv, p, make_view(o), lse, q_rot ? make_view(q_rot) : View4{nullptr, 0, 0, 0, 0});
+  kern<<<grid, block, pl.smem_bytes, st>>>(tq, tk, tv, p, make_view(o), lse);
   return 0;
 }
 
@@ -399,7 +406,7 @@ int launch_bwd(const swa_geom_t* g, const swa_rope_t* rope, bool prerotated, con
                const swa_tensor_t* yqk, const swa_tensor_t* yv, const float* lse, const float* delta,
                const swa_tensor_t* out_qk, const swa_tensor_t* out_v, int32_t* status, cudaStream_t st) {
   Plan pl;
-  if (!make_plan(g, prerotated ? nullptr : rope, DKDV ? 2 : 1, &pl)) {
+  if (!(prerotated ? make_plan_prerot(g, rope, DKDV ? 2 : 1, &pl) : make_plan(g, rope, DKDV ? 2 : 1, &pl))) {
     snprintf(g_tc_err, sizeof(g_tc_err), "no tile plan");
     return -1;
   }
@@ -419,12 +426,18 @@ int launch_bwd(const swa_geom_t* g, const swa_rope_t* rope, bool prerotated, con
       {{nullptr, bwd_kernel<true, DKDV, 1, false>, bwd_kernel<true, DKDV, 2, false>, nullptr, bwd_kernel<true, DKDV, 4, false>},
        {nullptr, bwd_kernel<true, DKDV, 1, true>, bwd_kernel<true, DKDV, 2, true>, nullptr, bwd_kernel<true, DKDV, 4, true>}}};
   // [dtype][n_rdim / 8]: no RoPE, or inputs already rotated and only the epilogue rotation
-  static const BwdKernel prerot_table[2][5] = {
-      {bwd2_kernel<false, DKDV, 0>, bwd2_kernel<false, DKDV, 1>, bwd2_kernel<false, DKDV, 2>, nullptr, bwd2_kernel<false, DKDV, 4>},
-      {bwd2_kernel<true, DKDV, 0>, bwd2_kernel<true, DKDV, 1>, bwd2_kernel<true, DKDV, 2>, nullptr, bwd2_kernel<true, DKDV, 4>}};
+  static const BwdKernel prerot_table[2][2][5] = {
+      {{bwd2_kernel<false, DKDV, 0, false>, bwd2_kernel<false, DKDV, 1, false>, bwd2_kernel<false, DKDV, 2, false>, nullptr,
+        bwd2_kernel<false, DKDV, 4, false>},
+       {bwd2_kernel<false, DKDV, 0, false>, bwd2_kernel<false, DKDV, 1, true>, bwd2_kernel<false, DKDV, 2, true>, nullptr,
+        bwd2_kernel<false, DKDV, 4, true>}},
+      {{bwd2_kernel<true, DKDV, 0, false>, bwd2_kernel<true, DKDV, 1, false>, bwd2_kernel<true, DKDV, 2, false>, nullptr,
+        bwd2_kernel<true, DKDV, 4, false>},
+       {bwd2_kernel<true, DKDV, 0, false>, bwd2_kernel<true, DKDV, 1, true>, bwd2_kernel<true, DKDV, 2, true>, nullptr,
+        bwd2_kernel<true, DKDV, 4, true>}}};
   const int ni = (rope && rope->idx) ? rope->n_rdim / 8 : 0;
   const int bf = g->dtype == SWA_BF16 ? 1 : 0;
-  BwdKernel kern = (prerotated || ni == 0) ? prerot_table[bf][ni] : fused_table[bf][pl.tab_bytes ? 1 : 0][ni];
+  BwdKernel kern = (prerotated || ni == 0) ? prerot_table[bf][pl.tab_bytes ? 1 : 0][ni] : fused_table[bf][pl.tab_bytes ? 1 : 0][ni];
   if (kern == nullptr) {
     snprintf(g_tc_err, sizeof(g_tc_err), "n_rdim %d has no tensor-core kernel", rope ? rope->n_rdim : 0);
     return -1;

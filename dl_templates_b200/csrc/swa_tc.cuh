@@ -22,11 +22,10 @@ bool describe_plan(const swa_geom_t* g, const swa_rope_t* rope, int which, int32
 
 int launch_fwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
                const swa_tensor_t* v, const swa_tensor_t* o, float* lse, int32_t* status, cudaStream_t st);
-// Forward with the keys already rotated (or no RoPE at all: rope == nullptr): the query tile is rotated on chip
-// and, when q_rot != nullptr, the rotated rows are stored there.
-int launch_fwd2(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
-                const swa_tensor_t* v, const swa_tensor_t* o, float* lse, const swa_tensor_t* q_rot, int32_t* status,
-                cudaStream_t st);
+// Forward without any rotation in the kernel: q and k are un-rotated inputs of a call without RoPE, or the
+// rotated copies a streaming pass made.
+int launch_fwd2(const swa_geom_t* g, const swa_tensor_t* q, const swa_tensor_t* k, const swa_tensor_t* v,
+                const swa_tensor_t* o, float* lse, int32_t* status, cudaStream_t st);
 int launch_dq(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* q, const swa_tensor_t* k,
               const swa_tensor_t* v, const swa_tensor_t* d_o, const float* lse, const float* delta,
               const swa_tensor_t* dq, int32_t* status, cudaStream_t st, bool prerotated = false);

@@ -30,24 +30,32 @@ namespace tc {
 
 struct Bwd2Shared {
   uint64_t x_full[2], x_empty[2];
-  uint64_t y_full[kMaxStages], y_ready[kMaxStages], y_empty[kMaxStages];
+  uint64_t y_full[kMaxStages], y_ready[kMaxStages], y_empty[kMaxStages], yx_free[kMaxStages];
   uint64_t sd_full[2], ds_full[2], pair_free[2], acc_full, acc_free;
   PenaltyTables pen;
   uint32_t tmem_base;
   int abort_flag;
   int abort_site;
 };
-static_assert(sizeof(Bwd2Shared) <= sizeof(BwdShared), "the planner sizes shared memory with BwdShared");
+static_assert(sizeof(Bwd2Shared) <= sizeof(BwdShared) + 64, "the planner sizes shared memory with BwdShared + 64");
 
 // Inverse rotation of one segment (R pairs (i, i + R)) of a row held in registers; `pos` is the token's
 // row of the cos/sin table (negative: not rotated).
-template <int RE>
-__device__ __forceinline__ void inv_rotate_segment(float* v, int pos, const float* __restrict__ table) {
+// TABS: the table row is read from the copy staged in shared memory (`tab_addr` = shared-space address of the table).
+template <int RE, bool TABS>
+__device__ __forceinline__ void inv_rotate_segment(float* v, int pos, const float* __restrict__ table, uint32_t tab_addr) {
   if (pos < 0) return;
   const float4* t4 = reinterpret_cast<const float4*>(table + (int64_t)pos * RE * 2);
+  const uint32_t ta = tab_addr + (uint32_t)pos * rope_tab_stride(RE);
 #pragma unroll
   for (int i = 0; i < RE; i += 2) {
-    const float4 c = __ldg(t4 + (i >> 1));               // (cos, sin) of pairs i and i + 1
+    float4 c;                                            // (cos, sin) of pairs i and i + 1
+    if constexpr (TABS) {
+      const uint4 u = ptx::lds128(ta + (i >> 1) * 16);
+      c = make_float4(__uint_as_float(u.x), __uint_as_float(u.y), __uint_as_float(u.z), __uint_as_float(u.w));
+    } else {
+      c = __ldg(t4 + (i >> 1));
+    }
     const float a0 = v[i], b0 = v[RE + i], a1 = v[i + 1], b1 = v[RE + i + 1];
     v[i] = a0 * c.x + b0 * c.y;
     v[RE + i] = b0 * c.x - a0 * c.y;
@@ -73,8 +81,9 @@ __device__ __forceinline__ void store64(void* dst, const float* v) {
                       pack2<BF16>(v[8 * u + 4], v[8 * u + 5]), pack2<BF16>(v[8 * u + 6], v[8 * u + 7]));
 }
 
-// NE: width of the inverse rotation of dQ / dK in the epilogue (n_rdim / 8; 0 = none).
-template <bool BF16, bool DKDV, int NE>
+// NE: width of the inverse rotation of dQ / dK in the epilogue (n_rdim / 8; 0 = none); TABS: the cos/sin
+// tables are staged in shared memory (the planner does that when it costs no stage of the block ring).
+template <bool BF16, bool DKDV, int NE, bool TABS>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ CUtensorMap tm_xv,
             const __grid_constant__ CUtensorMap tm_yqk, const __grid_constant__ CUtensorMap tm_yv, KParams p,
@@ -95,8 +104,12 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
   uint8_t* yqk_smem = xx_smem + 128 * kXRowBytes;
   uint8_t* yv_smem = yqk_smem + pl.stages * yqk_stage;
   uint8_t* yx_smem = yv_smem + pl.stages * yv_stage;
-  float* vec_smem = reinterpret_cast<float*>(yx_smem + pl.stages * yx_stage);   // [stage][-lse | delta][128]
-  Bwd2Shared* sh = reinterpret_cast<Bwd2Shared*>(reinterpret_cast<uint8_t*>(vec_smem) + pl.stages * 1024);
+  // -lse / delta of the streamed queries (dK/dV): a ring of stages + 2 slots [slot][-lse | delta][128], two deeper
+  // than the block ring because the warps that fill it run ahead of the loads
+  float* vec_smem = reinterpret_cast<float*>(yx_smem + pl.stages * yx_stage);
+  const int vslots = pl.stages + 2;
+  Bwd2Shared* sh = reinterpret_cast<Bwd2Shared*>(reinterpret_cast<uint8_t*>(vec_smem) + vslots * 1024);
+  uint8_t* tab_smem = reinterpret_cast<uint8_t*>(sh) + ((sizeof(BwdShared) + 64 + 15) & ~size_t(15));   // cos/sin tables (TABS)
   volatile int* abort_flag = &sh->abort_flag;
   // tensor memory: buffer pair b = (S at 2N b, dP at 2N b + N), accumulators behind the pairs
   const uint32_t acc_qk = nsb * 2 * N, acc_v = acc_qk + p.qch * 64;
@@ -117,6 +130,7 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
       mbar_init(&sh->y_full[s], 1);
       mbar_init(&sh->y_ready[s], 128);
       mbar_init(&sh->y_empty[s], 1);
+      mbar_init(&sh->yx_free[s], 1);
     }
     sh->abort_flag = 0;
     sh->abort_site = 0;
@@ -126,6 +140,7 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
     tmem_alloc(&sh->tmem_base, kBwdTmemCols);
     tmem_relinquish();
   }
+  if constexpr (TABS) stage_rope_tables(tab_smem, p.rope, threadIdx.x, kBwdThreads);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -164,6 +179,7 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
     uint64_t* const ds_bar = &sh->ds_full[g];
     int buf_par = 0;
     int stage = g % pl.stages, stage_par = (g / pl.stages) & 1;
+    int vslot = g;                                 // slot of the lse / delta ring of this group's next block
 #pragma unroll 1
     for (int it = 0, item = blockIdx.x; item < n_items; ++it, item += gridDim.x) {
       const int bh = item / tiles_per_head;
@@ -183,7 +199,9 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
         trace_ev(p, 2 + g, tn, m == 0 && it >= p.trace_it, 0 * 16 + (j & 15));
         wait_spin(&sh->sd_full[g], buf_par, 7);
         trace_ev(p, 2 + g, tn, m == 0 && it >= p.trace_it, 1 * 16 + (j & 15));
-        const float* vec = vec_smem + stage * 256;
+        const float* vec = vec_smem + vslot * 256;
+        vslot += 2;
+        if (vslot >= vslots) vslot -= vslots;
         if (DKDV) wait_spin(&sh->y_ready[stage], stage_par, 8);   // -lse / delta of the block's queries are staged
         buf_par ^= 1;
         stage += 2;
@@ -328,7 +346,8 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
       for (int s_item = blockIdx.x; s_item < n_items;) {
         trace_ev(p, 1, tn, tl && s_it >= p.trace_it, 2 * 16 + (s_j & 15));
         if (s_j == 0) wait_spin(&sh->x_full[s_xb], s_xb_par, 5);
-        wait_spin(&sh->y_ready[s_stage], s_stage_par, 6);
+        wait_spin(&sh->y_full[s_stage], s_stage_par, 12);    // the block has landed ...
+        wait_spin(&sh->y_ready[s_stage], s_stage_par, 6);    // ... and its mask rows (and lse / delta) are written
         // the pair is free once the accumulating MMAs of the block that used it last have completed
         if (G >= 2) wait_spin(&sh->pair_free[s_buf], ((G >> 1) - 1) & 1, 11);
         if (ok) {
@@ -355,6 +374,7 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
               for (int k = 0; k < 4; ++k, xd += 2, yd += 2, acc = 1u) umma_ss(d_tm, xd, yd, idesc_s, acc);
             }
             umma_commit(&sh->sd_full[s_buf]);
+            umma_commit(&sh->yx_free[s_stage]);                        // the mask rows of this stage may be overwritten
             if (s_j == s_nblk - 1) umma_commit(&sh->x_empty[s_xb]);   // last read of this resident buffer
           }
           __syncwarp();
@@ -435,6 +455,7 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
     using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
     const bool rope_on = NE > 0 && p.rope.idx != nullptr;
     const float scale = p.sm_scale;
+    const uint32_t tab_row = smem_u32(tab_smem), tab_col = tab_row + (uint32_t)p.rope.max_h * rope_tab_stride(R);
     int tn = 0;
     write_indicator_row<BF16>(xx_smem, t, 0, 1, p);               // the same for every item
     const bool row_on = t < N;
@@ -442,6 +463,7 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
 
     // Epilogue of one item: this thread's row of the accumulators -> registers (64 columns at a time), tensor
     // memory released as soon as the last column is read, then scaling, inverse rotation and the stores.
+    int32_t pend_packed = -1;                        // packed RoPE index of this thread's row of the pending item
     auto epilogue = [&](int item, int it) {
       const int bh = item / tiles_per_head, bi = bh / p.H, hi = bh - bi * p.H;
       const TilePos tp = tile_pos(p, item - bh * tiles_per_head);
@@ -449,7 +471,7 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
       const bool t_in = tr < p.t_h && tx < p.Wtok;
       const int64_t tok = (int64_t)tr * p.Wtok + tx;
       int irow = -1, icol = -1;
-      if (rope_on && t_in) decode_idx(__ldg(p.rope.idx + tok), p.rope.max_h, p.rope.max_w, irow, icol);
+      if (rope_on && t_in) decode_idx(pend_packed, p.rope.max_h, p.rope.max_w, irow, icol);
       T* qk_row = (T*)out_qk.ptr + bi * out_qk.s0 + hi * out_qk.s1 + tok * out_qk.s2;
       trace_ev(p, 5, tn, t == 0 && it >= p.trace_it, 0 * 16 + (it & 15));
       wait_spin(&sh->acc_full, it & 1, 9);
@@ -483,10 +505,10 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
             // rotated dims [0, 4R): row-angle pairs (i, i + R) in [0, 2R), column-angle pairs in [2R, 4R)
             if (rope_on) {
               if constexpr (R == 32) {
-                if (r < 2) inv_rotate_segment<R>(v, r ? icol : irow, r ? p.rope.col_cs : p.rope.row_cs);
+                if (r < 2) inv_rotate_segment<R, TABS>(v, r ? icol : irow, r ? p.rope.col_cs : p.rope.row_cs, r ? tab_col : tab_row);
               } else if (r == 0) {
-                inv_rotate_segment<R>(v, irow, p.rope.row_cs);
-                inv_rotate_segment<R>(v + 2 * R, icol, p.rope.col_cs);
+                inv_rotate_segment<R, TABS>(v, irow, p.rope.row_cs, tab_row);
+                inv_rotate_segment<R, TABS>(v + 2 * R, icol, p.rope.col_cs, tab_col);
               }
             }
           }
@@ -496,7 +518,10 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
       trace_ev(p, 5, tn, t == 0 && it >= p.trace_it, 3 * 16 + (it & 15));
     };
 
-    int stage = 0, stage_par = 0;
+    int stage = 0, stage_par = 1;                    // parity of the "free" phase a rewrite of this stage's rows waits for
+    int vslot = 0;
+    bool ring_full = false;
+    uint64_t pen_sig = ~0ull;                        // geometry the penalty tables in shared memory were built for
     uint32_t G = 0;                                  // stream position of the next block to prepare
     bool pend = false;                               // an item whose epilogue has not run yet
     int pend_item = 0, pend_it = 0;
@@ -527,15 +552,24 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
       };
       if (have) {
         load_vec(0);
-        named_bar_sync(5, 128);           // nobody still reads the previous item's tables
-        build_penalty_tables<BF16>(&sh->pen, t, p, tp, 128);
-        named_bar_sync(5, 128);
+        // the tables depend only on how the halo is clipped by the grid: interior tiles share them
+        const uint64_t sig = penalty_signature(p, tp);
+        if (sig != pen_sig) {
+          pen_sig = sig;
+          named_bar_sync(5, 128);           // nobody still reads the previous tables
+          build_penalty_tables<BF16>(&sh->pen, t, p, tp, 128);
+          named_bar_sync(5, 128);
+        }
       }
 #pragma unroll 1
       for (int j = 0;; ++j, ++G) {
-        // The block at stream position (last block of an item + stages) is the first one whose load had to wait
-        // for that item's last accumulating MMA: the item's epilogue runs right before it (or at the end of the
-        // next item when that one is shorter than the ring, or after the last item).
+        // These warps run ahead of the score MMAs by up to `stages` blocks (a stage's mask rows are free as soon as
+        // the score MMAs that read them have completed, and the lse / delta ring is two slots deeper than the block
+        // ring: the score MMAs of block G - stages were issued after the accumulating MMAs of block G - stages - 2,
+        // i.e. after the compute warps had finished reading that block's slot).  The block at stream position
+        // (last block of an item + 2 + stages) is the first one they would have to wait for until that item's
+        // last accumulating MMA has completed: the item's epilogue runs right before it (or at the end of a
+        // later item that ends earlier, or after the last item), hidden behind that lead.
         const bool at_end = j >= tp.nblk;
         if (pend && (at_end || G >= pend_G)) {
           epilogue(pend_item, pend_it);
@@ -545,27 +579,32 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
         const float a0 = nl, b0 = dl;
         load_vec(j + 1);                             // one block ahead: the latency hides behind this block's wait
         trace_ev(p, 4, tn, t == 0 && it >= p.trace_it, 0 * 16 + (j & 15));
-        wait_park(&sh->y_full[stage], (uint32_t)stage_par, 10);
+        if (ring_full) wait_park(&sh->yx_free[stage], (uint32_t)stage_par, 10);
         trace_ev(p, 4, tn, t == 0 && it >= p.trace_it, 1 * 16 + (j & 15));
         if (ok) {
           if (row_on) {
             write_penalty_row(yx_smem + stage * yx_stage, t, 0, 1, &sh->pen, j * pl.KR + jr, jc, pl.TH >> 3, pl.TW >> 3);
             if constexpr (DKDV) {
-              vec_smem[stage * 256 + t] = a0;
-              vec_smem[stage * 256 + 128 + t] = b0;
+              vec_smem[vslot * 256 + t] = a0;
+              vec_smem[vslot * 256 + 128 + t] = b0;
             }
           }
           fence_proxy_async_smem();
           mbar_arrive(&sh->y_ready[stage]);
         }
         trace_ev(p, 4, tn, t == 0 && it >= p.trace_it, 2 * 16 + (j & 15));
-        if (++stage == pl.stages) { stage = 0; stage_par ^= 1; }
+        if (++stage == pl.stages) { stage = 0; stage_par ^= 1; ring_full = true; }
+        if (++vslot == vslots) vslot = 0;
       }
       if (!have) break;
       pend = true;
       pend_item = item;
       pend_it = it;
-      pend_G = G - 1 + (uint32_t)pl.stages;
+      pend_G = G - 1 + (uint32_t)(pl.stages + 2);
+      if (rope_on) {                                 // fetched long before the epilogue needs it
+        const int tr = tp.r0 + t / pl.TW, tx = tp.x0 + t % pl.TW;
+        pend_packed = (tr < p.t_h && tx < p.Wtok) ? __ldg(p.rope.idx + (int64_t)tr * p.Wtok + tx) : -1;
+      }
     }
   }
 

@@ -179,6 +179,15 @@ __device__ __forceinline__ void build_penalty_tables(PenaltyTables* tab, int t, 
   }
 }
 
+// Everything build_penalty_tables reads, relative to the resident tile: two tiles with the same signature have
+// the same tables (all tiles whose halo the grid does not clip, for one).
+__device__ __forceinline__ uint64_t penalty_signature(const KParams& p, const TilePos& tp) {
+  const uint32_t up = (uint32_t)(tp.r0 - tp.hr_first), down = (uint32_t)(tp.hr_last - tp.r0);
+  const uint32_t left = (uint32_t)max(0, -tp.hx0), right = (uint32_t)max(0, tp.hx0 + kPenCols - p.Wtok);
+  const uint32_t phase = (uint32_t)(tp.x0 - tp.hx0);           // fixes x0 modulo b_size and the window offset
+  return ((uint64_t)(up | (down << 8) | (left << 16) | (right << 24))) | ((uint64_t)phase << 32);
+}
+
 // Penalty row of the streamed token at halo row index `hr` / halo column `jc` into row `row` of an x tile;
 // part 0 = units 0-1, part 1 = units 2-3 (a row may be shared by two threads).  `th8` = TH / 8.
 __device__ __forceinline__ void write_penalty_row(uint8_t* tile, int row, int part_lo, int part_hi,
@@ -190,6 +199,33 @@ __device__ __forceinline__ void write_penalty_row(uint8_t* tile, int row, int pa
     if (u < th8) v = tab->row[hr][u];
     else if (u - th8 < tw8) v = tab->col[jc][u - th8];
     *reinterpret_cast<uint4*>(xtile_unit(tile, row, u)) = v;
+  }
+}
+
+// The same for two rows at once, all table reads before all stores: a warp that writes four rows per lane would
+// otherwise wait for every store before its next load (both go through shared memory, and the compiler has to
+// assume that they alias).  A row index < 0 is skipped.
+__device__ __forceinline__ void write_penalty_rows2(uint8_t* tile, int row0, int row1, const PenaltyTables* tab, int hr0,
+                                                    int jc0, int hr1, int jc1, int th8, int tw8) {
+  uint4 v[2][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int hr = i ? hr1 : hr0, jc = i ? jc1 : jc0;
+    const bool on = (i ? row1 : row0) >= 0;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      v[i][u] = make_uint4(0u, 0u, 0u, 0u);
+      if (on && u < th8) v[i][u] = ptx::lds128(ptx::smem_u32(&tab->row[hr][u]));
+      else if (on && u - th8 < tw8) v[i][u] = ptx::lds128(ptx::smem_u32(&tab->col[jc][u - th8]));
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int row = i ? row1 : row0;
+    if (row < 0) continue;
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      ptx::sts128(ptx::smem_u32(xtile_unit(tile, row, u)), v[i][u].x, v[i][u].y, v[i][u].z, v[i][u].w);
   }
 }
 

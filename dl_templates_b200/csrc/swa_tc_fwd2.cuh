@@ -1,22 +1,25 @@
-// tcgen05 forward kernel for keys that need no rotation in shared memory: k is either not rotated at
-// all or is the rotated copy a streaming pass left behind; the QUERY tile of an item is still rotated
-// on chip (NQ > 0), once, and the rotated rows are written to a second tensor that the backward
-// kernels read instead of q.  Same mathematics, tile geometry, window mask and tensor-memory layout as
-// fwd_kernel (swa_tc_fwd.cuh); what differs is who does what:
+// tcgen05 forward kernel for inputs that need no rotation in shared memory: q and k are either not
+// rotated at all or are the rotated copies a streaming pass left behind (swa_fwd_rot).  Same mathematics,
+// tile geometry, window mask and tensor-memory layout as fwd_kernel (swa_tc_fwd.cuh); what differs is who
+// does what:
 //
 //   warp 0        TMA producer: query tile (double-buffered) and the ring of K / V halo blocks
 //   warp 1        SCORE issuer: S = Q K^T (+ the window mask as 32 extra contraction columns)
 //   warp 2        PV issuer:    O_g += P V with P read from tensor memory
 //   warps 4-11    two softmax groups on alternate blocks, one thread per query row each, each with its own
 //                 running maximum / sum and its own accumulator O_g
-//   warps 12-15   one thread per row: rotation of the query tile (+ store of the rotated row), window-mask
-//                 penalty rows of every streamed block, and the EPILOGUE of every item: the two groups'
-//                 partial results are merged (in an order fixed by block position), normalised and stored
+//   warps 12-15   one thread per row: window-mask penalty rows of every streamed block, and the EPILOGUE of
+//                 every item: the two groups' partial results are merged (in an order fixed by block
+//                 position), normalised and stored
 //
 // An item has only five to seven streamed blocks.  One warp issuing every MMA ran a dependent scalar
 // instruction stream of about 2000 cycles per block while the tensor pipe needs less than half of
 // that, and an epilogue inside the softmax groups idled both at every item boundary; hence two issuers
 // (the order a single issuer gave for free becomes the barrier s_free) and epilogue warps.
+// Measured and dropped: rotating the query tile in warps 12-15 as well (about 400 dependent instructions
+// per row cost 2700 cycles per item on the critical path, 1.1 ms per launch at the default workload,
+// against 0.1 ms for a streaming pass over q), and a single warp writing all mask rows right behind the
+// producer (four rows per lane made it the slowest role of the kernel).
 //
 // All waits are bounded; a timed-out wait raises a CTA-wide abort flag, every role runs its loops to the
 // end without touching anything, TMEM is freed and the status word records it.
@@ -28,21 +31,20 @@ namespace swa {
 namespace tc {
 
 struct Fwd2Shared {
-  uint64_t q_full[2], q_ready[2], q_empty[2];
-  uint64_t kv_full[kMaxStages], k_ready[kMaxStages], kv_empty[kMaxStages];
+  uint64_t q_full[2], q_empty[2];
+  uint64_t kv_full[kMaxStages], k_ready[kMaxStages], kv_empty[kMaxStages], kx_free[kMaxStages];
   uint64_t s_full[4], p_full[4], s_free[4], pv_done[2], o_full, o_free, ml_full[2], ml_empty[2];
   float ml[2][2][2][128];   // [item parity][group][maximum | sum][row]: handed to the epilogue warps
   PenaltyTables pen;        // window-mask penalty parts of the current item's halo rows / columns
   uint32_t tmem_base;
   int abort_flag;
 };
-static_assert(sizeof(Fwd2Shared) <= sizeof(FwdShared) + 64, "the planner sizes shared memory with FwdShared + 64");
+static_assert(sizeof(Fwd2Shared) <= sizeof(FwdShared) + 128, "the planner sizes shared memory with FwdShared + 128");
 
-// NQ: width of the rotation applied to the query tile (n_rdim / 8; 0 = none).
-template <bool BF16, int NQ>
+template <bool BF16>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-            const __grid_constant__ CUtensorMap tm_v, KParams p, View4 o, float* __restrict__ lse, View4 q_rot) {
+            const __grid_constant__ CUtensorMap tm_v, KParams p, View4 o, float* __restrict__ lse) {
   using namespace ptx;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -70,7 +72,6 @@ fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
   if (threadIdx.x == 0) {
     for (int s = 0; s < 2; ++s) {
       mbar_init(&sh->q_full[s], 1);
-      mbar_init(&sh->q_ready[s], 128);
       mbar_init(&sh->q_empty[s], 1);
       mbar_init(&sh->pv_done[s], 1);
       mbar_init(&sh->ml_full[s], 256);
@@ -87,6 +88,7 @@ fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       mbar_init(&sh->kv_full[s], 1);
       mbar_init(&sh->k_ready[s], 128);
       mbar_init(&sh->kv_empty[s], 1);
+      mbar_init(&sh->kx_free[s], 1);
     }
     sh->abort_flag = 0;
     fence_barrier_init();
@@ -306,8 +308,9 @@ fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       for (int s_item = blockIdx.x; s_item < n_items;) {
         const int qb = s_it & 1;
         trace_ev(p, 1, tn, tl && s_it >= p.trace_it, 2 * 16 + (s_j & 15));
-        if (s_j == 0) wait_spin(&sh->q_ready[qb], (s_it >> 1) & 1);
-        wait_spin(&sh->k_ready[s_stage], s_stage_par);
+        if (s_j == 0) wait_spin(&sh->q_full[qb], (s_it >> 1) & 1);
+        wait_spin(&sh->kv_full[s_stage], s_stage_par);    // the block has landed ...
+        wait_spin(&sh->k_ready[s_stage], s_stage_par);    // ... and its window-mask rows are written
         // the buffer is free once the PV MMA of the block that used it last has completed
         if (s_use >= 1) wait_spin(&sh->s_free[s_buf], (s_use - 1) & 1);
         if (ok) {
@@ -326,6 +329,7 @@ fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             for (int k = 0; k < 2; ++k)  // + indicator x penalty: the window mask
               umma_ss(sd, qx_desc0 + (uint64_t)(k * (kXStepBytes >> 4)), kxd + (uint64_t)(k * (kXStepBytes >> 4)), idesc_s, 1u);
             umma_commit(&sh->s_full[s_buf]);
+            umma_commit(&sh->kx_free[s_stage]);                      // the mask rows of this stage may be overwritten
             if (s_j == s_nblk - 1) umma_commit(&sh->q_empty[qb]);   // last read of this query buffer
           }
           __syncwarp();
@@ -392,18 +396,11 @@ fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
     const int quarter = warp & 3;
     const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
     using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
-    const bool rope_on = NQ > 0 && p.rope.idx != nullptr;
     const float c2 = p.scale_log2;
     int tn = 0;
     write_indicator_row<BF16>(qx_smem, t, 0, 1, p);               // the same for every item
     const bool row_on = t < N;
     const int jr = t / pl.KW, jc = t % pl.KW;                     // this thread's row inside every streamed block
-    RopeParts qparts;                                             // this thread rotates both halves of its query row
-    qparts.row = t;
-    qparts.lo = 0;
-    qparts.hi = 1;
-    qparts.active = true;
-
     // Epilogue of one item: merge the two groups' partial results of this thread's row and store it.
     // `gb` = stream position of the item's block 0, `nblk` = its blocks.
     auto epilogue = [&](int item, int it, uint32_t gb, int nblk) {
@@ -468,7 +465,9 @@ fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       trace_ev(p, 5, tn, t == 0 && it >= p.trace_it, 3 * 16 + (it & 15));
     };
 
-    int stage = 0, stage_par = 0;
+    int stage = 0, stage_par = 1;                    // parity of the "free" phase a rewrite of this stage's rows waits for
+    bool ring_full = false;
+    uint64_t pen_sig = ~0ull;                        // geometry the penalty tables in shared memory were built for
     uint32_t G = 0;                                  // stream position of the next block to prepare
     bool pend = false;                               // an item whose epilogue has not run yet
     int pend_item = 0, pend_it = 0, pend_nblk = 0;
@@ -476,53 +475,29 @@ fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
 #pragma unroll 1
     for (int it = 0, item = blockIdx.x;; ++it, item += gridDim.x) {   // one extra round flushes the last epilogue
       const bool have = item < n_items;
-      const int bh = have ? item / tiles_per_head : 0, bi = bh / p.H, hi = bh - bi * p.H;
+      const int bh = have ? item / tiles_per_head : 0;
       TilePos tp;
       tp.r0 = tp.x0 = tp.hx0 = tp.hr_first = tp.hr_last = 0;
       tp.nblk = 0;
       if (have) tp = tile_pos(p, item - bh * tiles_per_head);
       const uint32_t gb = G;
       if (have) {
-        const int qb = it & 1;
-        const int qr = tp.r0 + t / pl.TW, qx = tp.x0 + t % pl.TW;
-        const bool q_in = qr < p.t_h && qx < p.Wtok;
-        RopeRow rc;                                  // register cache of this thread's cos/sin values
-        rc.pos[0] = rc.pos[1] = -1;
-        if constexpr (NQ > 0) {
-          int32_t packed = -1;
-          if (rope_on && q_in) packed = __ldg(p.rope.idx + qr * p.Wtok + qx);
-          if (rope_on) rope_fetch_t<NQ>(rc, packed, qparts, p.rope);    // in flight while the tile arrives
-        }
-        named_bar_sync(5, 128);           // nobody still reads the previous item's tables
-        build_penalty_tables<BF16>(&sh->pen, t, p, tp, 128);
-        named_bar_sync(5, 128);
-        // ---- the query tile: rotate this thread's row in shared memory, hand the rotated row on
-        wait_park(&sh->q_full[qb], (uint32_t)((it >> 1) & 1));
-        if (ok) {
-          if constexpr (NQ > 0) {
-            if (rope_on) {
-              uint8_t* const tile = q_smem + qb * q_bytes;
-              rope_apply_t<BF16, NQ>(tile, 16384u, rc, qparts, p.rope);
-              if (q_in && q_rot.ptr != nullptr) {
-                T* dst = (T*)q_rot.ptr + bi * q_rot.s0 + hi * q_rot.s1 + ((int64_t)qr * p.Wtok + qx) * q_rot.s2;
-#pragma unroll 1
-                for (int c = 0; c < p.qch; ++c) {
-#pragma unroll
-                  for (int u = 0; u < 8; ++u)
-                    reinterpret_cast<uint4*>(dst + c * 64)[u] = lds128(smem_u32(swz(tile + c * 16384, t, u)));
-                }
-              }
-              fence_proxy_async_smem();
-            }
-          }
-          mbar_arrive(&sh->q_ready[qb]);
+        // the tables depend only on how the halo is clipped by the grid: interior tiles share them
+        const uint64_t sig = penalty_signature(p, tp);
+        if (sig != pen_sig) {
+          pen_sig = sig;
+          named_bar_sync(5, 128);           // nobody still reads the previous tables
+          build_penalty_tables<BF16>(&sh->pen, t, p, tp, 128);
+          named_bar_sync(5, 128);
         }
       }
 #pragma unroll 1
       for (int j = 0;; ++j, ++G) {
-        // The block at stream position (last block of an item + stages) is the first one whose load had to wait
-        // for that item's last PV MMA: the item's epilogue runs right before it (or at the end of the next item
-        // when that one is shorter than the ring, or after the last item).
+        // These warps run ahead of the score MMAs by up to `stages` blocks (a stage's mask rows are free as soon as
+        // the score MMA that read them has completed; the K / V data need not have landed).  The block at stream
+        // position (last block of an item + score buffers + stages) is the first one they would have to wait for
+        // until that item's last PV MMA has completed: the item's epilogue runs right before it (or at the end of
+        // a later item that ends earlier, or after the last item), hidden behind that lead.
         const bool at_end = j >= tp.nblk;
         if (pend && (at_end || G >= pend_G)) {
           epilogue(pend_item, pend_it, pend_gb, pend_nblk);
@@ -530,7 +505,7 @@ fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         }
         if (at_end) break;
         trace_ev(p, 4, tn, t == 0 && it >= p.trace_it, 0 * 16 + (j & 15));
-        wait_park(&sh->kv_full[stage], (uint32_t)stage_par);
+        if (ring_full) wait_park(&sh->kx_free[stage], (uint32_t)stage_par);
         trace_ev(p, 4, tn, t == 0 && it >= p.trace_it, 1 * 16 + (j & 15));
         if (ok) {
           if (row_on)
@@ -539,7 +514,7 @@ fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
           mbar_arrive(&sh->k_ready[stage]);
         }
         trace_ev(p, 4, tn, t == 0 && it >= p.trace_it, 2 * 16 + (j & 15));
-        if (++stage == pl.stages) { stage = 0; stage_par ^= 1; }
+        if (++stage == pl.stages) { stage = 0; stage_par ^= 1; ring_full = true; }
       }
       if (!have) break;
       pend = true;
@@ -547,7 +522,7 @@ fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       pend_it = it;
       pend_gb = gb;
       pend_nblk = tp.nblk;
-      pend_G = G - 1 + (uint32_t)pl.stages;
+      pend_G = G - 1 + (uint32_t)(pl.stages + nsb);
     }
   }
 

@@ -13,7 +13,7 @@ from typing import Optional, Sequence, Tuple
 
 import torch
 
-from .tiled_swa import swa_backward, swa_forward
+from .tiled_swa import swa_backward, swa_backward_rot, swa_forward, swa_forward_rot
 
 
 class HostPipeline:
@@ -35,12 +35,14 @@ class HostPipeline:
         self.s_out = torch.cuda.Stream(self.device)
         self.done = torch.cuda.Event()
         self._stage = None
+        self._buf_free = None      # per staging buffer: event after the last kernel that read it (kept ACROSS runs)
 
     def _staging(self, shapes, dtype):
         key = (tuple(shapes), dtype)
         if self._stage is None or self._stage[0] != key:
             bufs = [[torch.empty(s, dtype=dtype, device=self.device) for s in shapes] for _ in range(self.nbuf)]
             self._stage = (key, bufs)
+            self._buf_free = [None] * self.nbuf
         return self._stage[1]
 
     def run(self, q, k, v, do, outs: Sequence[Optional[torch.Tensor]], rope, window, sm_scale):
@@ -52,7 +54,9 @@ class HostPipeline:
         stage = self._staging(shapes, q.dtype)
         compute = torch.cuda.current_stream(self.device)
         in_ready = [torch.cuda.Event() for _ in range(self.nbuf)]
-        buf_free = [None] * self.nbuf
+        # A run may start while the kernels of the previous run still read the staging buffers (nothing else orders
+        # the copy-in stream after them): the "buffer is free" events therefore live on the object, not in the call.
+        buf_free = self._buf_free
         out_events = []
         n_chunks = (S + c - 1) // c
         for i in range(n_chunks):
@@ -68,10 +72,16 @@ class HostPipeline:
                 in_ready[b].record(self.s_in)
             compute.wait_event(in_ready[b])
             qd, kd, vd = dev[:3]
-            o, lse = swa_forward(qd, kd, vd, rope, *window, sm_scale)
-            res = (o,)
-            if with_bwd:
-                res += tuple(swa_backward(qd, kd, vd, o, lse, dev[3], rope, *window, sm_scale))
+            if rope is not None:      # rotated copies handed from forward to backward
+                o, lse, q_rot, k_rot = swa_forward_rot(qd, kd, vd, rope, *window, sm_scale)
+                res = (o,)
+                if with_bwd:
+                    res += tuple(swa_backward_rot(q_rot, k_rot, vd, o, lse, dev[3], rope, *window, sm_scale))
+            else:
+                o, lse = swa_forward(qd, kd, vd, None, *window, sm_scale)
+                res = (o,)
+                if with_bwd:
+                    res += tuple(swa_backward(qd, kd, vd, o, lse, dev[3], None, *window, sm_scale))
             ev = torch.cuda.Event()
             ev.record(compute)
             buf_free[b] = ev

@@ -6,8 +6,8 @@ Same names and argument order as the reference:
   ``TiledSwa.apply(q, k, v, b_size, t_height, t_width, row_size, col_size, sm_scale)``   (src/tiled_swa.py:604)
   ``tiled_swa_fwd(q, k, v, b_size, t_height, t_width, row_size, col_size, sm_scale=1.0)`` (src/tiled_swa.py:564)
 
-plus the composed entry the reference does not have, which rotates q and k on
-chip instead of in two extra passes over HBM:
+plus the composed entry the reference does not have (RoPE-2D and attention as one
+autograd function; q and k stay untouched, their gradients come back un-rotated):
 
   ``TiledSwaRope2D.apply(q, k, v, idx, row_cs_buffer, col_cs_buffer, b_size, t_height,
   t_width, row_size, col_size, sm_scale)``
@@ -318,37 +318,39 @@ class TiledSwa(torch.autograd.Function):
         return dq, dk, dv, None, None, None, None, None, None
 
 
-_rope_mode = os.environ.get("SWA_ROPE_MODE", "fused")
+_rope_mode = os.environ.get("SWA_ROPE_MODE", "handoff")
+_ROPE_MODES = ("handoff", "fused", "prerotate")
 
 
 def set_rope_mode(mode: str) -> str:
-    """How ``TiledSwaRope2D`` applies the rotation; returns the previous mode.
+    """How ``TiledSwaRope2D`` and ``TiledSwaPackedQKV`` apply the rotation; returns the previous mode.
 
-    ``"fused"`` (default): q and k are rotated on chip inside the attention kernels; no temporaries, but every
-    streamed row is rotated once per tile whose window contains it.  ``"prerotate"``: the stand-alone kernel
-    rotates copies of q and k once (src/fused_rope2d.py:126-168 followed by src/tiled_swa.py:604, the reference's
-    own composition), the attention kernels run without RoPE on the copies, which replace q and k among the saved
-    tensors, and dq, dk are rotated back in place; two extra passes over q and k, each row rotated once.
-    ``"auto"``: ``"prerotate"`` for problems whose cos/sin tables the fused kernels cannot stage in shared
-    memory (e.g. 256 x 256 positions with 128 rotated dims, where fusing was measured 1.7x slower), else ``"fused"``.
-    A module-level switch like the reference's ``use_fused_na()`` / ``use_autotuner()`` toggles."""
+    ``"handoff"`` (default): every q and k row is rotated exactly once, by a streaming pass that writes rotated
+    copies (``swa_forward_rot``); all three attention kernels read the copies, which replace q and k among the
+    tensors saved for backward (the reference keeps the same thing: its RoPE rotates q and k in place,
+    src/fused_rope2d.py:143-145), and the backward kernels rotate dq and dk back in their epilogues
+    (``swa_backward_rot``).  ``"fused"``: every kernel rotates the rows it streams in shared memory (no temporaries,
+    but a row is rotated once per tile whose window holds it: 4.4x at a 13 x 13 window).  ``"prerotate"``: the
+    reference's own composition (src/fused_rope2d.py:126-168 around src/tiled_swa.py:604) -- rotated copies,
+    attention without RoPE, separate in-place inverse rotation of dq and dk.  A module-level switch like the
+    reference's ``use_fused_na()`` / ``use_autotuner()`` toggles."""
     global _rope_mode
-    if mode not in ("fused", "prerotate", "auto"):
-        raise ValueError("rope mode must be 'fused', 'prerotate' or 'auto'")
+    if mode == "auto":
+        mode = "handoff"
+    if mode not in _ROPE_MODES:
+        raise ValueError(f"rope mode must be one of {_ROPE_MODES}")
     prev, _rope_mode = _rope_mode, mode
     return prev
 
 
-def _prerotate_wanted(q, v, rope, win) -> bool:
-    if rope is None or _rope_mode == "fused":
-        return False
-    if _rope_mode == "prerotate":
-        return True
-    g = _geom(q, v, *win, "auto")
-    r = _lib.make_rope(*rope)
-    plan = (C.c_int32 * 12)()
-    # tensor-core forward plan without staged tables (plan[8] == 0): the rotating warps would fetch from L2
-    return _lib.lib.swa_describe_plan(C.byref(g), C.byref(r), 0, plan) == 0 and plan[8] == 0
+def _mode_for(q, v, rope, win) -> str:
+    """The mode a call runs in: 'none' without RoPE; head dims that only reach the tensor-core kernels through
+    zero padding take the fused path (the padding wrapper lives there)."""
+    if rope is None:
+        return "none"
+    if _rope_mode == "handoff" and padded_head_dims(q, v, rope, *win) is not None:
+        return "fused"
+    return _rope_mode
 
 
 def _flat3(x):
@@ -356,12 +358,13 @@ def _flat3(x):
 
 
 class TiledSwaRope2D(torch.autograd.Function):
-    """RoPE-2D on q and k fused into the attention kernels.
+    """RoPE-2D and the attention as one autograd function.
 
     Equivalent to ``TiledSwa.apply(rope(q, idx), rope(k, idx), v, ...)`` with
-    ``rope`` = ``RotaryPE2D`` (src/fused_rope2d.py:124-168), but q and k are read
-    un-rotated, rotated on chip, and left unmodified; ``dq``/``dk`` are gradients
-    of the un-rotated tensors.  ``idx`` may be ``None`` (no rotation).
+    ``rope`` = ``RotaryPE2D`` (src/fused_rope2d.py:124-168), but q and k are left
+    unmodified and ``dq``/``dk`` are gradients of the un-rotated tensors (rotated back
+    inside the backward kernels).  How the rotation itself is done: ``set_rope_mode``.
+    ``idx`` may be ``None`` (no rotation).
     """
 
     @staticmethod
@@ -371,14 +374,17 @@ class TiledSwaRope2D(torch.autograd.Function):
         if rope is not None:
             assert idx.shape[0] == q.shape[2]
             assert row_cs_buffer.shape[1] == col_cs_buffer.shape[1]
-        ctx.prerotated = _prerotate_wanted(q, v, rope, (b_size, t_height, t_width, row_size, col_size, sm_scale))
-        if ctx.prerotated:
+        win = (b_size, t_height, t_width, row_size, col_size, sm_scale)
+        ctx.mode = _mode_for(q, v, rope, win)
+        if ctx.mode == "handoff":       # q, k below are the rotated copies: they are what backward needs
+            o, lse, q, k = swa_forward_rot(q, k, v, rope, *win)
+        elif ctx.mode == "prerotate":
             from .fused_rope2d import rope2d_apply_to
             q, k = (rope2d_apply_to(t.reshape(-1, t.shape[2], t.shape[3]) if t.is_contiguous() else
                                     t.contiguous().view(-1, t.shape[2], t.shape[3]), *rope).view(t.shape) for t in (q, k))
-            o, lse = swa_forward(q, k, v, None, b_size, t_height, t_width, row_size, col_size, sm_scale)
+            o, lse = swa_forward(q, k, v, None, *win)
         else:
-            o, lse = swa_forward(q, k, v, rope, b_size, t_height, t_width, row_size, col_size, sm_scale)
+            o, lse = swa_forward(q, k, v, rope, *win)
         if rope is None:
             ctx.save_for_backward(q, k, v, lse, o)
         else:
@@ -391,7 +397,9 @@ class TiledSwaRope2D(torch.autograd.Function):
         saved = ctx.saved_tensors
         q, k, v, lse, o = saved[:5]
         rope = tuple(saved[5:8]) if len(saved) == 8 else None
-        if ctx.prerotated:     # q, k are the rotated copies
+        if ctx.mode == "handoff":      # q, k are the rotated copies; dq, dk come back un-rotated
+            dq, dk, dv = swa_backward_rot(q, k, v, o, lse, do, rope, *ctx.win)
+        elif ctx.mode == "prerotate":  # q, k are the rotated copies
             from .fused_rope2d import rope2d_apply_
             dq, dk, dv = swa_backward(q, k, v, o, lse, do, None, *ctx.win)
             dq, dk = (t if t.is_contiguous() else t.contiguous() for t in (dq, dk))
@@ -425,18 +433,23 @@ class TiledSwaPackedQKV(torch.autograd.Function):
         q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
         rope = None if idx is None else (idx, row_cs_buffer, col_cs_buffer)
         o_buf = torch.empty((B, N, H, d), dtype=qkv.dtype, device=qkv.device)
-        _, lse = swa_forward(q, k, v, rope, b_size, t_height, t_width, row_size, col_size, sm_scale,
-                             out=o_buf.permute(0, 2, 1, 3))
-        saved = (qkv, lse, o_buf) if rope is None else (qkv, lse, o_buf, idx, row_cs_buffer, col_cs_buffer)
+        win = (b_size, t_height, t_width, row_size, col_size, sm_scale)
+        ctx.handoff = _mode_for(q, v, rope, win) == "handoff"
+        if ctx.handoff:   # the rotated copies ([B,H,N,d]) are kept for backward; v is still read from the packed tensor
+            _, lse, q_rot, k_rot = swa_forward_rot(q, k, v, rope, *win, out=o_buf.permute(0, 2, 1, 3))
+            saved = (qkv, lse, o_buf, idx, row_cs_buffer, col_cs_buffer, q_rot, k_rot)
+        else:
+            _, lse = swa_forward(q, k, v, rope, *win, out=o_buf.permute(0, 2, 1, 3))
+            saved = (qkv, lse, o_buf) if rope is None else (qkv, lse, o_buf, idx, row_cs_buffer, col_cs_buffer)
         ctx.save_for_backward(*saved)
-        ctx.win = (b_size, t_height, t_width, row_size, col_size, sm_scale)
+        ctx.win = win
         return o_buf.view(B, N, H * d)
 
     @staticmethod
     def backward(ctx, do):
         saved = ctx.saved_tensors
         qkv, lse, o_buf = saved[:3]
-        rope = tuple(saved[3:6]) if len(saved) == 6 else None
+        rope = tuple(saved[3:6]) if len(saved) >= 6 else None
         B, N, _, H, d = qkv.shape
         if do.stride(-1) != 1 or do.stride(1) % 8 or do.stride(0) % 8 or do.data_ptr() % 16:
             do = do.contiguous()
@@ -444,5 +457,8 @@ class TiledSwaPackedQKV(torch.autograd.Function):
         q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
         dqkv = torch.empty((B, N, 3, H, d), dtype=qkv.dtype, device=qkv.device)
         outs = tuple(dqkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
-        swa_backward(q, k, v, o_buf.permute(0, 2, 1, 3), lse, do4, rope, *ctx.win, out=outs)
+        if ctx.handoff:
+            swa_backward_rot(saved[6], saved[7], v, o_buf.permute(0, 2, 1, 3), lse, do4, rope, *ctx.win, out=outs)
+        else:
+            swa_backward(q, k, v, o_buf.permute(0, 2, 1, 3), lse, do4, rope, *ctx.win, out=outs)
         return (dqkv,) + (None,) * 9

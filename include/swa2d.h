@@ -94,11 +94,11 @@ int swa_bwd_dkdv(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t
                  const swa_tensor_t* dk, const swa_tensor_t* dv, int32_t* status, void* stream);
 
 /* The same three steps with the rotation handed on from kernel to kernel, so that every q and k row is rotated
- * exactly once on chip (swa_fwd / swa_bwd_* with rope != NULL rotate a streamed row once per tile whose window
- * holds it).  q_rot and k_rot are caller-provided tensors of the shapes of q and k; q and k stay untouched.
- *   swa_fwd_rot     - a streaming pass writes rope(k) to k_rot, then the attention kernel rotates each query tile
- *                     in shared memory before its MMAs, stores the rotated rows to q_rot, and streams k_rot.
- *                     Same o and lse as swa_fwd(rope).  Replaces the same launches as swa_fwd (two
+ * exactly once (swa_fwd / swa_bwd_* with rope != NULL rotate a streamed row once per tile whose window holds
+ * it).  q_rot and k_rot are caller-provided tensors of the shapes of q and k; q and k stay untouched.
+ *   swa_fwd_rot     - one streaming pass each writes rope(q) to q_rot and rope(k) to k_rot (clone + rotate, every
+ *                     byte moved once), then the attention kernel runs on the rotated copies with no rotation
+ *                     work of its own.  Same o and lse as swa_fwd(rope).  Replaces the same launches as swa_fwd (two
  *                     rope2d_fwd_kernel launches, src/fused_rope2d.py:138, and the forward kernel,
  *                     src/tiled_swa.py:611-637); what the reference leaves behind by rotating q and k in place
  *                     (src/fused_rope2d.py:143-145) is what q_rot / k_rot hold here.

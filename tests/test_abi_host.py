@@ -178,17 +178,65 @@ def test_planner_refuses_overrides_beyond_tensor_memory(monkeypatch):
     assert _plan(g, None, 0)[0] < 0
 
 
-def test_auto_rope_mode_follows_table_staging():
-    """'auto' pre-rotates exactly when the fused forward plan cannot stage the cos/sin tables (host-only check)."""
+def test_rope_mode_switch():
+    """``set_rope_mode`` accepts the three modes (and 'auto' as an alias of the default), returns the previous one,
+    rejects anything else; without RoPE a call has no mode (host-only check)."""
     from dl_templates_b200 import tiled_swa as ts
-    prev = swa.set_rope_mode("auto")
+    prev = swa.set_rope_mode("fused")
     try:
-        for grid, d, R, half, want in ((256, 128, 32, 15, True), (128, 64, 16, 6, False), (64, 64, 8, 3, False)):
-            q = torch.zeros(1, 1, grid * grid, d, dtype=torch.bfloat16)
-            rope = (torch.zeros(grid * grid, dtype=torch.int32), torch.zeros(grid, R, 2), torch.zeros(grid, R, 2))
-            assert ts._prerotate_wanted(q, q, rope, (1, grid, grid, half, half, 0.1)) is want
-        assert ts._prerotate_wanted(q, q, None, (1, grid, grid, half, half, 0.1)) is False
+        assert swa.set_rope_mode("auto") == "fused"
+        assert swa.set_rope_mode("prerotate") == "handoff"
+        q = torch.zeros(1, 1, 64 * 64, 64, dtype=torch.bfloat16)
+        assert ts._mode_for(q, q, None, (1, 64, 64, 3, 3, 0.1)) == "none"
     finally:
         swa.set_rope_mode(prev)
     with pytest.raises(ValueError):
         swa.set_rope_mode("sometimes")
+
+
+def test_noalloc_rejects_everything_before_its_first_launch():
+    """swa_bwd_noalloc runs every check of the three calls it makes before the first of them: a NULL output, a bad
+    RoPE description or a tensor-core request the dK/dV plan cannot serve is a negative return with nothing
+    enqueued (the launch counter does not move; no GPU is needed to see that)."""
+    g = _geom(t_height=16, t_width=16, row_size=2, col_size=2)
+    t = _lib.Tensor4()
+    t.ptr = 256
+    for i, st in enumerate((16 * 16 * 64, 16 * 16 * 64, 64, 1)):
+        t.stride[i] = st
+    null = _lib.Tensor4()
+    before = _lib.launch_count()
+    args = [C.byref(t)] * 5
+    lse = C.c_void_p(512)
+    ok_outs = [C.byref(t)] * 3
+    for bad in range(3):
+        outs = list(ok_outs)
+        outs[bad] = C.byref(null)
+        assert _lib.lib.swa_bwd_noalloc(C.byref(g), None, *args, lse, *outs, None, None) < 0
+        assert b"NULL" in _lib.lib.swa_last_error()
+    bad_rope = _lib.Rope(1024, 0, 0, 16, 16, 16)                       # tables missing
+    assert _lib.lib.swa_bwd_noalloc(C.byref(g), C.byref(bad_rope), *args, lse, *ok_outs, None, None) < 0
+    bad_rope = _lib.Rope(1024, 2048, 4096, 24, 16, 16)                 # 4 * n_rdim > d_qk
+    assert _lib.lib.swa_bwd_noalloc(C.byref(g), C.byref(bad_rope), *args, lse, *ok_outs, None, None) < 0
+    assert _lib.lib.swa_bwd_noalloc(C.byref(g), None, *args, None, *ok_outs, None, None) < 0   # lse NULL
+    g_tc = _geom(t_height=16, t_width=16, row_size=2, col_size=2, d_qk=48, impl="tc")          # no tensor-core kernel
+    assert _lib.lib.swa_bwd_noalloc(C.byref(g_tc), None, *args, lse, *ok_outs, None, None) < 0
+    assert _lib.launch_count() == before
+
+
+def test_rot_entries_need_a_rope_description():
+    """swa_fwd_rot / swa_bwd_*_rot exist for RoPE; without one they point at the plain entry points."""
+    g = _geom(t_height=16, t_width=16, row_size=2, col_size=2)
+    t = _lib.Tensor4()
+    t.ptr = 256
+    for i, st in enumerate((16 * 16 * 64, 16 * 16 * 64, 64, 1)):
+        t.stride[i] = st
+    p = C.c_void_p(512)
+    before = _lib.launch_count()
+    assert _lib.lib.swa_fwd_rot(C.byref(g), None, *([C.byref(t)] * 4), p, C.byref(t), C.byref(t), None, None) < 0
+    assert b"RoPE" in _lib.lib.swa_last_error()
+    assert _lib.lib.swa_bwd_dq_rot(C.byref(g), None, *([C.byref(t)] * 4), p, p, C.byref(t), None, None) < 0
+    assert _lib.lib.swa_bwd_dkdv_rot(C.byref(g), None, *([C.byref(t)] * 4), p, p, C.byref(t), C.byref(t), None, None) < 0
+    rope = _lib.Rope(1024, 2048, 4096, 16, 16, 16)
+    assert _lib.lib.swa_fwd_rot(C.byref(g), C.byref(rope), *([C.byref(t)] * 4), p, C.byref(t), C.byref(t), None, None) < 0
+    assert b"alias" in _lib.lib.swa_last_error()                      # q_rot / k_rot must be separate tensors
+    assert _lib.launch_count() == before

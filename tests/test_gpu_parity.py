@@ -17,14 +17,28 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def run_gpu(q, k, v, do, rope, win, sm_scale, impl="auto"):
-    """Forward (+ backward when ``do`` is given) through the ABI; returns CPU tensors."""
+PATHS = ["handoff", "fused"]
+
+
+def run_gpu(q, k, v, do, rope, win, sm_scale, impl="auto", path="fused"):
+    """Forward (+ backward when ``do`` is given) through the ABI; returns CPU tensors.
+
+    ``path`` (only matters with RoPE): ``"fused"`` = swa_fwd / swa_bwd_dq / swa_bwd_dkdv, every kernel rotates the rows
+    it streams; ``"handoff"`` = swa_fwd_rot / swa_bwd_dq_rot / swa_bwd_dkdv_rot, rotated copies handed from forward to
+    backward (the default of the autograd surfaces)."""
     qd, kd, vd = (t.to(DEV) for t in (q, k, v))
     rd = None if rope is None else tuple(t.to(DEV) for t in rope)
-    o, lse = swa.swa_forward(qd, kd, vd, rd, *win, sm_scale, impl=impl)
-    outs = [o]
-    if do is not None:
-        outs += list(swa.swa_backward(qd, kd, vd, o, lse, do.to(DEV), rd, *win, sm_scale, impl=impl))
+    if rd is not None and path == "handoff":
+        o, lse, q_rot, k_rot = swa.swa_forward_rot(qd, kd, vd, rd, *win, sm_scale, impl=impl)
+        outs = [o]
+        if do is not None:
+            outs += list(swa.swa_backward_rot(q_rot, k_rot, vd, o, lse, do.to(DEV), rd, *win, sm_scale, impl=impl))
+        assert torch.equal(qd.cpu(), q) and torch.equal(kd.cpu(), k)       # q and k stay untouched
+    else:
+        o, lse = swa.swa_forward(qd, kd, vd, rd, *win, sm_scale, impl=impl)
+        outs = [o]
+        if do is not None:
+            outs += list(swa.swa_backward(qd, kd, vd, o, lse, do.to(DEV), rd, *win, sm_scale, impl=impl))
     swa.check_status()
     return [t.float().cpu() for t in outs], lse.cpu()
 
@@ -37,57 +51,65 @@ def assert_close(got, want, dtype, names=("o", "dq", "dk", "dv"), what=""):
         assert a < ma and r < mr, f"{what} {n}: max_abs={a:.3e} (<{ma}) mean_rel={r:.3e} (<{mr})"
 
 
+@pytest.mark.parametrize("path", PATHS)
 @pytest.mark.parametrize("impl", ["auto", "simt"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("name", SWA_GOLDEN_CASES)
-def test_golden_cases(name, dtype, impl):
+def test_golden_cases(name, dtype, impl, path):
     g = load_golden(name)
     m = g["meta"]
     win = (m["b_size"], m["t_height"], m["t_width"], m["row_size"], m["col_size"])
     q, k, v, do = (g[x].to(dtype) for x in ("q", "k", "v", "do"))
     rope = (g["idx"], g["row_cs"], g["col_cs"]) if "idx" in g else None
-    got, _ = run_gpu(q, k, v, do, rope, win, g["sm_scale"], impl)
+    if rope is None and path != PATHS[0]:
+        pytest.skip("no RoPE in this case: both paths are the same call")
+    got, _ = run_gpu(q, k, v, do, rope, win, g["sm_scale"], impl, path)
     if dtype == torch.float32:
         want = [g["o"], g["dq"], g["dk"], g["dv"]]      # the reference's own stored outputs
     else:
         want = orc.fused_ref(q.float(), k.float(), v.float(), do.float(), *(rope or (None, None, None)), *win,
                              g["sm_scale"])
-    assert_close(got, want, dtype, what=f"{name}/{impl}")
+    assert_close(got, want, dtype, what=f"{name}/{impl}/{path}")
 
 
-def _config_check(cfg_name, B, H, impl="auto", windowed=False):
+def _config_check(cfg_name, B, H, impl="auto", windowed=False, path="handoff"):
     cfg = CONFIGS[cfg_name]
     c = make_case(cfg, B=B, H=H)
     rope = (c["idx"], c["row_cs"], c["col_cs"])
     do = c["do"] if cfg["bwd"] else None
-    got, lse = run_gpu(c["q"], c["k"], c["v"], do, rope, c["win"], c["sm_scale"], impl)
+    got, lse = run_gpu(c["q"], c["k"], c["v"], do, rope, c["win"], c["sm_scale"], impl, path)
     f = lambda t: None if t is None else t.float()
     want = orc.fused_ref(f(c["q"]), f(c["k"]), f(c["v"]), f(do), *rope, *c["win"], c["sm_scale"], windowed=windowed)
     if do is None:
         want = [want]
-    assert_close(got, want, cfg["dtype"], what=f"{cfg_name}/{impl}")
+    assert_close(got, want, cfg["dtype"], what=f"{cfg_name}/{impl}/{path}")
     return got
 
 
-def test_config1_fp32_full():
-    _config_check("cfg1", None, None)
+@pytest.mark.parametrize("path", PATHS)
+def test_config1_fp32_full(path):
+    _config_check("cfg1", None, None, path=path)
 
 
-def test_config2_bf16_forward_full():
-    _config_check("cfg2", None, None)
+@pytest.mark.parametrize("path", PATHS)
+def test_config2_bf16_forward_full(path):
+    _config_check("cfg2", None, None, path=path)
 
 
-def test_config3_fp16_dropped_idx():
+@pytest.mark.parametrize("path", PATHS)
+def test_config3_fp16_dropped_idx(path):
     # 8 of the 96 (batch, head) slices: the dense oracle is O(N^2) per slice
-    _config_check("cfg3", 2, 4)
+    _config_check("cfg3", 2, 4, path=path)
 
 
-def test_config4_mixed_dims_slices():
-    _config_check("cfg4", 1, 2, windowed=True)
+@pytest.mark.parametrize("path", PATHS)
+def test_config4_mixed_dims_slices(path):
+    _config_check("cfg4", 1, 2, windowed=True, path=path)
 
 
-def test_target_config_slices():
-    _config_check("target", 1, 2, windowed=True)
+@pytest.mark.parametrize("path", PATHS)
+def test_target_config_slices(path):
+    _config_check("target", 1, 2, windowed=True, path=path)
 
 
 def test_lse_matches_oracle():
@@ -142,11 +164,12 @@ def test_strided_inputs():
     assert_close([t.float().cpu() for t in (o, dq, dk, dv)], want, torch.bfloat16, what="strided")
 
 
-def test_bitwise_determinism():
+@pytest.mark.parametrize("path", PATHS)
+def test_bitwise_determinism(path):
     c = make_case(CONFIGS["cfg2"], B=1, H=2)
     rope = (c["idx"], c["row_cs"], c["col_cs"])
-    a, _ = run_gpu(c["q"], c["k"], c["v"], c["do"], rope, c["win"], c["sm_scale"])
-    b, _ = run_gpu(c["q"], c["k"], c["v"], c["do"], rope, c["win"], c["sm_scale"])
+    a, _ = run_gpu(c["q"], c["k"], c["v"], c["do"], rope, c["win"], c["sm_scale"], path=path)
+    b, _ = run_gpu(c["q"], c["k"], c["v"], c["do"], rope, c["win"], c["sm_scale"], path=path)
     for x, y in zip(a, b):
         assert torch.equal(x, y)
 
@@ -169,20 +192,23 @@ def test_rows_of_p_sum_to_one_and_linearity_in_v():
     assert (oc.float() - (2 * oa.float() + ob.float())).abs().max().item() < 6e-2
 
 
-def test_batch_head_slices_are_independent():
+@pytest.mark.parametrize("path", PATHS)
+def test_batch_head_slices_are_independent(path):
     """A sharded run must equal the unsharded one bitwise: computing slices [2:4) alone
     gives the same bits as those slices of the full call."""
     c = make_case(CONFIGS["cfg2"], B=1, H=4)
     rope = (c["idx"], c["row_cs"], c["col_cs"])
-    full, _ = run_gpu(c["q"], c["k"], c["v"], c["do"], rope, c["win"], c["sm_scale"])
-    part, _ = run_gpu(c["q"][:, 2:4], c["k"][:, 2:4], c["v"][:, 2:4], c["do"][:, 2:4], rope, c["win"], c["sm_scale"])
+    full, _ = run_gpu(c["q"], c["k"], c["v"], c["do"], rope, c["win"], c["sm_scale"], path=path)
+    part, _ = run_gpu(c["q"][:, 2:4], c["k"][:, 2:4], c["v"][:, 2:4], c["do"][:, 2:4], rope, c["win"], c["sm_scale"],
+                      path=path)
     for x, y in zip(full, part):
         assert torch.equal(x[:, 2:4], y)
 
 
+@pytest.mark.parametrize("path", PATHS)
 @pytest.mark.parametrize("b_size,G,wr,wc", [(2, 10, 2, 1), (4, 9, 1, 1), (16, 6, 1, 1)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-def test_tiles_of_several_tokens_on_the_tensor_core_path(b_size, G, wr, wc, dtype):
+def test_tiles_of_several_tokens_on_the_tensor_core_path(b_size, G, wr, wc, dtype, path):
     """b_size > 1 (the reference's own regime is 16): every token of a tile attends every token of
     the tiles in the window; RoPE indices are per token (tokens of a tile share its coordinates)."""
     torch.manual_seed(b_size)
@@ -198,21 +224,49 @@ def test_tiles_of_several_tokens_on_the_tensor_core_path(b_size, G, wr, wc, dtyp
     win = (b_size, G, G, wr, wc)
     qd, vd = q.to(DEV), v.to(DEV)
     assert swa.selected_impl(qd, vd, tuple(t.to(DEV) for t in rope), *win, 0.125) == "tc"
-    got, _ = run_gpu(q, k, v, do, rope, win, 0.125)
+    got, _ = run_gpu(q, k, v, do, rope, win, 0.125, path=path)
     want = orc.fused_ref(q.float(), k.float(), v.float(), do.float(), *rope, *win, 0.125)
-    assert_close(got, want, dtype, what=f"b_size={b_size}")
+    assert_close(got, want, dtype, what=f"b_size={b_size}/{path}")
 
 
-def test_config5_geometry_on_a_smaller_grid():
+@pytest.mark.parametrize("path", PATHS)
+def test_config5_geometry_on_a_smaller_grid(path):
     """d_qk = d_v = 128, 31x31 window, RoPE on all 128 dims (n_rdim 32) as in the largest configuration,
     on a 96x96 grid the windowed oracle finishes in seconds."""
     cfg = dict(CONFIGS["cfg5"])
     cfg["grid"] = 96
     c = make_case(cfg, B=1, H=1)
     rope = (c["idx"], c["row_cs"], c["col_cs"])
-    got, _ = run_gpu(c["q"], c["k"], c["v"], c["do"], rope, c["win"], c["sm_scale"])
+    got, _ = run_gpu(c["q"], c["k"], c["v"], c["do"], rope, c["win"], c["sm_scale"], path=path)
     want = orc.fused_ref(*(c[x].float() for x in ("q", "k", "v", "do")), *rope, *c["win"], c["sm_scale"], windowed=True)
-    assert_close(got, want, cfg["dtype"], what="cfg5 geometry")
+    assert_close(got, want, cfg["dtype"], what=f"cfg5 geometry/{path}")
+
+
+@pytest.mark.parametrize("path", PATHS)
+def test_config5_full_size_against_oracle_on_cropped_bands(path):
+    """The largest configuration at its stated size (256 x 256 grid, d = 128, 31 x 31 window, RoPE on all 128 dims,
+    one (batch, head) slice) on the tensor-core kernels, compared with the oracle on three bands of grid rows (top
+    border, interior, bottom border).  The window is truncated at the border, not shifted
+    (src/tiled_swa.py:704-710), so the oracle evaluated on the rows [a - 30, b + 30) of the grid -- with the
+    tokens' own packed indices, so the RoPE angles are those of the full grid -- reproduces the full-grid O, dQ
+    (15 rows of reach) and dK, dV (15 more) of rows [a, b) exactly."""
+    cfg = CONFIGS["cfg5"]
+    G, half = cfg["grid"], (cfg["w"] - 1) // 2
+    c = make_case(cfg, B=1, H=1)
+    rope = (c["idx"], c["row_cs"], c["col_cs"])
+    assert swa.selected_impl(c["q"].to(DEV), c["v"].to(DEV), tuple(t.to(DEV) for t in rope), *c["win"], c["sm_scale"],
+                             which=2) == "tc"
+    got, _ = run_gpu(c["q"], c["k"], c["v"], c["do"], rope, c["win"], c["sm_scale"], path=path)
+    for a, b in ((0, 24), (116, 140), (G - 24, G)):
+        lo, hi = max(0, a - 2 * half), min(G, b + 2 * half)
+        rows = slice(lo * G, hi * G)
+        crop = [c[x][:, :, rows].float() for x in ("q", "k", "v", "do")]
+        want = orc.fused_ref(*crop, c["idx"][rows], c["row_cs"], c["col_cs"], 1, hi - lo, G, half, half, c["sm_scale"],
+                             windowed=True)
+        keep = slice((a - lo) * G, (b - lo) * G)
+        full = slice(a * G, b * G)
+        assert_close([t[:, :, full] for t in got], [t[:, :, keep] for t in want], cfg["dtype"],
+                     what=f"cfg5 rows [{a},{b})/{path}")
 
 
 def test_config5_full_grid_properties():
@@ -239,7 +293,7 @@ def test_config5_full_grid_properties():
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("grid,w", [((21, 21), 7), ((37, 19), 5), ((9, 50), 9)])
-def test_ragged_grids_tensor_core_path(grid, w, dtype):
+def test_ragged_grids_tensor_core_path(grid, w, dtype, path="fused"):
     """Grids that are no multiple of the resident tile in rows or columns (partly empty tiles, one-block
     items), RoPE with dropped tokens and tokens whose row or column half alone is -1, forward + backward
     on the tcgen05 kernels against the oracle."""
@@ -260,9 +314,10 @@ def test_ragged_grids_tensor_core_path(grid, w, dtype):
     win = (1, th, tw, half, half)
     rope = (idx, tab_r, tab_c)
     assert swa.selected_impl(q.to(DEV), v.to(DEV), tuple(t.to(DEV) for t in rope), *win, 0.125, which=1, impl="auto") == "tc"
-    got, _ = run_gpu(q, k, v, do, rope, win, 0.125, impl="tc")
     want = orc.fused_ref(q.float(), k.float(), v.float(), do.float(), *rope, *win, 0.125)
-    assert_close(got, want, dtype, what=f"ragged {grid}")
+    for path in PATHS:
+        got, _ = run_gpu(q, k, v, do, rope, win, 0.125, impl="tc", path=path)
+        assert_close(got, want, dtype, what=f"ragged {grid}/{path}")
 
 
 def test_random_shapes_tensor_core_vs_simt():
@@ -271,7 +326,7 @@ def test_random_shapes_tensor_core_vs_simt():
     tests pin to the oracle) to within the 16-bit rounding of the outputs; nothing may hang or be non-finite."""
     import random
     rnd = random.Random(3)
-    n_tc = 0
+    n_tc = n_oracle = 0
     for case in range(48):
         th, tw = rnd.choice([5, 9, 16, 23, 31, 40, 47]), rnd.choice([6, 8, 13, 16, 24, 33, 50])
         b = rnd.choice([1, 1, 1, 2, 4])
@@ -303,7 +358,18 @@ def test_random_shapes_tensor_core_vs_simt():
             assert torch.isfinite(c.float()).all(), f"{what} {n}: non-finite"
             err = (a.float() - c.float()).abs().max().item()
             assert err < 4e-2, f"{what} {n}: max abs {err:.3e}"
-    assert n_tc >= 30
+        if n_tc % 2 == 0 and N <= 3000:
+            # every second shape the tensor-core kernels take also goes to the oracle (windowed form of the same
+            # arithmetic), on both paths: d_qk != d_v with 32 rotated pairs, wr != wc up to 12 / 10, three heads
+            rope_cpu = (None, None, None) if rope is None else tuple(t.cpu() for t in rope)
+            want = orc.fused_ref(q.float().cpu(), k.float().cpu(), v.float().cpu(), do.float().cpu(), *rope_cpu, *win, sc,
+                                 windowed=True)
+            for path in (PATHS if rope is not None else PATHS[:1]):
+                got, _ = run_gpu(q.cpu(), k.cpu(), v.cpu(), do.cpu(), None if rope is None else rope_cpu, win, sc,
+                                 impl="tc", path=path)
+                assert_close(got, want, dtype, what=f"{what} vs oracle/{path}")
+                n_oracle += 1
+    assert n_tc >= 30 and n_oracle >= 12
 
 
 def test_host_pipeline_matches_direct_calls():
@@ -311,7 +377,8 @@ def test_host_pipeline_matches_direct_calls():
     from dl_templates_b200.host_pipeline import HostPipeline
     c = make_case(CONFIGS["cfg2"], B=1, H=7)
     rope = tuple(t.to(DEV) for t in (c["idx"], c["row_cs"], c["col_cs"]))
-    direct, _ = run_gpu(c["q"], c["k"], c["v"], c["do"], (c["idx"], c["row_cs"], c["col_cs"]), c["win"], c["sm_scale"])
+    direct, _ = run_gpu(c["q"], c["k"], c["v"], c["do"], (c["idx"], c["row_cs"], c["col_cs"]), c["win"], c["sm_scale"],
+                        path="handoff")
     host_in = [c[x].pin_memory() for x in ("q", "k", "v", "do")]
     outs = [torch.empty_like(c[x]).pin_memory() for x in ("v", "q", "k", "v")]
     pipe = HostPipeline(DEV, chunk_slices=2)
@@ -321,6 +388,65 @@ def test_host_pipeline_matches_direct_calls():
     swa.check_status()
     for got, want in zip(outs, direct):
         assert torch.equal(got.float(), want)
+
+
+def test_host_pipeline_back_to_back_runs_do_not_race():
+    """Two runs on DIFFERENT inputs with nothing between them but the enqueue order: the copies of the second run into
+    the staging buffers must wait for the kernels of the first run that still read them."""
+    from dl_templates_b200.host_pipeline import HostPipeline
+    c = make_case(CONFIGS["cfg2"], B=1, H=6)
+    rope_cpu = (c["idx"], c["row_cs"], c["col_cs"])
+    rope = tuple(t.to(DEV) for t in rope_cpu)
+    ins_a = [c[x] for x in ("q", "k", "v", "do")]
+    ins_b = [torch.roll(t, 1, dims=1) * 0.5 for t in ins_a]
+    want_a, _ = run_gpu(*ins_a[:3], ins_a[3], rope_cpu, c["win"], c["sm_scale"], path="handoff")
+    want_b, _ = run_gpu(*ins_b[:3], ins_b[3], rope_cpu, c["win"], c["sm_scale"], path="handoff")
+    host_a, host_b = ([t.pin_memory() for t in ins] for ins in (ins_a, ins_b))
+    outs_a, outs_b = ([torch.empty_like(c[x]).pin_memory() for x in ("v", "q", "k", "v")] for _ in range(2))
+    pipe = HostPipeline(DEV, chunk_slices=2, n_buffers=2)
+    for _ in range(3):
+        pipe.run(*host_a, outs_a, rope, c["win"], c["sm_scale"])
+        pipe.run(*host_b, outs_b, rope, c["win"], c["sm_scale"])
+    torch.cuda.synchronize()
+    swa.check_status()
+    for got, want in zip(outs_a + outs_b, want_a + want_b):
+        assert torch.equal(got.float(), want)
+
+
+def test_outputs_stay_inside_their_rows():
+    """Canary test: every output is a strided view into a poisoned buffer with guard rows either side and guard
+    columns after every row; ragged grids (partly empty tiles at the right and bottom edges) on both paths.  After
+    forward and backward the outputs match the oracle and every guard element still holds the poison."""
+    POISON = -1234.0
+    for (th, tw, w, dqk, dv, R) in ((21, 19, 7, 64, 64, 16), (9, 50, 9, 64, 128, 8), (37, 11, 5, 128, 64, 32)):
+        N = th * tw
+        q, k, v, do = orc.seeded_inputs(1, 2, N, dqk, dv, torch.bfloat16, 5)
+        idx = orc.encode_idx(th, tw)
+        rope_cpu = (idx, orc.make_cs_table(R, th), orc.make_cs_table(R, tw))
+        rope = tuple(t.to(DEV) for t in rope_cpu)
+        half = (w - 1) // 2
+        win, sc = (1, th, tw, half, half), dqk ** -0.5
+        want = orc.fused_ref(q.float(), k.float(), v.float(), do.float(), *rope_cpu, *win, sc)
+        qd, kd, vd, dod = (t.to(DEV) for t in (q, k, v, do))
+
+        def guarded(d):
+            buf = torch.full((1, 2, N + 16, d + 8), POISON, dtype=torch.bfloat16, device=DEV)
+            return buf, buf[:, :, 8:N + 8, :d]
+
+        for path in PATHS:
+            (bo, o), (bq, dq), (bk, dk), (bv, dv_) = guarded(dv), guarded(dqk), guarded(dqk), guarded(dv)
+            if path == "handoff":
+                _, lse, qr, kr = swa.swa_forward_rot(qd, kd, vd, rope, *win, sc, impl="tc", out=o)
+                swa.swa_backward_rot(qr, kr, vd, o, lse, dod, rope, *win, sc, impl="tc", out=(dq, dk, dv_))
+            else:
+                _, lse = swa.swa_forward(qd, kd, vd, rope, *win, sc, impl="tc", out=o)
+                swa.swa_backward(qd, kd, vd, o, lse, dod, rope, *win, sc, impl="tc", out=(dq, dk, dv_))
+            swa.check_status()
+            assert_close([t.float().cpu() for t in (o, dq, dk, dv_)], want, torch.bfloat16, what=f"canary {th}x{tw}/{path}")
+            for buf, view, d in ((bo, o, dv), (bq, dq, dqk), (bk, dk, dqk), (bv, dv_, dv)):
+                guard = buf.clone()
+                guard[:, :, 8:N + 8, :d] = POISON
+                assert bool((guard == POISON).all()), f"canary {th}x{tw}/{path}: a guard element was overwritten"
 
 
 @pytest.mark.parametrize("with_rope", [True, False])
@@ -386,15 +512,16 @@ def test_reference_selftest_shape_runs_on_tensor_cores():
     assert_close(got, simt, torch.float16, what="self-test shape vs simt")
 
 
-def test_prerotate_mode_matches_fused_mode():
-    """``set_rope_mode('prerotate')`` (stand-alone rotation of copies, attention without RoPE, gradients rotated
-    back) against the oracle and against the fused mode; q and k stay unmodified in both."""
+def test_rope_modes_agree():
+    """The three ways ``TiledSwaRope2D`` can apply the rotation (``set_rope_mode``: rotated copies handed from forward
+    to backward; every kernel rotating what it streams; the reference's own composition with separate passes)
+    against the oracle and against each other; q and k stay unmodified in all of them."""
     c = make_case(CONFIGS["cfg3"], B=1, H=2)
     rope = tuple(t.to(DEV) for t in (c["idx"], c["row_cs"], c["col_cs"]))
     want = orc.fused_ref(c["q"].float(), c["k"].float(), c["v"].float(), c["do"].float(), c["idx"], c["row_cs"],
                          c["col_cs"], *c["win"], c["sm_scale"])
     results = {}
-    for mode in ("prerotate", "fused", "auto"):
+    for mode in ("handoff", "prerotate", "fused"):
         prev = swa.set_rope_mode(mode)
         try:
             q, k, v = (c[n].to(DEV).requires_grad_(True) for n in ("q", "k", "v"))
@@ -407,6 +534,7 @@ def test_prerotate_mode_matches_fused_mode():
         results[mode] = [t.detach().float().cpu() for t in (o, q.grad, k.grad, v.grad)]
         assert_close(results[mode], want, c["q"].dtype, what=mode)
     assert_close(results["prerotate"], results["fused"], c["q"].dtype, what="prerotate vs fused")
+    assert_close(results["handoff"], results["fused"], c["q"].dtype, what="handoff vs fused")
 
 
 @pytest.mark.parametrize("bs,th,tw,rs,cs", [(16, 6, 6, 1, 2), (32, 4, 5, 2, 1), (8, 7, 9, 1, 5), (16, 5, 12, 0, 2)])
