@@ -3,16 +3,19 @@
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--workload target|cfg2..cfg5] [--impl ours|reference]
 
-One "step" is one pass of the hot path over one batch of synthetic input: the fused
-RoPE-2D forward kernel, then the delta, dQ and dK/dV kernels.  Every rank works
-on its own (batch, head) slices; there is no collective on the data path (weak
+One "step" is one pass of the hot path over one batch of synthetic input: forward with
+RoPE-2D (two streaming passes that rotate q and k once, then the attention kernel), then
+the delta, dQ and dK/dV kernels (which rotate dq and dk back in their epilogues).  Every
+rank works on its own (batch, head) slices; there is no collective on the data path (weak
 scaling: the per-GPU batch is fixed).  Rank 0 prints ONE JSON line.
 
   value     whole-job windowed TFLOP/s with the inputs already resident in HBM
   e2e       the same through the public Python surface with pinned HOST buffers:
             q, k, v, dO copied host->device and o, dq, dk, dv copied back every step
-  roofline  the dominant kernel (largest share of a step) against the measured
-            bf16 tensor peak, from CUDA events around its launches in the timed region
+  roofline  the dominant kernel (largest share of a step) against the measured burst
+            bf16 tensor peak (the sustained one beside it), from CUDA events around its
+            launches in the timed region; `traffic` from the tracked ncu capture
+            profiles/traffic.json when it covers this workload and kernel, else null
   cpu_baseline  the CPU oracle (the reference's dense-mask + SDPA form) on a bounded
             sample of the same workload, on this box's host cores
 
@@ -35,13 +38,16 @@ import torch
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# DRAM bytes (read + write) per launch and per (batch, head) slice, from one `ncu --set full` capture at
-# B*H = 64 (profiles/ncu_full_target_bh64_all_kernels.md); traffic grows in proportion to B*H.
-TRAFFIC_BYTES_PER_BH = {
-    "target:fwd": (402.9e6 + 118.2e6) / 64,
-    "target:dq": (545.9e6 + 118.9e6) / 64,
-    "target:dkdv": (545.5e6 + 237.3e6) / 64,
-}
+
+def load_traffic():
+    """DRAM bytes (read + write) per launch and per (batch, head) slice from the tracked ncu capture, keyed
+    "workload:mode:kernel"; traffic grows in proportion to B*H.  Absent file or key: no figure is reported."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    try:
+        with open(path) as f:
+            return json.load(f)
+    except (OSError, ValueError):
+        return {}
 
 METRIC = "2D-SWA fwd+bwd TFLOP/s (windowed FLOPs, whole job)"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
@@ -59,9 +65,18 @@ def load_peaks():
     return d
 
 
+def workloads_module():
+    """The configuration table, loaded by path: importing the package would load the CUDA library, which the
+    reference arm (CPU only) has no business doing."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("swa2d_workloads", os.path.join(ROOT, "dl_templates_b200", "workloads.py"))
+    m = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(m)
+    return m
+
+
 def workload_dims(name):
-    from dl_templates_b200.workloads import CONFIGS
-    cfg = dict(CONFIGS[name])
+    cfg = dict(workloads_module().CONFIGS[name])
     cfg["name"] = name
     return cfg
 
@@ -166,9 +181,19 @@ def cpu_sample_step(case, cfg, n_slices):
 
 
 def cpu_case(cfg, n_slices):
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
-    from swa_cases import make_case     # seeded CPU inputs shared with the parity tests (imports the oracle)
-    return make_case(cfg, B=1, H=n_slices)
+    """Seeded CPU inputs of `n_slices` (batch, head) slices, built like the parity tests build theirs."""
+    from oracle import swa_oracle as orc
+    G = cfg["grid"]
+    N = G * G
+    q, k, v, do = orc.seeded_inputs(1, n_slices, N, cfg["d_qk"], cfg["d_v"], cfg["dtype"], 0)
+    idx = orc.encode_idx(G, G)
+    if cfg["drop"] > 0:
+        g = torch.Generator().manual_seed(1000)
+        idx[torch.bernoulli(torch.full((N,), cfg["drop"]), generator=g).bool()] = -1
+    tab = orc.make_cs_table(cfg["rope_dims"] // 4, G, 10000.0)
+    half = (cfg["w"] - 1) // 2
+    return dict(q=q, k=k, v=v, do=do, idx=idx, row_cs=tab, col_cs=tab.clone(), win=(1, G, G, half, half),
+                sm_scale=cfg["d_qk"] ** -0.5)
 
 
 def cpu_slices_for(cfg):
@@ -178,7 +203,7 @@ def cpu_slices_for(cfg):
 
 
 def run_cpu_reference(cfg, steps, warmup):
-    from dl_templates_b200.workloads import windowed_flops
+    windowed_flops = workloads_module().windowed_flops
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     n_slices = cpu_slices_for(cfg)
@@ -201,14 +226,19 @@ def run_cpu_reference(cfg, steps, warmup):
 # --------------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------------
-def device_case(cfg, bh_local, device, seed):
-    """Rank-local synthetic inputs [1, bh_local, N, d] drawn on the device."""
+def device_case(cfg, bh_local, device, seed, first_slice=0):
+    """Rank-local synthetic inputs [1, bh_local, N, d] drawn on the device.  Every (batch, head) slice has its own
+    generator, seeded by (seed, slice), so any slice of any rank can be redrawn alone (the verification leg does)."""
     import dl_templates_b200 as swa
     G = cfg["grid"]
     N = G * G
-    g = torch.Generator(device=device).manual_seed(seed)
-    mk = lambda d: torch.randn((1, bh_local, N, d), generator=g, device=device, dtype=torch.float32).to(cfg["dtype"])
-    q, k, v, do = mk(cfg["d_qk"]), mk(cfg["d_qk"]), mk(cfg["d_v"]), mk(cfg["d_v"])
+    q, k = (torch.empty((1, bh_local, N, cfg["d_qk"]), dtype=cfg["dtype"], device=device) for _ in range(2))
+    v, do = (torch.empty((1, bh_local, N, cfg["d_v"]), dtype=cfg["dtype"], device=device) for _ in range(2))
+    g = torch.Generator(device=device)
+    for s_ in range(bh_local):
+        g.manual_seed(1_000_003 * seed + first_slice + s_)
+        for t in (q, k, v, do):
+            t[0, s_].copy_(torch.randn((N, t.shape[-1]), generator=g, device=device, dtype=torch.float32))
     R = cfg["rope_dims"] // 4
     idx = swa.FusedInplaceRotaryPositionEncoding2D.encode_idx(G, G)
     if cfg["drop"] > 0:
@@ -245,7 +275,11 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-variants", action="store_true", help="skip the un-fused composition leg after the timed region")
     ap.add_argument("--e2e-chunk", type=int, default=32, help="(batch*head) slices per pipelined chunk of the e2e path")
-    ap.add_argument("--verify", action="store_true", help="gather outputs over NCCL and compare rank slices")
+    ap.add_argument("--verify", action="store_true", help="(default with more than one GPU) rank 0 recomputes every "
+                    "rank's first slice from that rank's seed and compares it bitwise with the slice gathered over NCCL")
+    ap.add_argument("--no-verify", action="store_true")
+    ap.add_argument("--no-strong", action="store_true", help="skip the strong-scaling leg (the largest configuration, "
+                    "256 (batch, head) slices split over the GPUs) that runs after the timed region of the target workload")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -281,7 +315,7 @@ def main():
         raise SystemExit("bench.py needs a CUDA device (sm_100a); there is no CPU fallback")
     import dl_templates_b200 as swa
     from dl_templates_b200 import _lib
-    from dl_templates_b200.workloads import windowed_flops
+    windowed_flops = workloads_module().windowed_flops
 
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
@@ -369,6 +403,9 @@ def main():
     ms_step = t.item() / args.steps
     value = step_flops * world / (ms_step * 1e-3) / 1e12
 
+    families = {n: swa.selected_impl(q, v, rope, *win, sm, which=w_, impl=impl)
+                for n, w_ in (("fwd", 0), ("dq", 1), ("dkdv", 2))}
+
     # ---------------------------------------------------------------- e2e with host buffers
     e2e = None
     if not args.no_e2e:
@@ -397,10 +434,19 @@ def main():
         if world > 1:
             dist.all_reduce(te, op=dist.ReduceOp.MAX)
         ms_e2e = te.item() / e2e_steps
+        # what the link itself allows: the same buffers copied both ways at once, all ranks together
+        barrier()
+        tc_ = torch.tensor([copy_ceiling_ms(host_in[:4 if cfg["bwd"] else 3], host_out[:n_out], device)], device=device,
+                           dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(tc_, op=dist.ReduceOp.MAX)
         e2e = {"value": step_flops * world / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
                "h2d_bytes_per_step": sum(x.numel() * x.element_size() for x in host_in),
                "d2h_bytes_per_step": sum(x.numel() * x.element_size() for x in host_out[:n_out]),
-               "ms_per_step": ms_e2e, "steps": e2e_steps, "host_cpus_near_gpu": near_cpus}
+               "ms_per_step": ms_e2e, "steps": e2e_steps, "host_cpus_near_gpu": near_cpus,
+               "copy_ceiling_ms": tc_.item(),
+               "copy_ceiling_note": "plain concurrent H2D + D2H copies of the same pinned buffers by all ranks at once "
+                                    "(max over ranks): the floor of ms_per_step on this host"}
         del host_in, host_out, pipe
 
     # ---------------------------------------------------------------- the un-fused composition, for comparison
@@ -441,12 +487,57 @@ def main():
         swa.check_status()
 
     # ---------------------------------------------------------------- optional verification gather
+    # Sharded == unsharded, bitwise: every rank contributes the outputs of its FIRST (batch, head) slice; rank 0
+    # regenerates that slice from the rank's seed, runs it alone on its own GPU and compares bit for bit.
     verified = None
-    if args.verify and world > 1:
-        from dl_templates_b200.sharding import gather_bh
-        o = step()[0]
-        full = gather_bh(o.float().sum(dim=(2, 3), keepdim=True), bh_local * world)
-        verified = bool(torch.isfinite(full).all().item())
+    if world > 1 and not args.no_verify:
+        outs = step()
+        mine = torch.cat([t[:, :1].reshape(-1).view(torch.int16 if t.element_size() == 2 else torch.int32).to(torch.int32)
+                          for t in outs])
+        gathered = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(gathered, mine)
+        if rank == 0:
+            verified = True
+            for r in range(world):
+                cr = device_case(cfg, 1, device, seed=r)      # slice 0 of rank r, redrawn from its own seed
+                ref = run_step(swa, cr, impl, handoff, cfg["bwd"])
+                flat = torch.cat([t.reshape(-1).view(torch.int16 if t.element_size() == 2 else torch.int32).to(torch.int32)
+                                  for t in ref])
+                verified = verified and bool(torch.equal(flat, gathered[r]))
+
+    # ---------------------------------------------------------------- strong scaling of the largest configuration
+    # 256 (batch, head) slices of the 256 x 256 / d = 128 / 31 x 31 problem split over the GPUs of the job (the split
+    # the specification names); runs after the timed region of the default workload, device-timed, max over ranks.
+    strong = None
+    if args.workload == "target" and args.layout == "bhnd" and args.rope_dims < 0 and not args.no_strong and not args.bh_per_gpu:
+        del q, k, v, do, c
+        torch.cuda.empty_cache()
+        big = workload_dims("cfg5")
+        total = big["B"] * big["H"]
+        if total % world == 0:
+            per = total // world
+            cb = device_case(big, per, device, seed=0, first_slice=rank * per)
+            for _ in range(2):
+                run_step(swa, cb, impl, True)
+            barrier()
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            n_strong = 3
+            s0.record(stream)
+            for _ in range(n_strong):
+                run_step(swa, cb, impl, True)
+            s1.record(stream)
+            barrier()
+            ts_ = torch.tensor([s0.elapsed_time(s1)], device=device, dtype=torch.float64)
+            if world > 1:
+                dist.all_reduce(ts_, op=dist.ReduceOp.MAX)
+            ms_s = ts_.item() / n_strong
+            hb = (big["w"] - 1) // 2
+            ff, fb = windowed_flops(total, big["grid"] ** 2, 1, hb, hb, big["d_qk"], big["d_v"])
+            strong = {"workload": "cfg5: 256x256 grid, 31x31 window, d=128, RoPE on 128 dims, fwd+bwd, 256 (batch, head) "
+                                  "slices in total", "scaling": "strong", "bh_per_gpu": per, "ms_per_step": ms_s,
+                      "value": (ff + fb) / (ms_s * 1e-3) / 1e12, "unit": "TFLOP/s", "steps": n_strong}
+            swa.check_status()
+            del cb
 
     if world > 1:
         dist.barrier()
@@ -466,15 +557,20 @@ def main():
     if dom == "delta":
         dom = max((n for n in med if n != "delta"), key=med.get)
     achieved = alg[dom] / (med[dom] * 1e-3) / 1e12
-    peak = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
-    per_bh = TRAFFIC_BYTES_PER_BH.get(f"{args.workload}:{dom}") if args.rope_dims < 0 else None
-    traffic = per_bh * bh_local if per_bh else None
+    # the timed region is a fraction of a second at full clock: the burst figure is the comparator
+    peak = peaks["bf16_tflops"]
+    sustained = peaks.get("bf16_tflops_sustained")
+    mode = "handoff" if handoff else ("fused" if rope is not None else "norope")
+    tr = load_traffic().get(f"{args.workload}:{mode}:{dom}") if args.rope_dims < 0 and args.layout == "bhnd" else None
+    traffic = tr["bytes_per_bh"] * bh_local if tr else None
     roofline = {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak, "traffic": traffic, "peak_source": peaks["_source"] + " (sustained bf16)",
+                "frac": achieved / peak, "traffic": traffic,
+                "traffic_source": (tr.get("source") if tr else None),
+                "peak_source": peaks["_source"] + " (burst bf16)",
+                "frac_of_sustained": (achieved / sustained) if sustained else None, "peak_sustained": sustained,
                 "kernel_ms": med,
                 "kernel_share": {n: med[n] / sum(med.values()) for n in med},
-                "kernel_family": {n: swa.selected_impl(q, v, rope, *win, sm, which=w_, impl=impl)
-                                  for n, w_ in (("fwd", 0), ("dq", 1), ("dkdv", 2))}}
+                "kernel_family": families}
 
     cpu_baseline = None
     if world == 1 and not args.no_cpu_baseline:
@@ -492,14 +588,58 @@ def main():
         "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": int(launches),
         "clocks": clocks,
     }
+    line["config"]["rope_mode"] = ("handoff: q and k rotated once by streaming passes, rotated copies handed to the "
+                                   "backward kernels, dq / dk rotated back in their epilogues") if handoff else \
+        ("fused: every kernel rotates the rows it streams" if rope is not None else "no RoPE")
     if prerot is not None:
         line["unfused_composition"] = prerot
+    if strong is not None:
+        line["strong_scaling_cfg5"] = strong
     if verified is not None:
-        line["verified_gather"] = verified
+        line["verified_sharded_equals_unsharded_bitwise"] = verified
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
     return 0
+
+
+def run_step(swa, c, impl, handoff, bwd=True):
+    """One forward (+ backward) on the tensors of `c` through the public Python surface; returns the outputs."""
+    q, k, v, do, rope, win, sm = c["q"], c["k"], c["v"], c["do"], c["rope"], c["win"], c["sm_scale"]
+    if rope is not None and handoff:
+        o, lse, qr, kr = swa.swa_forward_rot(q, k, v, rope, *win, sm, impl=impl)
+        return (o,) + (tuple(swa.swa_backward_rot(qr, kr, v, o, lse, do, rope, *win, sm, impl=impl)) if bwd else ())
+    o, lse = swa.swa_forward(q, k, v, rope, *win, sm, impl=impl)
+    return (o,) + (tuple(swa.swa_backward(q, k, v, o, lse, do, rope, *win, sm, impl=impl)) if bwd else ())
+
+
+def copy_ceiling_ms(host_in, host_out, device, repeats=3):
+    """Plain copies of the end-to-end leg's own pinned buffers, host->device and device->host at the same time on two
+    streams (one cudaMemcpyAsync per tensor): the time no pipeline over this link can beat."""
+    s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+    dev_in = [torch.empty_like(h, device=device) for h in host_in]
+    dev_out = [torch.empty_like(h, device=device) for h in host_out]
+    torch.cuda.synchronize(device)
+    best = None
+    for _ in range(repeats + 1):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        cur = torch.cuda.current_stream(device)
+        a.record(cur)
+        s_in.wait_event(a)
+        s_out.wait_event(a)
+        with torch.cuda.stream(s_in):
+            for d, h in zip(dev_in, host_in):
+                d.copy_(h, non_blocking=True)
+        with torch.cuda.stream(s_out):
+            for d, h in zip(dev_out, host_out):
+                h.copy_(d, non_blocking=True)
+        cur.wait_stream(s_in)
+        cur.wait_stream(s_out)
+        b.record(cur)
+        torch.cuda.synchronize(device)
+        t = a.elapsed_time(b)
+        best = t if best is None else min(best, t)
+    return best
 
 
 def swa_backward_timed(swa, _lib, q, k, v, o, lse, do, rope, win, sm, impl, ev, stream, outs=None, handoff=False):

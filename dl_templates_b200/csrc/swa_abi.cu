@@ -100,8 +100,9 @@ int swa_select_impl(const swa_geom_t* g, const swa_rope_t* rope, int32_t which) 
 int swa_describe_plan(const swa_geom_t* g, const swa_rope_t* rope, int32_t which, int32_t* out) {
   if (int e = check_geom(g)) return e;
   if (int e = check_rope(g, rope)) return e;
-  if (!out || which < 0 || which > 2) return fail(E_NULL, "swa_describe_plan: out is NULL or `which` not in 0..2");
-  if (swa::tc::unsupported_reason(g, rope, nullptr, 0, which) != nullptr || !swa::tc::describe_plan(g, rope, which, out))
+  if (!out || which < 0 || which > 5) return fail(E_NULL, "swa_describe_plan: out is NULL or `which` not in 0..5");
+  if (which >= 3 && !(rope && rope->idx)) return fail(E_ROPE, "swa_describe_plan: kernels 3..5 are the RoPE hand-off entries");
+  if (swa::tc::unsupported_reason(g, rope, nullptr, 0, which % 3, which >= 3) != nullptr || !swa::tc::describe_plan(g, rope, which, out))
     return fail(E_SHAPE, "the tensor-core kernels do not take this shape");
   return 0;
 }

@@ -97,7 +97,10 @@ int halo_width(const swa_geom_t* g, int TW) {
 //   tensor memory (512 columns): forward  score buffers at 128-column strides (packed when they do not fit) + two O accumulators;
 //                                backward nsb pairs (S, dP) of 2N columns + the accumulators
 //   shared memory:               nxb resident-tile buffers + indicator rows + stages x (block + penalty rows [+ lse, delta])
-bool make_plan_shape(const swa_geom_t* g, int which, int TH, int TW, uint32_t tab_bytes, Plan* out, long* cost_out = nullptr) {
+// `v2`: the plan is for the kernels without streamed rotation (swa_tc_fwd2.cuh / swa_tc_bwd2.cuh), whose shared-memory
+// block behind the ring differs: no fixed-size penalty tables (they are sized per plan), two more lse / delta slots.
+bool make_plan_shape(const swa_geom_t* g, int which, int TH, int TW, uint32_t tab_bytes, Plan* out, long* cost_out = nullptr,
+                     bool v2 = false) {
   Plan pl;
   pl.tab_bytes = tab_bytes;
   pl.TH = TH;
@@ -112,8 +115,11 @@ bool make_plan_shape(const swa_geom_t* g, int which, int TH, int TW, uint32_t ta
   const int acc_cols = which == 0 ? 0 : (which == 1 ? 64 * qch : 64 * (qch + vch));
   const int min_stages = 3;
   // alignment pad of the swizzled tiles + the kernel's barrier / exchange / penalty-table block behind the ring
-  // (the kernels without streamed rotation have a few more barriers, and two more lse / delta slots in backward)
-  const uint32_t kSmemSlack = 1024u + (((which == 0 ? (uint32_t)sizeof(FwdShared) + 128u : (uint32_t)sizeof(BwdShared) + 64u + 2048u) + 15u) & ~15u);
+  const uint32_t slack_v1 = 1024u + (((which == 0 ? (uint32_t)sizeof(FwdShared) : (uint32_t)sizeof(BwdShared)) + 15u) & ~15u);
+  const uint32_t slack_v2 = 1024u + (((which == 0 ? (uint32_t)sizeof(Fwd2Shared) : (uint32_t)sizeof(Bwd2Shared)) + 15u) & ~15u) +
+                            (which == 0 ? 0u : 2048u);
+  // per candidate block shape: the v2 kernels' penalty tables take (halo rows + KR + KW) entries of 32 bytes
+  auto slack_for = [&](int KR, int KW) { return v2 ? slack_v2 + (uint32_t)(halo_rows + KR + KW) * 32u : slack_v1; };
   {
     // backward: two (S, dP) pairs of 2N columns next to the accumulators (N = 64 always fits: 256 + 256 columns)
     const int nsb = 2;
@@ -127,7 +133,7 @@ bool make_plan_shape(const swa_geom_t* g, int which, int TH, int TW, uint32_t ta
         for (int KR = 1; KR <= 16; ++KR) {
           const int N = KW * KR;
           if (N > nmax || N % 16) continue;
-          if (fixed + min_stages * ((uint32_t)N * row_bytes + stage_extra) + kSmemSlack > kSmemLimit) continue;
+          if (fixed + min_stages * ((uint32_t)N * row_bytes + stage_extra) + slack_for(KR, KW) > kSmemLimit) continue;
           const long nblk = (halo_rows + KR - 1) / KR;
           const long cost = nblk * N * 16 + nblk * 400;  // executed columns + a per-block overhead
           if (best_cost < 0 || cost < best_cost) {
@@ -142,6 +148,9 @@ bool make_plan_shape(const swa_geom_t* g, int which, int TH, int TW, uint32_t ta
         pl.N = pl.KR * pl.KW;
       }
       const uint32_t stage = (uint32_t)pl.N * row_bytes + stage_extra;
+      const uint32_t kSmemSlack = slack_for(pl.KR, pl.KW);
+      pl.pen_rows = halo_rows + pl.KR;
+      pl.pen_cols = pl.KW;
       const int Wtok = g->t_width * g->b_size;
       pl.n_tiles_x = (Wtok + pl.TW - 1) / pl.TW;
       pl.n_tiles_y = (g->t_height + pl.TH - 1) / pl.TH;
@@ -180,18 +189,19 @@ uint32_t rope_table_bytes(const swa_rope_t* rope) {
 }
 
 // Tile shape for one choice of staged-table bytes; *cost = the planner's block cost of the plan taken.
-static bool make_plan_tab(const swa_geom_t* g, const swa_rope_t* rope, int which, uint32_t tab, Plan* out, long* cost) {
+static bool make_plan_tab(const swa_geom_t* g, const swa_rope_t* rope, int which, uint32_t tab, Plan* out, long* cost,
+                          bool v2 = false) {
   const char* th_names[3] = {"SWA_TC_TH_FWD", "SWA_TC_TH_DQ", "SWA_TC_TH_DKDV"};
   const int th = env_int(th_names[which], env_int("SWA_TC_TH", 0));
-  if (th == 8) return make_plan_shape(g, which, 8, 16, tab, out, cost);
-  if (th == 16) return make_plan_shape(g, which, 16, 8, tab, out, cost);
+  if (th == 8) return make_plan_shape(g, which, 8, 16, tab, out, cost, v2);
+  if (th == 16) return make_plan_shape(g, which, 16, 8, tab, out, cost, v2);
   if (which == 2) {
     // dK/dV (K tile resident, Q blocks streamed; its accumulators leave the narrowest blocks): the shape whose
     // blocks cost less by the planner's own measure -- 16 x 8 at the 13 x 13 window with d = 64, 8 x 16 once
     // d_v = 128 or the window grows (measured: 10 % and 13 % faster at 15 x 15 / d_v = 128 and 31 x 31 / d = 128)
     Plan a, b;
     long ca = 0, cb = 0;
-    const bool oa = make_plan_shape(g, which, 16, 8, tab, &a, &ca), ob = make_plan_shape(g, which, 8, 16, tab, &b, &cb);
+    const bool oa = make_plan_shape(g, which, 16, 8, tab, &a, &ca, v2), ob = make_plan_shape(g, which, 8, 16, tab, &b, &cb, v2);
     if (!oa && !ob) return false;
     const bool take_a = oa && (!ob || ca <= cb);
     *out = take_a ? a : b;
@@ -203,8 +213,8 @@ static bool make_plan_tab(const swa_geom_t* g, const swa_rope_t* rope, int which
   // ... and for the dQ kernel also when at most 32 of 64 q/k dims are rotated (measured 12 % faster at d_v = 128
   // with a 15 x 15 window and 3 % at the 13 x 13 window; at d_qk = 128 the 16 x 8 tile stays 27 % ahead)
   const bool wide_first = !(rope && rope->idx) || (which == 1 && rope->n_rdim <= 8 && g->d_qk == 64);
-  return wide_first ? (make_plan_shape(g, which, 8, 16, tab, out, cost) || make_plan_shape(g, which, 16, 8, tab, out, cost))
-                    : (make_plan_shape(g, which, 16, 8, tab, out, cost) || make_plan_shape(g, which, 8, 16, tab, out, cost));
+  return wide_first ? (make_plan_shape(g, which, 8, 16, tab, out, cost, v2) || make_plan_shape(g, which, 16, 8, tab, out, cost, v2))
+                    : (make_plan_shape(g, which, 16, 8, tab, out, cost, v2) || make_plan_shape(g, which, 8, 16, tab, out, cost, v2));
 }
 
 // The cos/sin tables are staged in shared memory when that does not cost block size: a plan with the tables is
@@ -230,8 +240,8 @@ bool make_plan_prerot(const swa_geom_t* g, const swa_rope_t* rope, int which, Pl
   const uint32_t tab = rope_table_bytes(rope);
   Plan with, without;
   long cw = 0, cn = 0;
-  const bool ok_n = make_plan_tab(g, nullptr, which, 0, &without, &cn);
-  if (ok_n && tab && make_plan_tab(g, nullptr, which, tab, &with, &cw) && cw <= cn && with.stages >= without.stages &&
+  const bool ok_n = make_plan_tab(g, nullptr, which, 0, &without, &cn, true);
+  if (ok_n && tab && make_plan_tab(g, nullptr, which, tab, &with, &cw, true) && cw <= cn && with.stages >= without.stages &&
       with.TH == without.TH) {
     *out = with;
     return true;
@@ -296,7 +306,8 @@ const char* unsupported_reason(const swa_geom_t* g, const swa_rope_t* rope, cons
   if (g->row_size > 64) return "row window too tall for the penalty tables";
   if ((int64_t)g->t_height * g->t_width * g->b_size > (1 << 30)) return "grid too large";
   Plan pl;
-  if (!(prerotated ? make_plan_prerot(g, which == 0 ? nullptr : rope, which, &pl) : make_plan(g, rope, which, &pl)))
+  const bool v2 = prerotated || !(rope && rope->idx);
+  if (!(v2 ? make_plan_prerot(g, which == 0 ? nullptr : rope, which, &pl) : make_plan(g, rope, which, &pl)))
     return "no tile plan fits (window too wide for one streamed block)";
   for (int i = 0; i < n_tensors; ++i)
     if (!tensor_ok(tensors[i])) return "tensors need unit last stride and 16-byte aligned rows";
@@ -304,24 +315,30 @@ const char* unsupported_reason(const swa_geom_t* g, const swa_rope_t* rope, cons
 }
 
 bool describe_plan(const swa_geom_t* g, const swa_rope_t* rope, int which, int32_t* out) {
+  // which 0..2: the kernel swa_fwd / swa_bwd_dq / swa_bwd_dkdv would run; 3..5: swa_fwd_rot / swa_bwd_dq_rot /
+  // swa_bwd_dkdv_rot.  Without RoPE, and for 3..5, these are the kernels without streamed rotation.
+  const bool prerot = which >= 3;
+  const int kind = which % 3;
+  const bool v2 = prerot || !(rope && rope->idx);
   Plan pl;
-  if (!make_plan(g, rope, which, &pl)) return false;
+  if (!(v2 ? make_plan_prerot(g, kind == 0 ? nullptr : rope, kind, &pl) : make_plan(g, rope, kind, &pl))) return false;
   const uint32_t qch = g->d_qk / 64, vch = g->d_v / 64, N = pl.N;
+  const uint32_t pen = v2 ? (uint32_t)(pl.pen_rows + pl.pen_cols) * 32u : 0u;   // v1: inside the kernels' shared block
   uint32_t used = 1023, tmem = 0;   // worst-case pad to the 1024-byte alignment of the swizzled tiles
-  if (which == 0) {
+  if (kind == 0) {
     used += 2 * qch * 16384u + 128u * kXRowBytes + pl.stages * N * ((qch + vch) * 128u + kXRowBytes);
-    used += ((uint32_t)sizeof(FwdShared) + 128u + 15u) & ~15u;   // the larger of the two forward kernels' blocks
+    used += (((v2 ? (uint32_t)sizeof(Fwd2Shared) : (uint32_t)sizeof(FwdShared)) + 15u) & ~15u) + pen;
     const uint32_t o_cols = vch * 64u;
     const uint32_t stride = (N <= 128u && pl.nsb * 128u + 2 * o_cols <= 512u) ? 128u : N;
     tmem = pl.nsb * stride + 2 * o_cols;
     if (stride < N) tmem = 1u << 30;   // a score buffer would not hold a block
   } else {
     used += pl.nxb * (qch + vch) * 16384u + 128u * kXRowBytes + pl.stages * (N * ((qch + vch) * 128u + kXRowBytes) + 1024u);
-    used += ((uint32_t)sizeof(BwdShared) + 64u + 2048u + 15u) & ~15u;   // the larger of the two backward kernels' blocks
-    tmem = 2 * 2 * N + 64u * qch + (which == 2 ? 64u * vch : 0u);
+    used += (((v2 ? (uint32_t)sizeof(Bwd2Shared) : (uint32_t)sizeof(BwdShared)) + 15u) & ~15u) + pen + (v2 ? 2048u : 0u);
+    tmem = 2 * 2 * N + 64u * qch + (kind == 2 ? 64u * vch : 0u);
   }
   used += pl.tab_bytes;
-  const int32_t v[12] = {pl.TH, pl.TW, pl.KR, pl.KW, pl.N, pl.stages, which == 0 ? pl.nsb : 2, which == 0 ? 2 : pl.nxb,
+  const int32_t v[12] = {pl.TH, pl.TW, pl.KR, pl.KW, pl.N, pl.stages, kind == 0 ? pl.nsb : 2, kind == 0 ? 2 : pl.nxb,
                          (int32_t)pl.tab_bytes, (int32_t)pl.smem_bytes, (int32_t)used, (int32_t)tmem};
   for (int i = 0; i < 12; ++i) out[i] = v[i];
   return true;
@@ -373,7 +390,7 @@ int launch_fwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* 
 int launch_fwd2(const swa_geom_t* g, const swa_tensor_t* q, const swa_tensor_t* k, const swa_tensor_t* v,
                 const swa_tensor_t* o, float* lse, int32_t* status, cudaStream_t st) {
   Plan pl;
-  if (!make_plan(g, nullptr, 0, &pl)) {      // nothing is rotated: the plan of the problem without RoPE
+  if (!make_plan_prerot(g, nullptr, 0, &pl)) {      // nothing is rotated: the plan of the problem without RoPE
     snprintf(g_tc_err, sizeof(g_tc_err), "no tile plan");
     return -1;
   }
@@ -406,7 +423,8 @@ int launch_bwd(const swa_geom_t* g, const swa_rope_t* rope, bool prerotated, con
                const swa_tensor_t* yqk, const swa_tensor_t* yv, const float* lse, const float* delta,
                const swa_tensor_t* out_qk, const swa_tensor_t* out_v, int32_t* status, cudaStream_t st) {
   Plan pl;
-  if (!(prerotated ? make_plan_prerot(g, rope, DKDV ? 2 : 1, &pl) : make_plan(g, rope, DKDV ? 2 : 1, &pl))) {
+  const bool v2 = prerotated || !(rope && rope->idx);      // the kernels without streamed rotation
+  if (!(v2 ? make_plan_prerot(g, rope, DKDV ? 2 : 1, &pl) : make_plan(g, rope, DKDV ? 2 : 1, &pl))) {
     snprintf(g_tc_err, sizeof(g_tc_err), "no tile plan");
     return -1;
   }

@@ -32,12 +32,10 @@ struct Bwd2Shared {
   uint64_t x_full[2], x_empty[2];
   uint64_t y_full[kMaxStages], y_ready[kMaxStages], y_empty[kMaxStages], yx_free[kMaxStages];
   uint64_t sd_full[2], ds_full[2], pair_free[2], acc_full, acc_free;
-  PenaltyTables pen;
   uint32_t tmem_base;
   int abort_flag;
   int abort_site;
 };
-static_assert(sizeof(Bwd2Shared) <= sizeof(BwdShared) + 64, "the planner sizes shared memory with BwdShared + 64");
 
 // Inverse rotation of one segment (R pairs (i, i + R)) of a row held in registers; `pos` is the token's
 // row of the cos/sin table (negative: not rotated).
@@ -109,7 +107,12 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
   float* vec_smem = reinterpret_cast<float*>(yx_smem + pl.stages * yx_stage);
   const int vslots = pl.stages + 2;
   Bwd2Shared* sh = reinterpret_cast<Bwd2Shared*>(reinterpret_cast<uint8_t*>(vec_smem) + vslots * 1024);
-  uint8_t* tab_smem = reinterpret_cast<uint8_t*>(sh) + ((sizeof(BwdShared) + 64 + 15) & ~size_t(15));   // cos/sin tables (TABS)
+  PenView pen;                                                   // window-mask penalty parts of the current item's halo
+  pen.row = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(sh) + ((sizeof(Bwd2Shared) + 15) & ~size_t(15)));
+  pen.col = pen.row + 2 * pl.pen_rows;
+  pen.n_rows = pl.pen_rows;
+  pen.n_cols = pl.pen_cols;
+  uint8_t* tab_smem = reinterpret_cast<uint8_t*>(pen.col + 2 * pl.pen_cols);   // cos/sin tables (TABS)
   volatile int* abort_flag = &sh->abort_flag;
   // tensor memory: buffer pair b = (S at 2N b, dP at 2N b + N), accumulators behind the pairs
   const uint32_t acc_qk = nsb * 2 * N, acc_v = acc_qk + p.qch * 64;
@@ -557,7 +560,7 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
         if (sig != pen_sig) {
           pen_sig = sig;
           named_bar_sync(5, 128);           // nobody still reads the previous tables
-          build_penalty_tables<BF16>(&sh->pen, t, p, tp, 128);
+          build_penalty_view<BF16>(pen, t, p, tp, 128);
           named_bar_sync(5, 128);
         }
       }
@@ -583,7 +586,7 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
         trace_ev(p, 4, tn, t == 0 && it >= p.trace_it, 1 * 16 + (j & 15));
         if (ok) {
           if (row_on) {
-            write_penalty_row(yx_smem + stage * yx_stage, t, 0, 1, &sh->pen, j * pl.KR + jr, jc, pl.TH >> 3, pl.TW >> 3);
+            write_penalty_row_v(yx_smem + stage * yx_stage, t, pen, j * pl.KR + jr, jc, pl.TH >> 3, pl.TW >> 3);
             if constexpr (DKDV) {
               vec_smem[vslot * 256 + t] = a0;
               vec_smem[vslot * 256 + 128 + t] = b0;

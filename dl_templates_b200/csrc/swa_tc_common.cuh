@@ -31,6 +31,7 @@ struct Plan {
   int n_tiles_x, n_tiles_y;
   int stages;          // streamed-block pipeline depth
   int nsb, nxb;        // backward: (S, dP) buffer pairs in tensor memory, resident-tile buffers in shared memory
+  int pen_rows, pen_cols;  // entries of the window-mask penalty tables the kernels without streamed rotation keep
   uint32_t tab_bytes;  // cos/sin tables staged in shared memory (0: read from global memory)
   uint32_t smem_bytes;
 };
@@ -179,11 +180,57 @@ __device__ __forceinline__ void build_penalty_tables(PenaltyTables* tab, int t, 
   }
 }
 
+// The same tables sized for the plan at hand (halo rows of one item, columns of one streamed block) instead of
+// for the largest window the kernels accept: 1.7 KB instead of 9 KB at a 13 x 13 window, which is what lets the
+// kernels that use them keep one more stage of the block ring.  Entry i of `row` / `col` = two 16-byte units.
+struct PenView {
+  uint4* row;          // [pen_rows][2]
+  uint4* col;          // [pen_cols][2]
+  int n_rows, n_cols;
+};
+
+template <bool BF16>
+__device__ __forceinline__ void build_penalty_view(const PenView& pv, int t, const KParams& p, const TilePos& tp, int nthreads) {
+  const float nb = -p.mask_b;
+#pragma unroll 1
+  for (int hr = t; hr < pv.n_rows; hr += nthreads) {
+    const int yr = tp.hr_first + hr;
+    const bool in = yr <= tp.hr_last;
+    const int lo = in ? yr - p.wr - tp.r0 : 1, hi = in ? yr + p.wr - tp.r0 : 0;
+    pv.row[2 * hr] = penalty_unit<BF16>(lo, hi, nb);
+    pv.row[2 * hr + 1] = penalty_unit<BF16>(lo - 8, hi - 8, nb);
+  }
+#pragma unroll 1
+  for (int jc = t; jc < pv.n_cols; jc += nthreads) {
+    const int yx = tp.hx0 + jc;
+    const bool in = yx >= 0 && yx < p.Wtok;
+    int lo = 1, hi = 0;
+    if (in) {
+      const int yc = yx / p.b;
+      lo = (yc - p.wc) * p.b - tp.x0;
+      hi = (yc + p.wc + 1) * p.b - tp.x0 - 1;
+    }
+    pv.col[2 * jc] = penalty_unit<BF16>(lo, hi, nb);
+    pv.col[2 * jc + 1] = penalty_unit<BF16>(lo - 8, hi - 8, nb);
+  }
+}
+
+// Whole penalty row (four 16-byte units) of the streamed token at halo row `hr` / block column `jc`.
+__device__ __forceinline__ void write_penalty_row_v(uint8_t* tile, int row, const PenView& pv, int hr, int jc, int th8, int tw8) {
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (u < th8) v = pv.row[2 * hr + u];
+    else if (u - th8 < tw8) v = pv.col[2 * jc + (u - th8)];
+    *reinterpret_cast<uint4*>(xtile_unit(tile, row, u)) = v;
+  }
+}
+
 // Everything build_penalty_tables reads, relative to the resident tile: two tiles with the same signature have
 // the same tables (all tiles whose halo the grid does not clip, for one).
 __device__ __forceinline__ uint64_t penalty_signature(const KParams& p, const TilePos& tp) {
   const uint32_t up = (uint32_t)(tp.r0 - tp.hr_first), down = (uint32_t)(tp.hr_last - tp.r0);
-  const uint32_t left = (uint32_t)max(0, -tp.hx0), right = (uint32_t)max(0, tp.hx0 + kPenCols - p.Wtok);
+  const uint32_t left = (uint32_t)max(0, -tp.hx0), right = (uint32_t)max(0, tp.hx0 + p.pl.KW - p.Wtok);   // columns of a block
   const uint32_t phase = (uint32_t)(tp.x0 - tp.hx0);           // fixes x0 modulo b_size and the window offset
   return ((uint64_t)(up | (down << 8) | (left << 16) | (right << 24))) | ((uint64_t)phase << 32);
 }

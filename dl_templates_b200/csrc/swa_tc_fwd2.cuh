@@ -35,11 +35,9 @@ struct Fwd2Shared {
   uint64_t kv_full[kMaxStages], k_ready[kMaxStages], kv_empty[kMaxStages], kx_free[kMaxStages];
   uint64_t s_full[4], p_full[4], s_free[4], pv_done[2], o_full, o_free, ml_full[2], ml_empty[2];
   float ml[2][2][2][128];   // [item parity][group][maximum | sum][row]: handed to the epilogue warps
-  PenaltyTables pen;        // window-mask penalty parts of the current item's halo rows / columns
   uint32_t tmem_base;
   int abort_flag;
 };
-static_assert(sizeof(Fwd2Shared) <= sizeof(FwdShared) + 128, "the planner sizes shared memory with FwdShared + 128");
 
 template <bool BF16>
 __global__ void __launch_bounds__(kFwdThreads, 1)
@@ -65,6 +63,11 @@ fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
   uint8_t* v_smem = k_smem + pl.stages * k_stage;
   uint8_t* kx_smem = v_smem + pl.stages * v_stage;
   Fwd2Shared* sh = reinterpret_cast<Fwd2Shared*>(kx_smem + pl.stages * kx_stage);
+  PenView pen;                                                   // window-mask penalty parts of the current item's halo
+  pen.row = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(sh) + ((sizeof(Fwd2Shared) + 15) & ~size_t(15)));
+  pen.col = pen.row + 2 * pl.pen_rows;
+  pen.n_rows = pl.pen_rows;
+  pen.n_cols = pl.pen_cols;
   volatile int* abort_flag = &sh->abort_flag;
 
   const int warp = threadIdx.x >> 5;
@@ -487,7 +490,7 @@ fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         if (sig != pen_sig) {
           pen_sig = sig;
           named_bar_sync(5, 128);           // nobody still reads the previous tables
-          build_penalty_tables<BF16>(&sh->pen, t, p, tp, 128);
+          build_penalty_view<BF16>(pen, t, p, tp, 128);
           named_bar_sync(5, 128);
         }
       }
@@ -509,7 +512,7 @@ fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         trace_ev(p, 4, tn, t == 0 && it >= p.trace_it, 1 * 16 + (j & 15));
         if (ok) {
           if (row_on)
-            write_penalty_row(kx_smem + stage * kx_stage, t, 0, 1, &sh->pen, j * pl.KR + jr, jc, pl.TH >> 3, pl.TW >> 3);
+            write_penalty_row_v(kx_smem + stage * kx_stage, t, pen, j * pl.KR + jr, jc, pl.TH >> 3, pl.TW >> 3);
           fence_proxy_async_smem();
           mbar_arrive(&sh->k_ready[stage]);
         }

@@ -159,7 +159,8 @@ int swa_bwd_noalloc(const swa_geom_t* g, const swa_rope_t* rope, const swa_tenso
  * geometry: SWA_IMPL_SIMT or SWA_IMPL_TC (negative = rejected). `which`: 0 fwd, 1 dq, 2 dkdv. */
 int swa_select_impl(const swa_geom_t* g, const swa_rope_t* rope, int32_t which);
 
-/* Resource plan of the tensor-core kernel `which` (0 fwd, 1 dq, 2 dkdv) for this geometry; host-only, needs no
+/* Resource plan of the tensor-core kernel `which` for this geometry (0, 1, 2: what swa_fwd, swa_bwd_dq, swa_bwd_dkdv
+ * would launch; 3, 4, 5: what swa_fwd_rot, swa_bwd_dq_rot, swa_bwd_dkdv_rot would launch); host-only, needs no
  * GPU.  A diagnostic without counterpart in the reference: tests use it to check that every plan stays inside
  * 227 KB of shared memory and 512 tensor-memory columns.  out[12] = tile rows, tile columns, block rows, block
  * columns, block tokens N, ring stages, score buffers (fwd) or (S, dP) pairs (bwd), resident-tile buffers,

@@ -130,11 +130,12 @@ def test_every_tile_plan_fits_shared_and_tensor_memory():
                     for dt in (torch.bfloat16, torch.float16):
                         g = _geom(dtype=dt, b_size=bs, t_height=th, t_width=tw, row_size=rs, col_size=cs, d_qk=d_qk,
                                   d_v=d_v)
-                        for which in (0, 1, 2):
+                        for which in ((0, 1, 2) if r is None else (0, 1, 2, 3, 4, 5)):
                             code, p = _plan(g, r, which)
                             if code != 0:
-                                assert _lib.lib.swa_select_impl(C.byref(g), None if r is None else C.byref(r),
-                                                                which) != _lib.IMPL_TC
+                                if which < 3:
+                                    assert _lib.lib.swa_select_impl(C.byref(g), None if r is None else C.byref(r),
+                                                                    which) != _lib.IMPL_TC
                                 continue
                             th_, tw_, kr, kw, n, stages, nsb, nxb, tab_b, req, used, tmem = p
                             what = (d_qk, d_v, n_rdim, max_hw, th, tw, bs, rs, cs, which, p)
@@ -152,7 +153,8 @@ def test_describe_plan_rejects_bad_arguments():
     g = _geom()
     assert _lib.lib.swa_describe_plan(C.byref(g), None, 0, None) < 0
     out = (C.c_int32 * 12)()
-    assert _lib.lib.swa_describe_plan(C.byref(g), None, 3, out) < 0
+    assert _lib.lib.swa_describe_plan(C.byref(g), None, 3, out) < 0      # the hand-off kernels need a RoPE description
+    assert _lib.lib.swa_describe_plan(C.byref(g), None, 6, out) < 0
     g32 = _geom(dtype=torch.float32)
     assert _lib.lib.swa_describe_plan(C.byref(g32), None, 0, out) < 0   # fp32 runs on the SIMT kernels
 
