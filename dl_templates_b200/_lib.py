@@ -37,7 +37,7 @@ class Rope(C.Structure):
 
 EXPORTS = ("swa_fwd", "swa_bwd_delta", "swa_bwd_dq", "swa_bwd_dkdv", "swa_fwd_rot", "swa_bwd_dq_rot", "swa_bwd_dkdv_rot",
            "swa_bwd_noalloc", "rope2d_apply",
-           "rope2d_apply_to", "swa_select_impl", "swa_describe_plan", "swa_launch_count", "swa_last_error", "swa_version")
+           "rope2d_apply_to", "swa_select_impl", "swa_describe_plan", "swa_refresh_env", "swa_launch_count", "swa_last_error", "swa_version")
 
 
 def _load() -> C.CDLL:
@@ -70,6 +70,7 @@ def _load() -> C.CDLL:
                  "swa_bwd_dkdv_rot", "swa_bwd_noalloc", "rope2d_apply",
                  "rope2d_apply_to", "swa_select_impl", "swa_describe_plan", "swa_version"):
         getattr(lib, name).restype = C.c_int
+    lib.swa_refresh_env.restype = None
     lib.swa_launch_count.restype = C.c_int64
     lib.swa_last_error.restype = C.c_char_p
     return lib

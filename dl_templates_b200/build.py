@@ -15,11 +15,11 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libswa2d.so")
-SOURCES = ["swa_abi.cu", "swa_tc.cu"]
-NVCC_FLAGS = [
-    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "-Xcompiler", "-fPIC", "-shared", "--use_fast_math", "-cudart", "shared",
-]
+# source -> extra flags.  The tensor-core kernels are built with fast math (ex2.approx / ftz in their softmax loops:
+# their outputs are 16-bit); the C ABI file holds the SIMT kernels, whose fp32 path must hold 1e-4 against the
+# oracle, and is built with IEEE division and exp2.
+SOURCES = {"swa_abi.cu": [], "swa_tc.cu": ["--use_fast_math"]}
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"]
 
 
 def nvcc_path() -> str:
@@ -40,13 +40,26 @@ def needs_build() -> bool:
 def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not needs_build():
         return LIB
-    cmd = [nvcc_path(), *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []),
-           *[os.path.join(CSRC, s) for s in SOURCES], "-o", LIB]
-    r = subprocess.run(cmd, capture_output=True, text=True)
-    if verbose or r.returncode != 0:
-        sys.stderr.write(r.stdout + r.stderr)
-    if r.returncode != 0:
+    nvcc = nvcc_path()
+    objdir = os.path.join(HERE, "build")
+    os.makedirs(objdir, exist_ok=True)
+    jobs = []
+    for src, extra in SOURCES.items():       # the translation units compile side by side
+        obj = os.path.join(objdir, src.replace(".cu", ".o"))
+        cmd = [nvcc, *NVCC_FLAGS, *extra, *(["-Xptxas", "-v"] if verbose else []), "-c", os.path.join(CSRC, src), "-o", obj]
+        jobs.append((obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+    failed = False
+    for obj, proc in jobs:
+        out, _ = proc.communicate()
+        if verbose or proc.returncode != 0:
+            sys.stderr.write(out)
+        failed = failed or proc.returncode != 0
+    if failed:
         raise RuntimeError("nvcc failed building libswa2d.so")
+    r = subprocess.run([nvcc, "-shared", "-cudart", "shared", *[o for o, _ in jobs], "-o", LIB], capture_output=True, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout + r.stderr)
+        raise RuntimeError("linking libswa2d.so failed")
     return LIB
 
 

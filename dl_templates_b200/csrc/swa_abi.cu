@@ -87,7 +87,8 @@ int resolve_impl(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t
 
 extern "C" {
 
-int swa_version(void) { return 1; }
+int swa_version(void) { return 2; }
+void swa_refresh_env(void) { swa::tc::refresh_env(); }
 const char* swa_last_error(void) { return g_err; }
 int64_t swa_launch_count(void) { return g_launches.load(); }
 

@@ -5,7 +5,9 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <map>
 #include <mutex>
+#include <tuple>
 #include <type_traits>
 
 #include "swa_tc.cuh"
@@ -75,9 +77,44 @@ int sm_count() {
   return cached[dev];
 }
 
-int env_int(const char* name, int dflt) {
+// Experiment knobs (environment variables), read ONCE per process -- a launch must not pay for a dozen getenv
+// calls -- and again only when refresh_env() is called (tests that vary them do).  -1 / 0 = not set.
+struct Knobs {
+  int nmax, nxb, kr, kw, stages, nsb, th_all, th[3], trace_it;
+  bool no_tabs, disable, verbose, trace;
+};
+std::mutex g_plan_mu;                 // guards the knobs and the plan cache
+bool g_knobs_read = false;
+Knobs g_knobs;
+
+int env_raw(const char* name, int dflt) {
   const char* v = getenv(name);
   return v ? atoi(v) : dflt;
+}
+void read_knobs_locked() {
+  Knobs k;
+  k.nmax = env_raw("SWA_TC_NMAX", 0);
+  k.nxb = env_raw("SWA_TC_NXB", 0);
+  k.kr = env_raw("SWA_TC_KR", 0);
+  k.kw = env_raw("SWA_TC_KW", 0);
+  k.stages = env_raw("SWA_TC_STAGES", 0);
+  k.nsb = env_raw("SWA_TC_NSB", 0);
+  k.th_all = env_raw("SWA_TC_TH", 0);
+  k.th[0] = env_raw("SWA_TC_TH_FWD", 0);
+  k.th[1] = env_raw("SWA_TC_TH_DQ", 0);
+  k.th[2] = env_raw("SWA_TC_TH_DKDV", 0);
+  k.trace_it = env_raw("SWA_TC_TRACE_IT", 1);
+  k.no_tabs = getenv("SWA_TC_NO_TABS") != nullptr;
+  k.disable = getenv("SWA_TC_DISABLE") != nullptr;
+  k.verbose = getenv("SWA_TC_VERBOSE") != nullptr;
+  k.trace = getenv("SWA_TC_TRACE") != nullptr;
+  g_knobs = k;
+  g_knobs_read = true;
+}
+Knobs knobs() {
+  std::lock_guard<std::mutex> lock(g_plan_mu);
+  if (!g_knobs_read) read_knobs_locked();
+  return g_knobs;
 }
 
 // Widest halo, in token columns, over all resident-tile columns.
@@ -102,11 +139,12 @@ int halo_width(const swa_geom_t* g, int TW) {
 bool make_plan_shape(const swa_geom_t* g, int which, int TH, int TW, uint32_t tab_bytes, Plan* out, long* cost_out = nullptr,
                      bool v2 = false) {
   Plan pl;
+  pl.ncb = 1;
   pl.tab_bytes = tab_bytes;
   pl.TH = TH;
   pl.TW = TW;
   const int hw = halo_width(g, pl.TW);
-  if (hw > kPenCols) return false;
+  if (!v2 && hw > kPenCols) return false;     // the kernels with streamed rotation keep a whole halo row per block row
   const int halo_rows = pl.TH + 2 * g->row_size;
   const int qch = g->d_qk / 64, vch = g->d_v / 64;
   const uint32_t x_bytes = (which == 0 ? qch : qch + vch) * 16384u;
@@ -119,52 +157,59 @@ bool make_plan_shape(const swa_geom_t* g, int which, int TH, int TW, uint32_t ta
   const uint32_t slack_v2 = 1024u + (((which == 0 ? (uint32_t)sizeof(Fwd2Shared) : (uint32_t)sizeof(Bwd2Shared)) + 15u) & ~15u) +
                             (which == 0 ? 0u : 2048u);
   // per candidate block shape: the v2 kernels' penalty tables take (halo rows + KR + KW) entries of 32 bytes
-  auto slack_for = [&](int KR, int KW) { return v2 ? slack_v2 + (uint32_t)(halo_rows + KR + KW) * 32u : slack_v1; };
+  auto slack_for = [&](int KR, int KW, int ncb) { return v2 ? slack_v2 + (uint32_t)(halo_rows + KR + KW * ncb) * 32u : slack_v1; };
   {
     // backward: two (S, dP) pairs of 2N columns next to the accumulators (N = 64 always fits: 256 + 256 columns)
     const int nsb = 2;
     int nmax = which == 0 ? 128 : (512 - acc_cols) / (2 * nsb);
     nmax = nmax > 128 ? 128 : nmax;
-    nmax = env_int("SWA_TC_NMAX", nmax);
-    for (int nxb = which == 0 ? 2 : env_int("SWA_TC_NXB", 2); nxb >= (which == 0 ? 2 : 1); --nxb) {
+    const Knobs kn = knobs();
+    if (kn.nmax) nmax = kn.nmax;
+    for (int nxb = which == 0 ? 2 : (kn.nxb ? kn.nxb : 2); nxb >= (which == 0 ? 2 : 1); --nxb) {
       const uint32_t fixed = nxb * x_bytes + 128u * kXRowBytes + tab_bytes;
       long best_cost = -1;
-      for (int KW = hw; KW <= kPenCols; ++KW)
-        for (int KR = 1; KR <= 16; ++KR) {
-          const int N = KW * KR;
-          if (N > nmax || N % 16) continue;
-          if (fixed + min_stages * ((uint32_t)N * row_bytes + stage_extra) + slack_for(KR, KW) > kSmemLimit) continue;
-          const long nblk = (halo_rows + KR - 1) / KR;
-          const long cost = nblk * N * 16 + nblk * 400;  // executed columns + a per-block overhead
-          if (best_cost < 0 || cost < best_cost) {
-            best_cost = cost;
-            pl.KR = KR; pl.KW = KW; pl.N = N;
+      // ncb = column blocks per halo row: 1 whenever a block can span the halo; the kernels without streamed
+      // rotation also take halos wider than any block and walk them in several column blocks
+      for (int ncb = 1; ncb <= (v2 ? 16 : 1) && best_cost < 0; ++ncb)
+        for (int KW = (hw + ncb - 1) / ncb; KW <= kPenCols && (ncb == 1 || KW * (ncb - 1) < hw); ++KW)
+          for (int KR = 1; KR <= 16; ++KR) {
+            const int N = KW * KR;
+            if (N > nmax || N % 16) continue;
+            if (fixed + min_stages * ((uint32_t)N * row_bytes + stage_extra) + slack_for(KR, KW, ncb) > kSmemLimit) continue;
+            const long nblk = (long)((halo_rows + KR - 1) / KR) * ncb;
+            const long cost = nblk * N * 16 + nblk * 400;  // executed columns + a per-block overhead
+            if (best_cost < 0 || cost < best_cost) {
+              best_cost = cost;
+              pl.KR = KR; pl.KW = KW; pl.N = N; pl.ncb = ncb;
+            }
           }
-        }
       if (best_cost < 0) continue;
-      if (int v = env_int("SWA_TC_KR", 0)) {
-        pl.KR = v;
-        pl.KW = env_int("SWA_TC_KW", pl.KW);
+      if (kn.kr) {
+        pl.KR = kn.kr;
+        if (kn.kw) pl.KW = kn.kw;
         pl.N = pl.KR * pl.KW;
+        pl.ncb = 1;
+        // an override must still hold a whole halo row per block row and fit the penalty-table columns
+        if (pl.KW < hw || pl.KW > kPenCols || pl.KR > 16) return false;
       }
       const uint32_t stage = (uint32_t)pl.N * row_bytes + stage_extra;
-      const uint32_t kSmemSlack = slack_for(pl.KR, pl.KW);
+      const uint32_t kSmemSlack = slack_for(pl.KR, pl.KW, pl.ncb);
       pl.pen_rows = halo_rows + pl.KR;
-      pl.pen_cols = pl.KW;
+      pl.pen_cols = pl.KW * pl.ncb;
       const int Wtok = g->t_width * g->b_size;
       pl.n_tiles_x = (Wtok + pl.TW - 1) / pl.TW;
       pl.n_tiles_y = (g->t_height + pl.TH - 1) / pl.TH;
       pl.nxb = nxb;
       pl.stages = min_stages;
       while (pl.stages < kMaxStages && fixed + (pl.stages + 1) * stage + kSmemSlack <= kSmemLimit) ++pl.stages;
-      pl.stages = env_int("SWA_TC_STAGES", pl.stages);
+      if (kn.stages) pl.stages = kn.stages;
       pl.smem_bytes = fixed + pl.stages * stage + kSmemSlack;
       if (which == 0) {
         // forward: score buffers = look-ahead of the score MMAs: 3 next to the two accumulators, 4 (packed at N-column
         // strides) when tensor memory allows and the block ring is deep enough to feed them (measured)
         int n = pl.stages >= 6 ? 4 : 3;
         while (n > 2 && n * pl.N + 2 * 64 * vch > 512) --n;
-        pl.nsb = env_int("SWA_TC_NSB", n);
+        pl.nsb = kn.nsb ? kn.nsb : n;
       } else {
         pl.nsb = nsb;
       }
@@ -185,14 +230,14 @@ bool make_plan_shape(const swa_geom_t* g, int which, int TH, int TW, uint32_t ta
 uint32_t rope_table_bytes(const swa_rope_t* rope) {
   if (!rope || !rope->idx) return 0;
   const uint64_t b = (uint64_t)(rope->max_h + rope->max_w) * rope_tab_stride(rope->n_rdim);
-  return b <= 48 * 1024 && !getenv("SWA_TC_NO_TABS") ? (uint32_t)((b + 15) & ~15ull) : 0;
+  return b <= 48 * 1024 && !knobs().no_tabs ? (uint32_t)((b + 15) & ~15ull) : 0;
 }
 
 // Tile shape for one choice of staged-table bytes; *cost = the planner's block cost of the plan taken.
 static bool make_plan_tab(const swa_geom_t* g, const swa_rope_t* rope, int which, uint32_t tab, Plan* out, long* cost,
                           bool v2 = false) {
-  const char* th_names[3] = {"SWA_TC_TH_FWD", "SWA_TC_TH_DQ", "SWA_TC_TH_DKDV"};
-  const int th = env_int(th_names[which], env_int("SWA_TC_TH", 0));
+  const Knobs kn = knobs();
+  const int th = kn.th[which] ? kn.th[which] : kn.th_all;
   if (th == 8) return make_plan_shape(g, which, 8, 16, tab, out, cost, v2);
   if (th == 16) return make_plan_shape(g, which, 16, 8, tab, out, cost, v2);
   if (which == 2) {
@@ -220,7 +265,31 @@ static bool make_plan_tab(const swa_geom_t* g, const swa_rope_t* rope, int which
 // The cos/sin tables are staged in shared memory when that does not cost block size: a plan with the tables is
 // taken only if its blocks are as cheap as those of the plan without them (40 KB of tables beside d = 128 tiles
 // would force 48-token instead of 80-token blocks, measured 1.5x slower in the forward kernel).
-bool make_plan(const swa_geom_t* g, const swa_rope_t* rope, int which, Plan* out) {
+// Plans are cached: the search below is a few thousand candidate shapes, repeated for the three kernels of every
+// step with the same geometry.  Key = everything the planner reads.
+using PlanKey = std::tuple<int, int, int, int, int, int, int, int, int, int, int, int, int>;
+std::map<PlanKey, std::pair<bool, Plan>> g_plan_cache;
+
+PlanKey plan_key(const swa_geom_t* g, const swa_rope_t* rope, int which, bool v2) {
+  const bool has = rope && rope->idx;
+  return PlanKey(which + (v2 ? 3 : 0), g->t_height, g->t_width, g->b_size, g->row_size, g->col_size, g->d_qk, g->d_v,
+                 has ? rope->n_rdim : 0, has ? rope->max_h : 0, has ? rope->max_w : 0, g->dtype == SWA_BF16 ? 1 : 0, 0);
+}
+bool cache_lookup(const PlanKey& k, bool* ok, Plan* out) {
+  std::lock_guard<std::mutex> lock(g_plan_mu);
+  auto it = g_plan_cache.find(k);
+  if (it == g_plan_cache.end()) return false;
+  *ok = it->second.first;
+  *out = it->second.second;
+  return true;
+}
+void cache_store(const PlanKey& k, bool ok, const Plan& pl) {
+  std::lock_guard<std::mutex> lock(g_plan_mu);
+  if (g_plan_cache.size() > 4096) g_plan_cache.clear();
+  g_plan_cache[k] = std::make_pair(ok, pl);
+}
+
+bool make_plan_uncached(const swa_geom_t* g, const swa_rope_t* rope, int which, Plan* out) {
   const uint32_t tab = rope_table_bytes(rope);
   Plan with, without;
   long cw = 0, cn = 0;
@@ -236,7 +305,18 @@ bool make_plan(const swa_geom_t* g, const swa_rope_t* rope, int which, Plan* out
 // Plan of the kernels that rotate no streamed row (rotation handed on between the kernels, or no RoPE): the
 // tile shape of the problem without RoPE; the tables (needed once per item only) are staged when that costs
 // neither block size nor a stage of the ring.
-bool make_plan_prerot(const swa_geom_t* g, const swa_rope_t* rope, int which, Plan* out) {
+bool make_plan(const swa_geom_t* g, const swa_rope_t* rope, int which, Plan* out) {
+  const PlanKey key = plan_key(g, rope, which, false);
+  bool ok = false;
+  if (cache_lookup(key, &ok, out)) return ok;
+  Plan pl{};
+  ok = make_plan_uncached(g, rope, which, &pl);
+  cache_store(key, ok, pl);
+  if (ok) *out = pl;
+  return ok;
+}
+
+bool make_plan_prerot_uncached(const swa_geom_t* g, const swa_rope_t* rope, int which, Plan* out) {
   const uint32_t tab = rope_table_bytes(rope);
   Plan with, without;
   long cw = 0, cn = 0;
@@ -261,6 +341,17 @@ bool mask_constants(float sm_scale, float* a, float* b) {
   return aa * bb >= need;
 }
 
+bool make_plan_prerot(const swa_geom_t* g, const swa_rope_t* rope, int which, Plan* out) {
+  const PlanKey key = plan_key(g, rope, which, true);
+  bool ok = false;
+  if (cache_lookup(key, &ok, out)) return ok;
+  Plan pl{};
+  ok = make_plan_prerot_uncached(g, rope, which, &pl);
+  cache_store(key, ok, pl);
+  if (ok) *out = pl;
+  return ok;
+}
+
 KParams make_params(const swa_geom_t* g, const swa_rope_t* rope, const Plan& pl, int32_t* status) {
   KParams p;
   p.t_h = g->t_height;
@@ -279,23 +370,33 @@ KParams make_params(const swa_geom_t* g, const swa_rope_t* rope, const Plan& pl,
   p.n_items = pl.n_tiles_x * pl.n_tiles_y * g->B * g->H;
   p.status = status;
   // the Python layer hands a 4 KiB status buffer: words 0-3 status, bytes 16.. = 4 roles x 32 clock samples
-  p.trace = (status != nullptr && getenv("SWA_TC_TRACE")) ? reinterpret_cast<long long*>(status + 4) : nullptr;
-  p.trace_it = env_int("SWA_TC_TRACE_IT", 1);
+  const Knobs kn = knobs();
+  p.trace = (status != nullptr && kn.trace) ? reinterpret_cast<long long*>(status + 4) : nullptr;
+  p.trace_it = kn.trace_it;
   return p;
 }
 
-bool tensor_ok(const swa_tensor_t* t) {
+// What a tensor map of these kernels can describe: unit last stride, 16-byte aligned base and rows, and strictly
+// positive strides (a batch or head dimension broadcast with stride 0 cannot be encoded; extents of 1 are
+// given a legal stride when the map is built).  `B`, `H` = extents of the first two dimensions.
+bool tensor_ok(const swa_tensor_t* t, int B, int H) {
   return t->stride[3] == 1 && ((uintptr_t)t->ptr % 16) == 0 && t->stride[0] % 8 == 0 && t->stride[1] % 8 == 0 &&
-         t->stride[2] % 8 == 0 && t->stride[2] > 0;
+         t->stride[2] % 8 == 0 && t->stride[2] > 0 && (B == 1 || t->stride[0] > 0) && (H == 1 || t->stride[1] > 0);
 }
 
 }  // namespace
 
 const char* last_error() { return g_tc_err; }
 
+void refresh_env() {
+  std::lock_guard<std::mutex> lock(g_plan_mu);
+  read_knobs_locked();
+  g_plan_cache.clear();
+}
+
 const char* unsupported_reason(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* const* tensors,
                                int n_tensors, int which, bool prerotated) {
-  if (getenv("SWA_TC_DISABLE")) return "disabled by SWA_TC_DISABLE";
+  if (knobs().disable) return "disabled by SWA_TC_DISABLE";
   if (g->dtype != SWA_F16 && g->dtype != SWA_BF16) return "fp32 runs on the SIMT kernels";
   if ((g->d_qk != 64 && g->d_qk != 128) || (g->d_v != 64 && g->d_v != 128)) return "head dims must be 64 or 128";
   if (!(g->sm_scale > 0.f)) return "sm_scale must be positive";
@@ -308,9 +409,9 @@ const char* unsupported_reason(const swa_geom_t* g, const swa_rope_t* rope, cons
   Plan pl;
   const bool v2 = prerotated || !(rope && rope->idx);
   if (!(v2 ? make_plan_prerot(g, which == 0 ? nullptr : rope, which, &pl) : make_plan(g, rope, which, &pl)))
-    return "no tile plan fits (window too wide for one streamed block)";
+    return "no tile plan fits (window too wide for one streamed block of the kernels with streamed rotation)";
   for (int i = 0; i < n_tensors; ++i)
-    if (!tensor_ok(tensors[i])) return "tensors need unit last stride and 16-byte aligned rows";
+    if (!tensor_ok(tensors[i], g->B, g->H)) return "tensors need unit last stride, positive strides and 16-byte aligned rows";
   return nullptr;
 }
 
@@ -380,7 +481,7 @@ int launch_fwd(const swa_geom_t* g, const swa_rope_t* rope, const swa_tensor_t* 
     snprintf(g_tc_err, sizeof(g_tc_err), "cudaFuncSetAttribute(%u bytes): %s", pl.smem_bytes, cudaGetErrorString(e));
     return -1;
   }
-  if (getenv("SWA_TC_VERBOSE"))
+  if (knobs().verbose)
     fprintf(stderr, "[swa2d] fwd plan: tile %dx%d, block %dx%d (N=%d), stages %d, tables %u, smem %u, %d items on %u CTAs\n",
             pl.TH, pl.TW, pl.KR, pl.KW, pl.N, pl.stages, pl.tab_bytes, pl.smem_bytes, n_items, grid.x);
   kern<<<grid, block, pl.smem_bytes, st>>>(tq, tk, tv, p, make_view(o), lse);
@@ -407,7 +508,7 @@ int launch_fwd2(const swa_geom_t* g, const swa_tensor_t* q, const swa_tensor_t* 
     snprintf(g_tc_err, sizeof(g_tc_err), "cudaFuncSetAttribute(%u bytes): %s", pl.smem_bytes, cudaGetErrorString(e));
     return -1;
   }
-  if (getenv("SWA_TC_VERBOSE"))
+  if (knobs().verbose)
     fprintf(stderr, "[swa2d] fwd2 plan: tile %dx%d, block %dx%d (N=%d), stages %d, score buffers %d, smem %u, %d items on %u CTAs\n",
             pl.TH, pl.TW, pl.KR, pl.KW, pl.N, pl.stages, pl.nsb, pl.smem_bytes, p.n_items, grid.x);
   kern<<<grid, block, pl.smem_bytes, st>>>(tq, tk, tv, p, make_view(o), lse);
@@ -465,7 +566,7 @@ int launch_bwd(const swa_geom_t* g, const swa_rope_t* rope, bool prerotated, con
     snprintf(g_tc_err, sizeof(g_tc_err), "cudaFuncSetAttribute(%u bytes): %s", pl.smem_bytes, cudaGetErrorString(e));
     return -1;
   }
-  if (getenv("SWA_TC_VERBOSE"))
+  if (knobs().verbose)
     fprintf(stderr, "[swa2d] %s plan: tile %dx%d, block %dx%d (N=%d), stages %d, nsb %d, nxb %d, tables %u, smem %u, %d items on %u CTAs\n",
             DKDV ? "dkdv" : "dq", pl.TH, pl.TW, pl.KR, pl.KW, pl.N, pl.stages, pl.nsb, pl.nxb, pl.tab_bytes, pl.smem_bytes, p.n_items, grid.x);
   kern<<<grid, block, pl.smem_bytes, st>>>(mxqk, mxv, myqk, myv, p, lse, delta, make_view(out_qk),

@@ -14,6 +14,10 @@ const char* unsupported_reason(const swa_geom_t* g, const swa_rope_t* rope, cons
                                int n_tensors, int which, bool prerotated = false);
 const char* last_error();
 
+// Re-read the SWA_TC_* experiment knobs from the environment and drop the cached plans (both are otherwise read /
+// computed once per process).
+void refresh_env();
+
 // Resource plan the tensor-core kernel `which` would run with (host-only, no GPU needed): out[0..11] =
 // TH, TW, KR, KW, N, stages, score buffers (forward) / buffer pairs (backward), resident-tile buffers,
 // staged-table bytes, dynamic shared memory requested, shared memory the kernel's layout really uses

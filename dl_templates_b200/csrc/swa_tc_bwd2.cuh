@@ -18,6 +18,9 @@
 // streams run side by side; the order the single issuer gave for free ("the accumulating MMAs of the
 // block that used this pair last were issued before") becomes one more barrier, pair_free, that the
 // accumulate issuer commits and the score issuer waits for.
+// Measured and dropped: two compute threads per resident row, each on half of every block's columns (a block's
+// compute phase halves, but both groups then work on the SAME block, the blocks of an item become strictly
+// sequential and dK/dV went from 2.14 to 2.59 ms per launch).
 //
 // All waits are bounded; a timed-out wait raises a CTA-wide abort flag, every role runs its loops to the
 // end without touching anything, TMEM is freed and the status word records it.
@@ -32,6 +35,7 @@ struct Bwd2Shared {
   uint64_t x_full[2], x_empty[2];
   uint64_t y_full[kMaxStages], y_ready[kMaxStages], y_empty[kMaxStages], yx_free[kMaxStages];
   uint64_t sd_full[2], ds_full[2], pair_free[2], acc_full, acc_free;
+  uint64_t vec_ready[kMaxStages + 2];   // dK/dV: the lse / delta slot of a block is written (one barrier per slot)
   uint32_t tmem_base;
   int abort_flag;
   int abort_site;
@@ -129,6 +133,7 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
     }
     mbar_init(&sh->acc_full, 1);
     mbar_init(&sh->acc_free, 128);
+    for (int s = 0; s < kMaxStages + 2; ++s) mbar_init(&sh->vec_ready[s], 128);
     for (int s = 0; s < kMaxStages; ++s) {
       mbar_init(&sh->y_full[s], 1);
       mbar_init(&sh->y_ready[s], 128);
@@ -181,8 +186,7 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
     const uint32_t s_tm = lane_base + g * 2 * N, d_tm = s_tm + N;
     uint64_t* const ds_bar = &sh->ds_full[g];
     int buf_par = 0;
-    int stage = g % pl.stages, stage_par = (g / pl.stages) & 1;
-    int vslot = g;                                 // slot of the lse / delta ring of this group's next block
+    int vslot = g, vpar = 0;                       // slot of the lse / delta ring of this group's next block, its barrier parity
 #pragma unroll 1
     for (int it = 0, item = blockIdx.x; item < n_items; ++it, item += gridDim.x) {
       const int bh = item / tiles_per_head;
@@ -203,13 +207,16 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
         wait_spin(&sh->sd_full[g], buf_par, 7);
         trace_ev(p, 2 + g, tn, m == 0 && it >= p.trace_it, 1 * 16 + (j & 15));
         const float* vec = vec_smem + vslot * 256;
+        // -lse / delta of the block's queries are staged.  One barrier per slot of that ring, not the stage's
+        // y_ready: the warps that fill the slots run ahead of the block ring and may complete a stage's y_ready twice
+        // before this warp has looked at it, but they cannot refill a slot before this warp has read it (see there).
+        if (DKDV) wait_spin(&sh->vec_ready[vslot], vpar, 8);
         vslot += 2;
-        if (vslot >= vslots) vslot -= vslots;
-        if (DKDV) wait_spin(&sh->y_ready[stage], stage_par, 8);   // -lse / delta of the block's queries are staged
+        if (vslot >= vslots) { vslot -= vslots; vpar ^= 1; }
         buf_par ^= 1;
-        stage += 2;
-        if (stage >= pl.stages) { stage -= pl.stages; stage_par ^= 1; }
-        const int blk_first = tp.hr_first + j * pl.KR, blk_last = blk_first + pl.KR - 1;
+        int band, cblk;
+        block_pos(pl, j, band, cblk);
+        const int blk_first = tp.hr_first + band * pl.KR, blk_last = blk_first + pl.KR - 1;
         const bool seen = !(blk_last < see_lo || blk_first > see_hi);
         if (ok) {
           tc_fence_after();
@@ -319,13 +326,15 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
           trace_ev(p, 0, tn, tl && it >= p.trace_it, 1 * 16 + (j & 15));
           if (ok && elect_one()) {
             mbar_arrive_expect_tx(&sh->y_full[stage], yqk_stage + yv_stage);
-            const int row = tp.hr_first + j * pl.KR;
+            int band, cblk;
+            block_pos(pl, j, band, cblk);
+            const int row = tp.hr_first + band * pl.KR, col = tp.hx0 + cblk * pl.KW;
 #pragma unroll 1
             for (int c = 0; c < p.qch; ++c)
-              tma_load_5d(yqk_smem + stage * yqk_stage + c * blk_bytes, &tm_yqk, &sh->y_full[stage], c * 64, tp.hx0, row, hi, bi);
+              tma_load_5d(yqk_smem + stage * yqk_stage + c * blk_bytes, &tm_yqk, &sh->y_full[stage], c * 64, col, row, hi, bi);
 #pragma unroll 1
             for (int c = 0; c < p.vch; ++c)
-              tma_load_5d(yv_smem + stage * yv_stage + c * blk_bytes, &tm_yv, &sh->y_full[stage], c * 64, tp.hx0, row, hi, bi);
+              tma_load_5d(yv_smem + stage * yv_stage + c * blk_bytes, &tm_yv, &sh->y_full[stage], c * 64, col, row, hi, bi);
           }
           __syncwarp();
           if (++stage == pl.stages) { stage = 0; stage_par ^= 1; ring_full = true; }
@@ -538,16 +547,17 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
       tp.nblk = 0;
       if (have) tp = tile_pos(p, item - bh * tiles_per_head);
       const int64_t vec_base = (int64_t)bh * p.t_h * p.Wtok;
-      const int c = tp.hx0 + jc;
-      const bool c_in = row_on && c >= 0 && c < p.Wtok;
+
       // -lse and delta of this thread's row of block j (dK/dV: the streamed rows are queries)
       float nl = -INFINITY, dl = 0.f;
       auto load_vec = [&](int j) {
         nl = -INFINITY;
         dl = 0.f;
         if constexpr (DKDV) {
-          const int row = tp.hr_first + j * pl.KR + jr;
-          if (c_in && j < tp.nblk && row < p.t_h) {
+          int band, cblk;
+          block_pos(pl, j, band, cblk);
+          const int row = tp.hr_first + band * pl.KR + jr, c = tp.hx0 + cblk * pl.KW + jc;
+          if (row_on && c >= 0 && c < p.Wtok && j < tp.nblk && row < p.t_h) {
             nl = -__ldg(lse + vec_base + (int64_t)row * p.Wtok + c);
             dl = __ldg(delta + vec_base + (int64_t)row * p.Wtok + c);
           }
@@ -586,7 +596,9 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
         trace_ev(p, 4, tn, t == 0 && it >= p.trace_it, 1 * 16 + (j & 15));
         if (ok) {
           if (row_on) {
-            write_penalty_row_v(yx_smem + stage * yx_stage, t, pen, j * pl.KR + jr, jc, pl.TH >> 3, pl.TW >> 3);
+            int band, cblk;
+            block_pos(pl, j, band, cblk);
+            write_penalty_row_v(yx_smem + stage * yx_stage, t, pen, band * pl.KR + jr, cblk * pl.KW + jc, pl.TH >> 3, pl.TW >> 3);
             if constexpr (DKDV) {
               vec_smem[vslot * 256 + t] = a0;
               vec_smem[vslot * 256 + 128 + t] = b0;
@@ -594,6 +606,7 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
           }
           fence_proxy_async_smem();
           mbar_arrive(&sh->y_ready[stage]);
+          if constexpr (DKDV) mbar_arrive(&sh->vec_ready[vslot]);
         }
         trace_ev(p, 4, tn, t == 0 && it >= p.trace_it, 2 * 16 + (j & 15));
         if (++stage == pl.stages) { stage = 0; stage_par ^= 1; ring_full = true; }

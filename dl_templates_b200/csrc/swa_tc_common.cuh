@@ -28,6 +28,8 @@ constexpr int kMaxStages = 8;   // depth limit of the streamed-block ring
 struct Plan {
   int TH, TW;          // resident tile: rows x token columns (TH*TW == 128)
   int KR, KW, N;       // streamed block: rows x token columns, N = KR*KW
+  int ncb;             // column blocks per halo row (1: a block spans the halo; more: only the kernels without
+                       // streamed rotation, for halos wider than one block)
   int n_tiles_x, n_tiles_y;
   int stages;          // streamed-block pipeline depth
   int nsb, nxb;        // backward: (S, dP) buffer pairs in tensor memory, resident-tile buffers in shared memory
@@ -66,7 +68,7 @@ __device__ __forceinline__ TilePos tile_pos(const KParams& p, int tile_idx) {
   t.hx0 = (t.x0 / p.b - p.wc) * p.b;
   t.hr_first = max(t.r0 - p.wr, 0);
   t.hr_last = min(t.r0 + p.pl.TH - 1 + p.wr, p.t_h - 1);
-  t.nblk = (t.hr_last - t.hr_first + p.pl.KR) / p.pl.KR;
+  t.nblk = (t.hr_last - t.hr_first + p.pl.KR) / p.pl.KR * p.pl.ncb;
   return t;
 }
 
@@ -74,7 +76,13 @@ __device__ __forceinline__ TilePos tile_pos(const KParams& p, int tile_idx) {
 __device__ __forceinline__ int item_blocks(const KParams& p, int item, int tiles_per_head) {
   const int tile = item % tiles_per_head, ty = tile / p.pl.n_tiles_x, r0 = ty * p.pl.TH;
   const int first = max(r0 - p.wr, 0), last = min(r0 + p.pl.TH - 1 + p.wr, p.t_h - 1);
-  return (last - first + p.pl.KR) / p.pl.KR;
+  return (last - first + p.pl.KR) / p.pl.KR * p.pl.ncb;
+}
+
+// Block j of an item: the blocks walk the halo row band by row band, `ncb` column blocks per band.
+__device__ __forceinline__ void block_pos(const Plan& pl, int j, int& band, int& cblk) {
+  band = pl.ncb == 1 ? j : j / pl.ncb;
+  cblk = j - band * pl.ncb;
 }
 
 template <bool BF16>
@@ -230,7 +238,7 @@ __device__ __forceinline__ void write_penalty_row_v(uint8_t* tile, int row, cons
 // the same tables (all tiles whose halo the grid does not clip, for one).
 __device__ __forceinline__ uint64_t penalty_signature(const KParams& p, const TilePos& tp) {
   const uint32_t up = (uint32_t)(tp.r0 - tp.hr_first), down = (uint32_t)(tp.hr_last - tp.r0);
-  const uint32_t left = (uint32_t)max(0, -tp.hx0), right = (uint32_t)max(0, tp.hx0 + p.pl.KW - p.Wtok);   // columns of a block
+  const uint32_t left = (uint32_t)max(0, -tp.hx0), right = (uint32_t)max(0, tp.hx0 + p.pl.pen_cols - p.Wtok);
   const uint32_t phase = (uint32_t)(tp.x0 - tp.hx0);           // fixes x0 modulo b_size and the window offset
   return ((uint64_t)(up | (down << 8) | (left << 16) | (right << 24))) | ((uint64_t)phase << 32);
 }

@@ -16,7 +16,10 @@
 // instruction stream of about 2000 cycles per block while the tensor pipe needs less than half of
 // that, and an epilogue inside the softmax groups idled both at every item boundary; hence two issuers
 // (the order a single issuer gave for free becomes the barrier s_free) and epilogue warps.
-// Measured and dropped: rotating the query tile in warps 12-15 as well (about 400 dependent instructions
+// Measured and dropped: two threads per query row, each on half of every block's columns with the row maximum
+// exchanged through shared memory (the softmax phase of a block halves, but both groups then work on the SAME
+// block and the blocks of an item become strictly sequential: 1.47 ms per launch against 1.17 ms); rotating the
+// query tile in warps 12-15 as well (about 400 dependent instructions
 // per row cost 2700 cycles per item on the critical path, 1.1 ms per launch at the default workload,
 // against 0.1 ms for a streaming pass over q), and a single warp writing all mask rows right behind the
 // producer (four rows per lane made it the slowest role of the kernel).
@@ -150,7 +153,9 @@ fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         trace_ev(p, 2 + g, tn, m == 0 && it >= p.trace_it, 1 * 16 + (j & 15));
         sbuf += 2;                                // two positions on in the ring of nsb buffers
         if (sbuf >= nsb) { sbuf -= nsb; spar ^= 1; }
-        const int blk_first = tp.hr_first + j * pl.KR, blk_last = blk_first + pl.KR - 1;
+        int band, cblk;
+        block_pos(pl, j, band, cblk);
+        const int blk_first = tp.hr_first + band * pl.KR, blk_last = blk_first + pl.KR - 1;
         const bool seen = !(blk_last < see_lo || blk_first > see_hi);
         if (ok) {
           tc_fence_after();
@@ -282,13 +287,15 @@ fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
           if (ring_full) wait_park(&sh->kv_empty[stage], stage_par);
           if (ok && elect_one()) {
             mbar_arrive_expect_tx(&sh->kv_full[stage], k_stage + v_stage);
-            const int row = tp.hr_first + j * pl.KR;
+            int band, cblk;
+            block_pos(pl, j, band, cblk);
+            const int row = tp.hr_first + band * pl.KR, col = tp.hx0 + cblk * pl.KW;
 #pragma unroll 1
             for (int c = 0; c < p.qch; ++c)
-              tma_load_5d(k_smem + stage * k_stage + c * blk_bytes, &tm_k, &sh->kv_full[stage], c * 64, tp.hx0, row, hi, bi);
+              tma_load_5d(k_smem + stage * k_stage + c * blk_bytes, &tm_k, &sh->kv_full[stage], c * 64, col, row, hi, bi);
 #pragma unroll 1
             for (int c = 0; c < p.vch; ++c)
-              tma_load_5d(v_smem + stage * v_stage + c * blk_bytes, &tm_v, &sh->kv_full[stage], c * 64, tp.hx0, row, hi, bi);
+              tma_load_5d(v_smem + stage * v_stage + c * blk_bytes, &tm_v, &sh->kv_full[stage], c * 64, col, row, hi, bi);
           }
           __syncwarp();
           if (++stage == pl.stages) { stage = 0; stage_par ^= 1; ring_full = true; }
@@ -511,8 +518,11 @@ fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         if (ring_full) wait_park(&sh->kx_free[stage], (uint32_t)stage_par);
         trace_ev(p, 4, tn, t == 0 && it >= p.trace_it, 1 * 16 + (j & 15));
         if (ok) {
-          if (row_on)
-            write_penalty_row_v(kx_smem + stage * kx_stage, t, pen, j * pl.KR + jr, jc, pl.TH >> 3, pl.TW >> 3);
+          if (row_on) {
+            int band, cblk;
+            block_pos(pl, j, band, cblk);
+            write_penalty_row_v(kx_smem + stage * kx_stage, t, pen, band * pl.KR + jr, cblk * pl.KW + jc, pl.TH >> 3, pl.TW >> 3);
+          }
           fence_proxy_async_smem();
           mbar_arrive(&sh->k_ready[stage]);
         }

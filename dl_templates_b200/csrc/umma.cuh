@@ -117,7 +117,10 @@ constexpr uint32_t kWaitMaxPolls = 1u << 22;  // polls (spinning) resp. sleeps b
 // function per mode.  The kernels are instruction-fetch bound in their rarely executed scalar
 // parts, so every call site has to stay small.
 constexpr uint32_t kPollNoSuspend = 0xffffffffu;
-constexpr unsigned long long kWaitBudgetNs = 200ull * 1000 * 1000;   // a wait gives up after 0.2 s of wall time
+// A wait gives up after one second of wall time: far beyond any legitimate wait of these kernels (a whole launch
+// takes milliseconds), yet short enough to leave a mis-synchronised kernel quickly; long enough that a context
+// that is time-sliced with another process does not trip it.
+constexpr unsigned long long kWaitBudgetNs = 1000ull * 1000 * 1000;
 __device__ __forceinline__ unsigned long long global_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));

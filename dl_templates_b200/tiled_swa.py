@@ -34,6 +34,7 @@ import torch
 from . import _lib
 
 _status_words = {}
+_status_mirrors = {}      # per device: (pinned host copy of the status word, event after the copy)
 
 
 def _status(device: torch.device) -> torch.Tensor:
@@ -45,16 +46,46 @@ def _status(device: torch.device) -> torch.Tensor:
     return _status_words[key]
 
 
+def _raise_timeout(key, vals):
+    raise RuntimeError(f"swa2d kernel reported a bounded-wait timeout on {key}: status={vals} "
+                       "(its outputs are incomplete)")
+
+
+def _watch_status(device: torch.device) -> None:
+    """A timed-out kernel must not go unnoticed by callers that never synchronise on it: after every batch of
+    launches the status word is copied to pinned host memory on the same stream (16 bytes, no synchronisation),
+    and every later call first looks at the copies that have arrived."""
+    key = (device.type, device.index)
+    if key not in _status_mirrors:
+        _status_mirrors[key] = (torch.zeros(4, dtype=torch.int32).pin_memory(), torch.cuda.Event())
+    host, ev = _status_mirrors[key]
+    host.copy_(_status(device)[:4], non_blocking=True)
+    ev.record(torch.cuda.current_stream(device))
+
+
+def _poll_status() -> None:
+    """Raise if a status copy that has ALREADY arrived reports a timed-out wait (never blocks)."""
+    for key, (host, ev) in _status_mirrors.items():
+        if ev.query() and int(host[0]) != 0:
+            vals = host.tolist()
+            host.zero_()
+            _status_words[key].zero_()
+            _raise_timeout(key, vals)
+
+
 def check_status(device=None) -> None:
     """Synchronise and raise if any kernel reported a timed-out wait."""
     for key, word in _status_words.items():
         vals = word[:4].cpu().tolist()
         if vals[0] != 0:
             word.zero_()
-            raise RuntimeError(f"swa2d kernel reported a bounded-wait timeout on {key}: status={vals}")
+            if key in _status_mirrors:
+                _status_mirrors[key][0].zero_()
+            _raise_timeout(key, vals)
 
 
 def _check_inputs(q, k, v, b_size, t_height, t_width):
+    _poll_status()
     if not (q.is_cuda and k.is_cuda and v.is_cuda):
         raise RuntimeError("dl_templates_b200 runs on CUDA tensors only (sm_100a); there is no CPU path")
     if q.dim() != 4 or k.shape != q.shape or v.shape[:3] != q.shape[:3]:
@@ -151,6 +182,7 @@ def swa_forward(q, k, v, rope, b_size, t_height, t_width, row_size, col_size, sm
         code = _lib.lib.swa_fwd(C.byref(g), _ref(r), C.byref(tq), C.byref(tk), C.byref(tv), C.byref(to),
                                 lse.data_ptr(), _status(q.device).data_ptr(), _lib.stream_ptr(q.device))
     _lib.check(code, "swa_fwd")
+    _watch_status(q.device)
     if os.environ.get("SWA_DEBUG_SYNC"):
         check_status()
     return o, lse
@@ -162,6 +194,7 @@ def swa_backward(q, k, v, o, lse, do, rope, b_size, t_height, t_width, row_size,
     (gradients of the un-rotated q and k when ``rope`` is given).  ``out``: optional
     ``(dq, dk, dv)`` tensors or strided views to write into (e.g. the three slices of one
     packed ``[B,N,3,H,d]`` gradient buffer)."""
+    _poll_status()        # e.g. the forward of this very step: its status copy has usually arrived by now
     B, H, N, _ = q.shape
     q, k, v, o, do = _materialise(q, k, v, o, do)   # e.g. the expanded (stride-0) gradient of ``o.sum()``
     pad = padded_head_dims(q, v, rope, b_size, t_height, t_width, row_size, col_size, sm_scale, impl)
@@ -194,6 +227,7 @@ def swa_backward(q, k, v, o, lse, do, rope, b_size, t_height, t_width, row_size,
         _lib.check(_lib.lib.swa_bwd_dkdv(C.byref(g), _ref(r), C.byref(tq), C.byref(tk), C.byref(tv), C.byref(tdo),
                                          lse.data_ptr(), delta.data_ptr(), C.byref(tdk), C.byref(tdv), status, st),
                    "swa_bwd_dkdv")
+    _watch_status(q.device)
     if os.environ.get("SWA_DEBUG_SYNC"):
         check_status()
     return dq, dk, dv
@@ -226,6 +260,7 @@ def swa_forward_rot(q, k, v, rope, b_size, t_height, t_width, row_size, col_size
                                     lse.data_ptr(), C.byref(tqr), C.byref(tkr), _status(q.device).data_ptr(),
                                     _lib.stream_ptr(q.device))
     _lib.check(code, "swa_fwd_rot")
+    _watch_status(q.device)
     if os.environ.get("SWA_DEBUG_SYNC"):
         check_status()
     return o, lse, q_rot, k_rot
@@ -236,6 +271,7 @@ def swa_backward_rot(q_rot, k_rot, v, o, lse, do, rope, b_size, t_height, t_widt
     """Backward pass on the rotated copies ``swa_forward_rot`` left behind: delta, ``swa_bwd_dq_rot``,
     ``swa_bwd_dkdv_rot``.  Returns ``(dq, dk, dv)``, gradients of the UN-rotated q and k (the kernels rotate dq and
     dk back in their epilogues).  ``out`` as in ``swa_backward``."""
+    _poll_status()
     B, H, N, _ = q_rot.shape
     q_rot, k_rot, v, o, do = _materialise(q_rot, k_rot, v, o, do)
     with torch.cuda.device(q_rot.device):
@@ -257,6 +293,7 @@ def swa_backward_rot(q_rot, k_rot, v, o, lse, do, rope, b_size, t_height, t_widt
         _lib.check(_lib.lib.swa_bwd_dkdv_rot(C.byref(g), C.byref(r), C.byref(tq), C.byref(tk), C.byref(tv),
                                              C.byref(tdo), lse.data_ptr(), delta.data_ptr(), C.byref(tdk),
                                              C.byref(tdv), status, st), "swa_bwd_dkdv_rot")
+    _watch_status(q_rot.device)
     if os.environ.get("SWA_DEBUG_SYNC"):
         check_status()
     return dq, dk, dv
@@ -280,6 +317,7 @@ def swa_backward_noalloc(q, k, v, o, lse, do, rope, b_size, t_height, t_width, r
                                         C.byref(tdo), lse.data_ptr(), C.byref(tdq), C.byref(tdk), C.byref(tdv),
                                         _status(q.device).data_ptr(), _lib.stream_ptr(q.device))
     _lib.check(code, "swa_bwd_noalloc")
+    _watch_status(q.device)
     return dq, dk, dv
 
 

@@ -168,6 +168,11 @@ int swa_select_impl(const swa_geom_t* g, const swa_rope_t* rope, int32_t which);
  * alignment pad included), tensor-memory columns used.  Negative return: the shape runs on the SIMT kernels. */
 int swa_describe_plan(const swa_geom_t* g, const swa_rope_t* rope, int32_t which, int32_t* out);
 
+/* The planner's experiment knobs (environment variables SWA_TC_*) are read once per process and tile plans are
+ * cached per geometry; this re-reads the environment and drops the cache.  A diagnostic without counterpart in
+ * the reference (its Triton autotuner keeps a comparable per-shape cache, src/tiled_swa.py:135-142); host-only. */
+void swa_refresh_env(void);
+
 /* Number of kernel launches this library has enqueued from the calling process. */
 int64_t swa_launch_count(void);
 

@@ -25,7 +25,7 @@ def test_library_exports_every_declared_symbol():
     assert set(names) == set(_lib.EXPORTS)
     for n in names:
         assert hasattr(_lib.lib, n), n
-    assert _lib.lib.swa_version() == 1
+    assert _lib.lib.swa_version() == 2
 
 
 def _geom(**kw):
@@ -161,23 +161,69 @@ def test_describe_plan_rejects_bad_arguments():
 
 def test_planner_refuses_overrides_beyond_tensor_memory(monkeypatch):
     """The experiment knobs cannot produce a plan that overflows the 512 tensor-memory columns or the barrier
-    arrays: such a plan is refused on the host instead of being launched."""
+    arrays, or a block narrower than the halo: such a plan is refused on the host instead of being launched.  The
+    library reads its knobs once per process, so every change is followed by swa_refresh_env."""
     g = _geom(t_height=128, t_width=128, row_size=6, col_size=6)
     assert _plan(g, None, 1)[0] == 0
-    monkeypatch.setenv("SWA_TC_NMAX", "160")
-    monkeypatch.setenv("SWA_TC_KR", "8")
-    monkeypatch.setenv("SWA_TC_KW", "20")
-    monkeypatch.setenv("SWA_TC_TH", "16")
-    assert _plan(g, None, 1)[0] < 0 and _plan(g, None, 2)[0] < 0      # 2 pairs x 2 x 160 columns do not fit
-    monkeypatch.setenv("SWA_TC_NSB", "2")
-    code, p = _plan(g, None, 0)                                          # forward: 2 x 160 + 128 columns fit
-    assert code == 0 and p[4] == 160 and p[11] == 448
-    monkeypatch.setenv("SWA_TC_NSB", "3")
-    assert _plan(g, None, 0)[0] < 0
-    for k in ("SWA_TC_NMAX", "SWA_TC_KR", "SWA_TC_KW", "SWA_TC_NSB"):
-        monkeypatch.delenv(k)
-    monkeypatch.setenv("SWA_TC_STAGES", "9")
-    assert _plan(g, None, 0)[0] < 0
+
+    def knobs(**kw):
+        for k in ("SWA_TC_NMAX", "SWA_TC_KR", "SWA_TC_KW", "SWA_TC_TH", "SWA_TC_NSB", "SWA_TC_STAGES"):
+            monkeypatch.delenv(k, raising=False)
+        for k, v in kw.items():
+            monkeypatch.setenv("SWA_TC_" + k, str(v))
+        _lib.lib.swa_refresh_env()
+
+    try:
+        knobs(NMAX=160, KR=8, KW=20, TH=16)
+        assert _plan(g, None, 1)[0] < 0 and _plan(g, None, 2)[0] < 0      # 2 pairs x 2 x 160 columns do not fit
+        knobs(NMAX=160, KR=8, KW=20, TH=16, NSB=2)
+        code, p = _plan(g, None, 0)                                          # forward: 2 x 160 + 128 columns fit
+        assert code == 0 and p[4] == 160 and p[11] == 448
+        knobs(NMAX=160, KR=8, KW=20, TH=16, NSB=3)
+        assert _plan(g, None, 0)[0] < 0
+        knobs(TH=16, KR=4, KW=16)                                            # narrower than the 20-column halo
+        assert _plan(g, None, 0)[0] < 0
+        knobs(STAGES=9)
+        assert _plan(g, None, 0)[0] < 0
+    finally:
+        knobs()
+    assert _plan(g, None, 0)[0] == 0
+
+
+def test_plans_are_cached_and_cheap():
+    """The second request for a plan is a map lookup: far below the cost of the search (host-only timing, generous
+    bound), and identical to the first."""
+    import time
+    g = _geom(t_height=96, t_width=80, row_size=5, col_size=7)
+    _lib.lib.swa_refresh_env()
+    t0 = time.perf_counter()
+    first = _plan(g, None, 2)
+    t1 = time.perf_counter()
+    for _ in range(200):
+        again = _plan(g, None, 2)
+    t2 = time.perf_counter()
+    assert again == first and first[0] == 0
+    assert (t2 - t1) / 200 < 20e-6
+
+
+def test_broadcast_strides_fall_back_to_simt():
+    """A 16-bit tensor broadcast over batch or heads (stride 0) cannot be described by a tensor map: AUTO demotes the
+    call to the SIMT kernels instead of failing in the map encoder; a forced tensor-core request is rejected."""
+    g = _geom(B=2, H=3, t_height=16, t_width=16, row_size=2, col_size=2)
+    ok = _lib.Tensor4()
+    ok.ptr = 256
+    for i, st in enumerate((3 * 256 * 64, 256 * 64, 64, 1)):
+        ok.stride[i] = st
+    bc = _lib.Tensor4()
+    bc.ptr = 256
+    for i, st in enumerate((0, 256 * 64, 64, 1)):
+        bc.stride[i] = st
+    lse = C.c_void_p(512)
+    g_tc = _geom(B=2, H=3, t_height=16, t_width=16, row_size=2, col_size=2, impl="tc")
+    before = _lib.launch_count()
+    code = _lib.lib.swa_fwd(C.byref(g_tc), None, C.byref(bc), C.byref(ok), C.byref(ok), C.byref(ok), lse, None, None)
+    assert code < 0 and b"positive strides" in _lib.lib.swa_last_error()
+    assert _lib.launch_count() == before
 
 
 def test_rope_mode_switch():

@@ -4,6 +4,8 @@ the CPU oracle and the stored reference outputs.
 Ground truth for bf16/fp16 is the oracle evaluated in fp32 on the rounded inputs.
 Tolerances: max-abs 2e-2 and mean-rel 5e-3 for bf16/fp16, 1e-4 for fp32.
 """
+import ctypes as C
+
 import pytest
 import torch
 
@@ -358,7 +360,7 @@ def test_random_shapes_tensor_core_vs_simt():
             assert torch.isfinite(c.float()).all(), f"{what} {n}: non-finite"
             err = (a.float() - c.float()).abs().max().item()
             assert err < 4e-2, f"{what} {n}: max abs {err:.3e}"
-        if n_tc % 2 == 0 and N <= 3000:
+        if n_tc % 2 == 0 and N <= 3000 and wr + wc > 0:      # (a 1 x 1 window has dq = dk = 0: no relative error to speak of)
             # every second shape the tensor-core kernels take also goes to the oracle (windowed form of the same
             # arithmetic), on both paths: d_qk != d_v with 32 rotated pairs, wr != wc up to 12 / 10, three heads
             rope_cpu = (None, None, None) if rope is None else tuple(t.cpu() for t in rope)
@@ -555,6 +557,35 @@ def test_wide_halo_runs_on_tensor_cores(bs, th, tw, rs, cs):
     got, _ = run_gpu(q, k, v, do, rope, win, 0.125)
     want = orc.fused_ref(q.float(), k.float(), v.float(), do.float(), *rope, *win, 0.125)
     assert_close(got, want, torch.bfloat16, what=f"wide halo b={bs} col={cs}")
+
+
+@pytest.mark.parametrize("bs,th,tw,rs,cs,d_qk,d_v", [(16, 8, 12, 1, 4, 64, 64), (16, 6, 14, 2, 5, 64, 128),
+                                                    (32, 5, 9, 1, 3, 128, 64), (4, 9, 60, 1, 25, 64, 64)])
+def test_halos_wider_than_a_block_stay_on_tensor_cores(bs, th, tw, rs, cs, d_qk, d_v):
+    """Halos of 150 to 250 token columns -- wider than any streamed block (128 tokens at most): kernel-9 / -11 sized
+    windows over tiles of 16 or 32 tokens, the regime of the reference's own harness (src/tiled_swa.py:736-757).  The
+    kernels without streamed rotation walk such a halo in several column blocks per row band; without RoPE and on
+    the hand-off path nothing falls to the SIMT kernels any more."""
+    torch.manual_seed(bs + cs)
+    B, H = 1, 2
+    N = bs * th * tw
+    q, k = (torch.randn(B, H, N, d_qk).to(torch.bfloat16) for _ in range(2))
+    v, do = (torch.randn(B, H, N, d_v).to(torch.bfloat16) for _ in range(2))
+    win, sc = (bs, th, tw, rs, cs), d_qk ** -0.5
+    idx = torch.arange(N, dtype=torch.int32) // bs          # every token of a tile shares the tile's position
+    idx = (((idx // tw) << 16) | (idx % tw)).to(torch.int32)
+    rope = (idx, swa.make_cs_table(16, th), swa.make_cs_table(16, tw))
+    g = swa.tiled_swa._geom(q, v, *win, sc, "auto")
+    plan = (C.c_int32 * 12)()
+    r = swa._lib.make_rope(*rope)
+    for which in (3, 4, 5):
+        assert swa._lib.lib.swa_describe_plan(C.byref(g), C.byref(r), which, plan) == 0, "hand-off kernels must take it"
+        assert plan[3] < (2 * cs + 1) * bs                  # block narrower than the halo: several column blocks
+    for rp, path in ((None, "fused"), (rope, "handoff")):
+        got, _ = run_gpu(q, k, v, do, rp, win, sc, impl="tc", path=path)
+        want = orc.fused_ref(q.float(), k.float(), v.float(), do.float(), *(rp or (None, None, None)), *win, sc,
+                             windowed=True)
+        assert_close(got, want, torch.bfloat16, what=f"wide halo b={bs} col={cs} {path}")
 
 
 def test_expanded_gradient_keeps_tensor_core_path():

@@ -37,13 +37,15 @@ def _run_both(cfg_name, B, H, grid=None):
     g = ts._geom(q, v, *c["win"], c["sm_scale"], "auto")
     r = _lib.make_rope(*rope)
     t4 = [_lib.tensor4(t) for t in (q, k, v, o, do, *outs)]
-    before = torch.cuda.memory_allocated(DEV)
+    torch.cuda.synchronize()
+    n_allocs = lambda: torch.cuda.memory_stats(DEV).get("allocation.all.allocated", 0)   # allocations so far (a count)
+    before = n_allocs()
     code = _lib.lib.swa_bwd_noalloc(C.byref(g), C.byref(r), *(C.byref(t) for t in t4[:5]), lse.data_ptr(),
                                     *(C.byref(t) for t in t4[5:]), ts._status(torch.device(DEV)).data_ptr(),
                                     _lib.stream_ptr(torch.device(DEV)))
     assert code == 0, _lib.lib.swa_last_error().decode()
     torch.cuda.synchronize()
-    assert torch.cuda.memory_allocated(DEV) == before
+    assert n_allocs() == before, "the allocation-free entry point must not allocate device memory"
     swa.check_status()
     return want, outs
 
