@@ -303,8 +303,8 @@ bool make_plan_uncached(const swa_geom_t* g, const swa_rope_t* rope, int which, 
 }
 
 // Plan of the kernels that rotate no streamed row (rotation handed on between the kernels, or no RoPE): the
-// tile shape of the problem without RoPE; the tables (needed once per item only) are staged when that costs
-// neither block size nor a stage of the ring.
+// tile shape of the problem without RoPE; the tables (read once per item, in the epilogue) are staged when that
+// costs no block size and leaves at least three stages of the ring.
 bool make_plan(const swa_geom_t* g, const swa_rope_t* rope, int which, Plan* out) {
   const PlanKey key = plan_key(g, rope, which, false);
   bool ok = false;
@@ -321,8 +321,10 @@ bool make_plan_prerot_uncached(const swa_geom_t* g, const swa_rope_t* rope, int 
   Plan with, without;
   long cw = 0, cn = 0;
   const bool ok_n = make_plan_tab(g, nullptr, which, 0, &without, &cn, true);
-  if (ok_n && tab && make_plan_tab(g, nullptr, which, tab, &with, &cw, true) && cw <= cn && with.stages >= without.stages &&
-      with.TH == without.TH) {
+  // (measured: a fourth or fifth stage of the ring is worth nothing here, table rows fetched from L2 inside the
+  // epilogue cost 0.2 to 0.3 ms per launch at the default workload)
+  if (ok_n && tab && make_plan_tab(g, nullptr, which, tab, &with, &cw, true) && cw <= cn &&
+      (with.stages >= without.stages || with.stages >= 3) && with.TH == without.TH) {
     *out = with;
     return true;
   }

@@ -41,48 +41,6 @@ struct Bwd2Shared {
   int abort_site;
 };
 
-// Inverse rotation of one segment (R pairs (i, i + R)) of a row held in registers; `pos` is the token's
-// row of the cos/sin table (negative: not rotated).
-// TABS: the table row is read from the copy staged in shared memory (`tab_addr` = shared-space address of the table).
-template <int RE, bool TABS>
-__device__ __forceinline__ void inv_rotate_segment(float* v, int pos, const float* __restrict__ table, uint32_t tab_addr) {
-  if (pos < 0) return;
-  const float4* t4 = reinterpret_cast<const float4*>(table + (int64_t)pos * RE * 2);
-  const uint32_t ta = tab_addr + (uint32_t)pos * rope_tab_stride(RE);
-#pragma unroll
-  for (int i = 0; i < RE; i += 2) {
-    float4 c;                                            // (cos, sin) of pairs i and i + 1
-    if constexpr (TABS) {
-      const uint4 u = ptx::lds128(ta + (i >> 1) * 16);
-      c = make_float4(__uint_as_float(u.x), __uint_as_float(u.y), __uint_as_float(u.z), __uint_as_float(u.w));
-    } else {
-      c = __ldg(t4 + (i >> 1));
-    }
-    const float a0 = v[i], b0 = v[RE + i], a1 = v[i + 1], b1 = v[RE + i + 1];
-    v[i] = a0 * c.x + b0 * c.y;
-    v[RE + i] = b0 * c.x - a0 * c.y;
-    v[i + 1] = a1 * c.z + b1 * c.w;
-    v[RE + i + 1] = b1 * c.z - a1 * c.w;
-  }
-}
-
-// 64 consecutive accumulator columns of this thread's row: tensor memory -> registers.
-__device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t* r) {
-  ptx::tmem_ld16(taddr, r);
-  ptx::tmem_ld16(taddr + 16, r + 16);
-  ptx::tmem_ld16(taddr + 32, r + 32);
-  ptx::tmem_ld16(taddr + 48, r + 48);
-}
-
-template <bool BF16>
-__device__ __forceinline__ void store64(void* dst, const float* v) {
-  uint4* d = reinterpret_cast<uint4*>(dst);
-#pragma unroll
-  for (int u = 0; u < 8; ++u)
-    d[u] = make_uint4(pack2<BF16>(v[8 * u], v[8 * u + 1]), pack2<BF16>(v[8 * u + 2], v[8 * u + 3]),
-                      pack2<BF16>(v[8 * u + 4], v[8 * u + 5]), pack2<BF16>(v[8 * u + 6], v[8 * u + 7]));
-}
-
 // NE: width of the inverse rotation of dQ / dK in the epilogue (n_rdim / 8; 0 = none); TABS: the cos/sin
 // tables are staged in shared memory (the planner does that when it costs no stage of the block ring).
 template <bool BF16, bool DKDV, int NE, bool TABS>
@@ -473,8 +431,11 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
     const bool row_on = t < N;
     const int jr = t / pl.KW, jc = t % pl.KW;                     // this thread's row inside every streamed block
 
-    // Epilogue of one item: this thread's row of the accumulators -> registers (64 columns at a time), tensor
-    // memory released as soon as the last column is read, then scaling, inverse rotation and the stores.
+    // Epilogue of one item: this thread's row of the accumulators goes tensor memory -> registers -> global 16 columns
+    // (and, where rotated, their 16 partner columns) at a time.  Only a few dozen values are ever live: holding a
+    // whole 64-column row made the rotating variants of this kernel 0.2 ms per launch slower than the plain ones
+    // (register pressure in one role degrades the code of all roles of a kernel).  Tensor memory is released when
+    // the last column has been read; the accumulating MMAs of the next item are issued a whole compute phase later.
     int32_t pend_packed = -1;                        // packed RoPE index of this thread's row of the pending item
     auto epilogue = [&](int item, int it) {
       const int bh = item / tiles_per_head, bi = bh / p.H, hi = bh - bi * p.H;
@@ -485,47 +446,88 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
       int irow = -1, icol = -1;
       if (rope_on && t_in) decode_idx(pend_packed, p.rope.max_h, p.rope.max_w, irow, icol);
       T* qk_row = (T*)out_qk.ptr + bi * out_qk.s0 + hi * out_qk.s1 + tok * out_qk.s2;
+      const int dqk = 64 * p.qch;
       trace_ev(p, 5, tn, t == 0 && it >= p.trace_it, 0 * 16 + (it & 15));
       wait_spin(&sh->acc_full, it & 1, 9);
       trace_ev(p, 5, tn, t == 0 && it >= p.trace_it, 1 * 16 + (it & 15));
       if (ok) {
         tc_fence_after();
-        float v[64];                                 // 64 accumulator columns of this thread's row
-        uint32_t* const a = reinterpret_cast<uint32_t*>(v);
-        // dV first, the rotated accumulator last: tensor memory is released before the rotation and the stores
+        // 16 plain columns: scale, convert, store
+        auto plain16 = [&](uint32_t taddr, T* dst, float mul, bool last) {
+          uint32_t a[16];
+          float v[16];
+          tmem_ld16(taddr, a);
+          tmem_wait_ld();
+          if (last) { tc_fence_before(); mbar_arrive(&sh->acc_free); }
+#pragma unroll
+          for (int e = 0; e < 16; ++e) v[e] = __uint_as_float(a[e]) * mul;
+          if (t_in) store16<BF16>(dst, v);
+        };
+        // dV first, the rotated accumulator last
         if constexpr (DKDV) {
           T* v_row = (T*)out_v.ptr + bi * out_v.s0 + hi * out_v.s1 + tok * out_v.s2;
 #pragma unroll 1
-          for (int r = 0; r < p.vch; ++r) {
-            tmem_ld64(lane_base + acc_v + 64 * r, a);
-            tmem_wait_ld();
-            if (t_in) store64<BF16>(v_row + 64 * r, v);
-          }
+          for (int c = 0; c < 64 * p.vch; c += 16) plain16(lane_base + acc_v + c, v_row + c, 1.f, false);
         }
+        const uint32_t aqk = lane_base + acc_qk;
+        int c_plain = 0;                              // first column that is not rotated
+        if constexpr (NE > 0) {
+          if (rope_on) {
+            // rotated dims [0, 4R): row-angle pairs (i, i + R) in [0, 2R), column-angle pairs in [2R, 4R).  One step =
+            // NP pairs: columns [c0, c0 + NP) with their partners [c0 + R, c0 + R + NP).
+            constexpr int NP = R >= 16 ? 16 : 8;
+            c_plain = 4 * R;
 #pragma unroll 1
-        for (int r = 0; r < p.qch; ++r) {
-          tmem_ld64(lane_base + acc_qk + 64 * r, a);
-          tmem_wait_ld();
-          if (r == p.qch - 1) {                      // everything has been read: the next item may accumulate
-            tc_fence_before();
-            mbar_arrive(&sh->acc_free);
-            trace_ev(p, 5, tn, t == 0 && it >= p.trace_it, 2 * 16 + (it & 15));
-          }
+            for (int seg = 0; seg < 2; ++seg) {
+              const int pos = seg ? icol : irow;
+#pragma unroll 1
+              for (int i0 = 0; i0 < R; i0 += NP) {
+                const int c0 = 2 * seg * R + i0;
+                uint32_t a[NP], b[NP];
+                float x0[NP], x1[NP];
+                if constexpr (NP == 16) { tmem_ld16(aqk + c0, a); tmem_ld16(aqk + c0 + R, b); }
+                else { tmem_ld8(aqk + c0, a); tmem_ld8(aqk + c0 + R, b); }
+                tmem_wait_ld();
+                if (seg == 1 && i0 + NP >= R && c_plain >= dqk) { tc_fence_before(); mbar_arrive(&sh->acc_free); }
 #pragma unroll
-          for (int e = 0; e < 64; ++e) v[e] *= scale;
-          if constexpr (NE > 0) {
-            // rotated dims [0, 4R): row-angle pairs (i, i + R) in [0, 2R), column-angle pairs in [2R, 4R)
-            if (rope_on) {
-              if constexpr (R == 32) {
-                if (r < 2) inv_rotate_segment<R, TABS>(v, r ? icol : irow, r ? p.rope.col_cs : p.rope.row_cs, r ? tab_col : tab_row);
-              } else if (r == 0) {
-                inv_rotate_segment<R, TABS>(v, irow, p.rope.row_cs, tab_row);
-                inv_rotate_segment<R, TABS>(v + 2 * R, icol, p.rope.col_cs, tab_col);
+                for (int e = 0; e < NP; ++e) { x0[e] = __uint_as_float(a[e]) * scale; x1[e] = __uint_as_float(b[e]) * scale; }
+                if (pos >= 0) {
+                  const float4* t4 = reinterpret_cast<const float4*>((seg ? p.rope.col_cs : p.rope.row_cs) + ((int64_t)pos * R + i0) * 2);
+                  const uint32_t ta = (seg ? tab_col : tab_row) + (uint32_t)pos * rope_tab_stride(R) + i0 * 8;
+#pragma unroll
+                  for (int e = 0; e < NP; e += 2) {
+                    float4 c;                          // (cos, sin) of pairs e and e + 1
+                    if constexpr (TABS) {
+                      const uint4 u = lds128(ta + (e >> 1) * 16);
+                      c = make_float4(__uint_as_float(u.x), __uint_as_float(u.y), __uint_as_float(u.z), __uint_as_float(u.w));
+                    } else {
+                      c = __ldg(t4 + (e >> 1));
+                    }
+                    const float p0 = x0[e], q0 = x1[e], p1 = x0[e + 1], q1 = x1[e + 1];
+                    x0[e] = p0 * c.x + q0 * c.y;
+                    x1[e] = q0 * c.x - p0 * c.y;
+                    x0[e + 1] = p1 * c.z + q1 * c.w;
+                    x1[e + 1] = q1 * c.z - p1 * c.w;
+                  }
+                }
+                if (t_in) {
+                  if constexpr (NP == 16) {
+                    store16<BF16>(qk_row + c0, x0);
+                    store16<BF16>(qk_row + c0 + R, x1);
+                  } else {
+                    *reinterpret_cast<uint4*>(qk_row + c0) = make_uint4(pack2<BF16>(x0[0], x0[1]), pack2<BF16>(x0[2], x0[3]),
+                                                                        pack2<BF16>(x0[4], x0[5]), pack2<BF16>(x0[6], x0[7]));
+                    *reinterpret_cast<uint4*>(qk_row + c0 + R) = make_uint4(pack2<BF16>(x1[0], x1[1]), pack2<BF16>(x1[2], x1[3]),
+                                                                            pack2<BF16>(x1[4], x1[5]), pack2<BF16>(x1[6], x1[7]));
+                  }
+                }
               }
             }
           }
-          if (t_in) store64<BF16>(qk_row + 64 * r, v);
         }
+#pragma unroll 1
+        for (int c = c_plain; c < dqk; c += 16) plain16(aqk + c, qk_row + c, scale, c + 16 >= dqk);
+        trace_ev(p, 5, tn, t == 0 && it >= p.trace_it, 2 * 16 + (it & 15));
       }
       trace_ev(p, 5, tn, t == 0 && it >= p.trace_it, 3 * 16 + (it & 15));
     };
