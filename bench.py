@@ -180,25 +180,40 @@ def cpu_sample_step(case, cfg, n_slices):
     return o
 
 
+def cpu_band_rows(cfg):
+    """Grid rows of the CPU sample: the whole grid up to 16384 tokens, else a band of full-width rows of about that
+    many tokens (the dense [N, N] mask of the 256 x 256 grid alone would be 17 GB)."""
+    G = cfg["grid"]
+    return G if G * G <= 16384 else max(cfg["w"], 16384 // G)
+
+
 def cpu_case(cfg, n_slices):
     """Seeded CPU inputs of `n_slices` (batch, head) slices, built like the parity tests build theirs."""
     from oracle import swa_oracle as orc
     G = cfg["grid"]
-    N = G * G
+    rows = cpu_band_rows(cfg)
+    N = rows * G
     q, k, v, do = orc.seeded_inputs(1, n_slices, N, cfg["d_qk"], cfg["d_v"], cfg["dtype"], 0)
-    idx = orc.encode_idx(G, G)
+    idx = orc.encode_idx(rows, G)
     if cfg["drop"] > 0:
         g = torch.Generator().manual_seed(1000)
         idx[torch.bernoulli(torch.full((N,), cfg["drop"]), generator=g).bool()] = -1
     tab = orc.make_cs_table(cfg["rope_dims"] // 4, G, 10000.0)
     half = (cfg["w"] - 1) // 2
-    return dict(q=q, k=k, v=v, do=do, idx=idx, row_cs=tab, col_cs=tab.clone(), win=(1, G, G, half, half),
+    return dict(q=q, k=k, v=v, do=do, idx=idx, row_cs=tab, col_cs=tab.clone(), win=(1, rows, G, half, half),
                 sm_scale=cfg["d_qk"] ** -0.5)
+
+
+def cpu_sample_text(cfg, n_slices, workload):
+    rows, G = cpu_band_rows(cfg), cfg["grid"]
+    what = f"{n_slices} (batch,head) slice(s) of {workload}" if rows == G else \
+        f"a band of {rows} full rows ({rows * G} tokens) of {n_slices} (batch,head) slice(s) of {workload}"
+    return what + " per step, dense [N,N] mask + SDPA + autograd, fp32"
 
 
 def cpu_slices_for(cfg):
     """(batch, head) slices per CPU step: dense attention is O(N^2) per slice."""
-    N = cfg["grid"] ** 2
+    N = cpu_band_rows(cfg) * cfg["grid"]
     return 1 if N >= 8192 else (4 if N >= 4096 else 8)
 
 
@@ -209,7 +224,7 @@ def run_cpu_reference(cfg, steps, warmup):
     n_slices = cpu_slices_for(cfg)
     case = cpu_case(cfg, n_slices)
     half = (cfg["w"] - 1) // 2
-    fwd, bwd = windowed_flops(n_slices, cfg["grid"] ** 2, 1, half, half, cfg["d_qk"], cfg["d_v"])
+    fwd, bwd = windowed_flops(n_slices, cpu_band_rows(cfg) * cfg["grid"], 1, half, half, cfg["d_qk"], cfg["d_v"])
     flops = fwd + (bwd if cfg["bwd"] else 0.0)
     for _ in range(warmup):
         cpu_sample_step(case, cfg, n_slices)
@@ -297,8 +312,7 @@ def main():
             return 0
         steps, warmup = max(1, min(args.steps, 10)), max(1, min(args.warmup, 2))
         tf, ms, cores, n_slices, _ = run_cpu_reference(cfg, steps, warmup)
-        sample = (f"{n_slices} (batch,head) slice(s) of {args.workload} per step, dense [N,N] mask + SDPA + autograd, "
-                  f"fp32, {steps} steps")
+        sample = f"{cpu_sample_text(cfg, n_slices, args.workload)}, {steps} steps"
         print(json.dumps({
             "impl": "reference", "metric": METRIC, "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus,
             "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
@@ -576,8 +590,8 @@ def main():
     if world == 1 and not args.no_cpu_baseline:
         tf, ms, cores, n_slices, n_cpu_steps = run_cpu_reference(cfg, steps=None, warmup=1)
         cpu_baseline = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
-                        "sample": f"{n_slices} (batch,head) slice(s) of {args.workload} per step, dense [N,N] mask + "
-                                  f"SDPA + autograd, fp32, {n_cpu_steps} steps, {ms:.0f} ms/step"}
+                        "sample": f"{cpu_sample_text(cfg, n_slices, args.workload)}, {n_cpu_steps} steps, "
+                                  f"{ms:.0f} ms/step"}
 
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,

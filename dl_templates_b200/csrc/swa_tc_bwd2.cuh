@@ -435,7 +435,7 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
     // (and, where rotated, their 16 partner columns) at a time.  Only a few dozen values are ever live: holding a
     // whole 64-column row made the rotating variants of this kernel 0.2 ms per launch slower than the plain ones
     // (register pressure in one role degrades the code of all roles of a kernel).  Tensor memory is released when
-    // the last column has been read; the accumulating MMAs of the next item are issued a whole compute phase later.
+    // the last column has been read.
     int32_t pend_packed = -1;                        // packed RoPE index of this thread's row of the pending item
     auto epilogue = [&](int item, int it) {
       const int bh = item / tiles_per_head, bi = bh / p.H, hi = bh - bi * p.H;
@@ -447,86 +447,106 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
       if (rope_on && t_in) decode_idx(pend_packed, p.rope.max_h, p.rope.max_w, irow, icol);
       T* qk_row = (T*)out_qk.ptr + bi * out_qk.s0 + hi * out_qk.s1 + tok * out_qk.s2;
       const int dqk = 64 * p.qch;
+      // rotated dims [0, 4R): row-angle pairs (i, i + R) in [0, 2R), column-angle pairs in [2R, 4R).  One rotated step =
+      // NP pairs: columns [c0, c0 + NP) with their partners [c0 + R, c0 + R + NP).
+      constexpr int NP = R >= 16 ? 16 : 8;
+      constexpr int SPS = R / NP;                      // steps per segment
+      const int nrot = (NE > 0 && rope_on) ? 2 * SPS : 0;
+      // Tables in global memory (too large to stage): the (cos, sin) values of a step are fetched one step ahead --
+      // those of the first step before the wait for the accumulators -- and the dV columns are stored between the
+      // rotated steps, so that the L2 latency of the fetch is covered by work instead of being paid once per step.
+      float4 cs[NP / 2];
+      auto fetch = [&](int r) {
+        if constexpr (NE > 0 && !TABS) {
+          const int seg = r / SPS, i0 = (r - seg * SPS) * NP, pos = seg ? icol : irow;
+          if (pos >= 0) {
+            const float4* t4 = reinterpret_cast<const float4*>((seg ? p.rope.col_cs : p.rope.row_cs) + ((int64_t)pos * R + i0) * 2);
+#pragma unroll
+            for (int e = 0; e < NP / 2; ++e) cs[e] = __ldg(t4 + e);
+          }
+        }
+      };
+      if (nrot > 0) fetch(0);
       trace_ev(p, 5, tn, t == 0 && it >= p.trace_it, 0 * 16 + (it & 15));
       wait_spin(&sh->acc_full, it & 1, 9);
       trace_ev(p, 5, tn, t == 0 && it >= p.trace_it, 1 * 16 + (it & 15));
       if (ok) {
         tc_fence_after();
         // 16 plain columns: scale, convert, store
+        auto release = [&]() { tc_fence_before(); mbar_arrive(&sh->acc_free); };   // after the last load of the item
         auto plain16 = [&](uint32_t taddr, T* dst, float mul, bool last) {
           uint32_t a[16];
           float v[16];
           tmem_ld16(taddr, a);
           tmem_wait_ld();
-          if (last) { tc_fence_before(); mbar_arrive(&sh->acc_free); }
+          if (last) release();
 #pragma unroll
           for (int e = 0; e < 16; ++e) v[e] = __uint_as_float(a[e]) * mul;
           if (t_in) store16<BF16>(dst, v);
         };
-        // dV first, the rotated accumulator last
-        if constexpr (DKDV) {
-          T* v_row = (T*)out_v.ptr + bi * out_v.s0 + hi * out_v.s1 + tok * out_v.s2;
-#pragma unroll 1
-          for (int c = 0; c < 64 * p.vch; c += 16) plain16(lane_base + acc_v + c, v_row + c, 1.f, false);
-        }
+        [[maybe_unused]] T* v_row = qk_row;
+        if constexpr (DKDV) v_row = (T*)out_v.ptr + bi * out_v.s0 + hi * out_v.s1 + tok * out_v.s2;
+        const int dv = DKDV ? 64 * p.vch : 0;
+        int cv = 0;                                   // next dV column
         const uint32_t aqk = lane_base + acc_qk;
-        int c_plain = 0;                              // first column that is not rotated
+        const bool qk_rest = nrot * 2 * NP < dqk;      // plain columns of dQ / dK behind the rotated ones: read last
         if constexpr (NE > 0) {
-          if (rope_on) {
-            // rotated dims [0, 4R): row-angle pairs (i, i + R) in [0, 2R), column-angle pairs in [2R, 4R).  One step =
-            // NP pairs: columns [c0, c0 + NP) with their partners [c0 + R, c0 + R + NP).
-            constexpr int NP = R >= 16 ? 16 : 8;
-            c_plain = 4 * R;
+          const int v_per_step = nrot > 0 ? ((dv / 16 + nrot - 1) / nrot) * 16 : 0;
 #pragma unroll 1
-            for (int seg = 0; seg < 2; ++seg) {
-              const int pos = seg ? icol : irow;
-#pragma unroll 1
-              for (int i0 = 0; i0 < R; i0 += NP) {
-                const int c0 = 2 * seg * R + i0;
-                uint32_t a[NP], b[NP];
-                float x0[NP], x1[NP];
-                if constexpr (NP == 16) { tmem_ld16(aqk + c0, a); tmem_ld16(aqk + c0 + R, b); }
-                else { tmem_ld8(aqk + c0, a); tmem_ld8(aqk + c0 + R, b); }
-                tmem_wait_ld();
-                if (seg == 1 && i0 + NP >= R && c_plain >= dqk) { tc_fence_before(); mbar_arrive(&sh->acc_free); }
+          for (int r = 0; r < nrot; ++r) {
+            const int seg = r / SPS, i0 = (r - seg * SPS) * NP, pos = seg ? icol : irow;
+            const int c0 = 2 * seg * R + i0;
+            uint32_t a[NP], b[NP];
+            float x0[NP], x1[NP];
+            if constexpr (NP == 16) { tmem_ld16(aqk + c0, a); tmem_ld16(aqk + c0 + R, b); }
+            else { tmem_ld8(aqk + c0, a); tmem_ld8(aqk + c0 + R, b); }
+            tmem_wait_ld();
+            if (r == nrot - 1 && cv >= dv && !qk_rest) release();
 #pragma unroll
-                for (int e = 0; e < NP; ++e) { x0[e] = __uint_as_float(a[e]) * scale; x1[e] = __uint_as_float(b[e]) * scale; }
-                if (pos >= 0) {
-                  const float4* t4 = reinterpret_cast<const float4*>((seg ? p.rope.col_cs : p.rope.row_cs) + ((int64_t)pos * R + i0) * 2);
-                  const uint32_t ta = (seg ? tab_col : tab_row) + (uint32_t)pos * rope_tab_stride(R) + i0 * 8;
+            for (int e = 0; e < NP; ++e) { x0[e] = __uint_as_float(a[e]) * scale; x1[e] = __uint_as_float(b[e]) * scale; }
+            if (pos >= 0) {
+              [[maybe_unused]] const uint32_t ta = (seg ? tab_col : tab_row) + (uint32_t)pos * rope_tab_stride(R) + i0 * 8;
 #pragma unroll
-                  for (int e = 0; e < NP; e += 2) {
-                    float4 c;                          // (cos, sin) of pairs e and e + 1
-                    if constexpr (TABS) {
-                      const uint4 u = lds128(ta + (e >> 1) * 16);
-                      c = make_float4(__uint_as_float(u.x), __uint_as_float(u.y), __uint_as_float(u.z), __uint_as_float(u.w));
-                    } else {
-                      c = __ldg(t4 + (e >> 1));
-                    }
-                    const float p0 = x0[e], q0 = x1[e], p1 = x0[e + 1], q1 = x1[e + 1];
-                    x0[e] = p0 * c.x + q0 * c.y;
-                    x1[e] = q0 * c.x - p0 * c.y;
-                    x0[e + 1] = p1 * c.z + q1 * c.w;
-                    x1[e + 1] = q1 * c.z - p1 * c.w;
-                  }
+              for (int e = 0; e < NP; e += 2) {
+                float4 c;                              // (cos, sin) of pairs e and e + 1
+                if constexpr (TABS) {
+                  const uint4 u = lds128(ta + (e >> 1) * 16);
+                  c = make_float4(__uint_as_float(u.x), __uint_as_float(u.y), __uint_as_float(u.z), __uint_as_float(u.w));
+                } else {
+                  c = cs[e >> 1];
                 }
-                if (t_in) {
-                  if constexpr (NP == 16) {
-                    store16<BF16>(qk_row + c0, x0);
-                    store16<BF16>(qk_row + c0 + R, x1);
-                  } else {
-                    *reinterpret_cast<uint4*>(qk_row + c0) = make_uint4(pack2<BF16>(x0[0], x0[1]), pack2<BF16>(x0[2], x0[3]),
-                                                                        pack2<BF16>(x0[4], x0[5]), pack2<BF16>(x0[6], x0[7]));
-                    *reinterpret_cast<uint4*>(qk_row + c0 + R) = make_uint4(pack2<BF16>(x1[0], x1[1]), pack2<BF16>(x1[2], x1[3]),
-                                                                            pack2<BF16>(x1[4], x1[5]), pack2<BF16>(x1[6], x1[7]));
-                  }
-                }
+                const float p0 = x0[e], q0 = x1[e], p1 = x0[e + 1], q1 = x1[e + 1];
+                x0[e] = p0 * c.x + q0 * c.y;
+                x1[e] = q0 * c.x - p0 * c.y;
+                x0[e + 1] = p1 * c.z + q1 * c.w;
+                x1[e + 1] = q1 * c.z - p1 * c.w;
               }
+            }
+            if (r + 1 < nrot) fetch(r + 1);
+            if (t_in) {
+              if constexpr (NP == 16) {
+                store16<BF16>(qk_row + c0, x0);
+                store16<BF16>(qk_row + c0 + R, x1);
+              } else {
+                *reinterpret_cast<uint4*>(qk_row + c0) = make_uint4(pack2<BF16>(x0[0], x0[1]), pack2<BF16>(x0[2], x0[3]),
+                                                                    pack2<BF16>(x0[4], x0[5]), pack2<BF16>(x0[6], x0[7]));
+                *reinterpret_cast<uint4*>(qk_row + c0 + R) = make_uint4(pack2<BF16>(x1[0], x1[1]), pack2<BF16>(x1[2], x1[3]),
+                                                                        pack2<BF16>(x1[4], x1[5]), pack2<BF16>(x1[6], x1[7]));
+              }
+            }
+            if constexpr (DKDV) {
+              const int stop = cv + v_per_step < dv ? cv + v_per_step : dv;
+#pragma unroll 1
+              for (; cv < stop; cv += 16) plain16(lane_base + acc_v + cv, v_row + cv, 1.f, r == nrot - 1 && cv + 16 >= dv && !qk_rest);
             }
           }
         }
+        if constexpr (DKDV) {
 #pragma unroll 1
-        for (int c = c_plain; c < dqk; c += 16) plain16(aqk + c, qk_row + c, scale, c + 16 >= dqk);
+          for (; cv < dv; cv += 16) plain16(lane_base + acc_v + cv, v_row + cv, 1.f, cv + 16 >= dv && !qk_rest);
+        }
+#pragma unroll 1
+        for (int c = nrot * 2 * NP; c < dqk; c += 16) plain16(aqk + c, qk_row + c, scale, c + 16 >= dqk);
         trace_ev(p, 5, tn, t == 0 && it >= p.trace_it, 2 * 16 + (it & 15));
       }
       trace_ev(p, 5, tn, t == 0 && it >= p.trace_it, 3 * 16 + (it & 15));
