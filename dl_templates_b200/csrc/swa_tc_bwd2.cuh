@@ -472,81 +472,93 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
       trace_ev(p, 5, tn, t == 0 && it >= p.trace_it, 1 * 16 + (it & 15));
       if (ok) {
         tc_fence_after();
-        // 16 plain columns: scale, convert, store
-        auto release = [&]() { tc_fence_before(); mbar_arrive(&sh->acc_free); };   // after the last load of the item
-        auto plain16 = [&](uint32_t taddr, T* dst, float mul, bool last) {
+        [[maybe_unused]] T* v_row = qk_row;
+        if constexpr (DKDV) v_row = (T*)out_v.ptr + bi * out_v.s0 + hi * out_v.s1 + tok * out_v.s2;
+        const int dv = DKDV ? 64 * p.vch : 0;
+        const uint32_t aqk = lane_base + acc_qk;
+        const int v_per_step = nrot > 0 ? (dv / 16 + nrot - 1) / nrot : 0;   // dV chunks stored after every rotated step
+        // ONE loop whose body holds the rotated step and the plain 16-column chunk once each: this code runs once per
+        // item between long stretches of other roles' loops, so it is fetched cold every time, and what it costs is
+        // its size (with a second and third inlined copy of the plain chunk the rotating dK/dV kernels were 8 % slower
+        // than the plain ones although neither the table reads nor the arithmetic could be measured).
+        int r = 0, v_owed = 0;                        // next rotated step; dV chunks still to store before it
+        int cv = 0, cq = nrot * 2 * NP;               // next plain column of dV and of dQ / dK
+#pragma unroll 1
+        while (true) {
+          if (r < nrot && v_owed == 0) {
+            if constexpr (NE > 0) {
+              const int seg = r / SPS, i0 = (r - seg * SPS) * NP, pos = seg ? icol : irow;
+              const int c0 = 2 * seg * R + i0;
+              uint32_t a[NP], b[NP];
+              float x0[NP], x1[NP];
+              if constexpr (NP == 16) { tmem_ld16(aqk + c0, a); tmem_ld16(aqk + c0 + R, b); }
+              else { tmem_ld8(aqk + c0, a); tmem_ld8(aqk + c0 + R, b); }
+              tmem_wait_ld();
+              ++r;
+              if (r == nrot && cv >= dv && cq >= dqk) { tc_fence_before(); mbar_arrive(&sh->acc_free); }
+#pragma unroll
+              for (int e = 0; e < NP; ++e) { x0[e] = __uint_as_float(a[e]) * scale; x1[e] = __uint_as_float(b[e]) * scale; }
+              if (pos >= 0) {
+                [[maybe_unused]] const uint32_t ta = (seg ? tab_col : tab_row) + (uint32_t)pos * rope_tab_stride(R) + i0 * 8;
+#pragma unroll
+                for (int e = 0; e < NP; e += 2) {
+                  float4 c;                            // (cos, sin) of pairs e and e + 1
+                  if constexpr (TABS) {
+                    const uint4 u = lds128(ta + (e >> 1) * 16);
+                    c = make_float4(__uint_as_float(u.x), __uint_as_float(u.y), __uint_as_float(u.z), __uint_as_float(u.w));
+                  } else {
+                    c = cs[e >> 1];
+                  }
+                  const float p0 = x0[e], q0 = x1[e], p1 = x0[e + 1], q1 = x1[e + 1];
+                  x0[e] = p0 * c.x + q0 * c.y;
+                  x1[e] = q0 * c.x - p0 * c.y;
+                  x0[e + 1] = p1 * c.z + q1 * c.w;
+                  x1[e + 1] = q1 * c.z - p1 * c.w;
+                }
+              }
+              if (r < nrot) fetch(r);
+              if (t_in) {
+                if constexpr (NP == 16) {
+                  store16<BF16>(qk_row + c0, x0);
+                  store16<BF16>(qk_row + c0 + R, x1);
+                } else {
+                  *reinterpret_cast<uint4*>(qk_row + c0) = make_uint4(pack2<BF16>(x0[0], x0[1]), pack2<BF16>(x0[2], x0[3]),
+                                                                      pack2<BF16>(x0[4], x0[5]), pack2<BF16>(x0[6], x0[7]));
+                  *reinterpret_cast<uint4*>(qk_row + c0 + R) = make_uint4(pack2<BF16>(x1[0], x1[1]), pack2<BF16>(x1[2], x1[3]),
+                                                                          pack2<BF16>(x1[4], x1[5]), pack2<BF16>(x1[6], x1[7]));
+                }
+              }
+              v_owed = v_per_step;
+            }
+            continue;
+          }
+          // 16 plain columns: dV while there are any, then the un-rotated rest of dQ / dK
+          uint32_t taddr;
+          T* dst;
+          float mul;
+          if (cv < dv) {
+            taddr = lane_base + acc_v + cv; dst = v_row + cv; mul = 1.f;
+            cv += 16;
+            if (v_owed > 0) --v_owed;
+            if (cv >= dv) v_owed = 0;
+          } else if (r < nrot) {
+            v_owed = 0;
+            continue;
+          } else if (cq < dqk) {
+            taddr = aqk + cq; dst = qk_row + cq; mul = scale;
+            cq += 16;
+          } else {
+            break;
+          }
           uint32_t a[16];
           float v[16];
           tmem_ld16(taddr, a);
           tmem_wait_ld();
-          if (last) release();
+          if (r == nrot && cv >= dv && cq >= dqk) { tc_fence_before(); mbar_arrive(&sh->acc_free); }   // the last load
 #pragma unroll
           for (int e = 0; e < 16; ++e) v[e] = __uint_as_float(a[e]) * mul;
           if (t_in) store16<BF16>(dst, v);
-        };
-        [[maybe_unused]] T* v_row = qk_row;
-        if constexpr (DKDV) v_row = (T*)out_v.ptr + bi * out_v.s0 + hi * out_v.s1 + tok * out_v.s2;
-        const int dv = DKDV ? 64 * p.vch : 0;
-        int cv = 0;                                   // next dV column
-        const uint32_t aqk = lane_base + acc_qk;
-        const bool qk_rest = nrot * 2 * NP < dqk;      // plain columns of dQ / dK behind the rotated ones: read last
-        if constexpr (NE > 0) {
-          const int v_per_step = nrot > 0 ? ((dv / 16 + nrot - 1) / nrot) * 16 : 0;
-#pragma unroll 1
-          for (int r = 0; r < nrot; ++r) {
-            const int seg = r / SPS, i0 = (r - seg * SPS) * NP, pos = seg ? icol : irow;
-            const int c0 = 2 * seg * R + i0;
-            uint32_t a[NP], b[NP];
-            float x0[NP], x1[NP];
-            if constexpr (NP == 16) { tmem_ld16(aqk + c0, a); tmem_ld16(aqk + c0 + R, b); }
-            else { tmem_ld8(aqk + c0, a); tmem_ld8(aqk + c0 + R, b); }
-            tmem_wait_ld();
-            if (r == nrot - 1 && cv >= dv && !qk_rest) release();
-#pragma unroll
-            for (int e = 0; e < NP; ++e) { x0[e] = __uint_as_float(a[e]) * scale; x1[e] = __uint_as_float(b[e]) * scale; }
-            if (pos >= 0) {
-              [[maybe_unused]] const uint32_t ta = (seg ? tab_col : tab_row) + (uint32_t)pos * rope_tab_stride(R) + i0 * 8;
-#pragma unroll
-              for (int e = 0; e < NP; e += 2) {
-                float4 c;                              // (cos, sin) of pairs e and e + 1
-                if constexpr (TABS) {
-                  const uint4 u = lds128(ta + (e >> 1) * 16);
-                  c = make_float4(__uint_as_float(u.x), __uint_as_float(u.y), __uint_as_float(u.z), __uint_as_float(u.w));
-                } else {
-                  c = cs[e >> 1];
-                }
-                const float p0 = x0[e], q0 = x1[e], p1 = x0[e + 1], q1 = x1[e + 1];
-                x0[e] = p0 * c.x + q0 * c.y;
-                x1[e] = q0 * c.x - p0 * c.y;
-                x0[e + 1] = p1 * c.z + q1 * c.w;
-                x1[e + 1] = q1 * c.z - p1 * c.w;
-              }
-            }
-            if (r + 1 < nrot) fetch(r + 1);
-            if (t_in) {
-              if constexpr (NP == 16) {
-                store16<BF16>(qk_row + c0, x0);
-                store16<BF16>(qk_row + c0 + R, x1);
-              } else {
-                *reinterpret_cast<uint4*>(qk_row + c0) = make_uint4(pack2<BF16>(x0[0], x0[1]), pack2<BF16>(x0[2], x0[3]),
-                                                                    pack2<BF16>(x0[4], x0[5]), pack2<BF16>(x0[6], x0[7]));
-                *reinterpret_cast<uint4*>(qk_row + c0 + R) = make_uint4(pack2<BF16>(x1[0], x1[1]), pack2<BF16>(x1[2], x1[3]),
-                                                                        pack2<BF16>(x1[4], x1[5]), pack2<BF16>(x1[6], x1[7]));
-              }
-            }
-            if constexpr (DKDV) {
-              const int stop = cv + v_per_step < dv ? cv + v_per_step : dv;
-#pragma unroll 1
-              for (; cv < stop; cv += 16) plain16(lane_base + acc_v + cv, v_row + cv, 1.f, r == nrot - 1 && cv + 16 >= dv && !qk_rest);
-            }
-          }
         }
-        if constexpr (DKDV) {
-#pragma unroll 1
-          for (; cv < dv; cv += 16) plain16(lane_base + acc_v + cv, v_row + cv, 1.f, cv + 16 >= dv && !qk_rest);
-        }
-#pragma unroll 1
-        for (int c = nrot * 2 * NP; c < dqk; c += 16) plain16(aqk + c, qk_row + c, scale, c + 16 >= dqk);
         trace_ev(p, 5, tn, t == 0 && it >= p.trace_it, 2 * 16 + (it & 15));
       }
       trace_ev(p, 5, tn, t == 0 && it >= p.trace_it, 3 * 16 + (it & 15));
