@@ -449,7 +449,7 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
       const int dqk = 64 * p.qch;
       // rotated dims [0, 4R): row-angle pairs (i, i + R) in [0, 2R), column-angle pairs in [2R, 4R).  One rotated step =
       // NP pairs: columns [c0, c0 + NP) with their partners [c0 + R, c0 + R + NP).
-      constexpr int NP = R >= 16 ? 16 : 8;
+      constexpr int NP = (R >= 16 && TABS) ? 16 : 8;   // tables in global memory: 8, the prefetched (cos, sin) values take registers
       constexpr int SPS = R / NP;                      // steps per segment
       const int nrot = (NE > 0 && rope_on) ? 2 * SPS : 0;
       // Tables in global memory (too large to stage): the (cos, sin) values of a step are fetched one step ahead --
