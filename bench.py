@@ -293,6 +293,8 @@ def main():
     ap.add_argument("--verify", action="store_true", help="(default with more than one GPU) rank 0 recomputes every "
                     "rank's first slice from that rank's seed and compares it bitwise with the slice gathered over NCCL")
     ap.add_argument("--no-verify", action="store_true")
+    ap.add_argument("--no-spatial", action="store_true", help="skip the row-sharded leg (more than one GPU: the grid "
+                    "rows of the default workload split across the ranks, halo rows exchanged over NCCL)")
     ap.add_argument("--no-strong", action="store_true", help="skip the strong-scaling leg (the largest configuration, "
                     "256 (batch, head) slices split over the GPUs) that runs after the timed region of the target workload")
     args = ap.parse_args()
@@ -420,6 +422,27 @@ def main():
     families = {n: swa.selected_impl(q, v, rope, *win, sm, which=w_, impl=impl)
                 for n, w_ in (("fwd", 0), ("dq", 1), ("dkdv", 2))}
 
+    # ---------------------------------------------------------------- optional verification gather
+    # Sharded == unsharded, bitwise: every rank contributes the outputs of its FIRST (batch, head) slice; rank 0
+    # regenerates that slice from the rank's seed, runs it alone on its own GPU and compares bit for bit.  Runs right
+    # after the timed region: the un-fused composition leg further down rotates q and k in place and back, which
+    # returns them only to within rounding.
+    verified = None
+    if world > 1 and not args.no_verify:
+        outs = step()
+        mine = torch.cat([t[:, :1].reshape(-1).view(torch.int16 if t.element_size() == 2 else torch.int32).to(torch.int32)
+                          for t in outs])
+        gathered = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(gathered, mine)
+        if rank == 0:
+            verified = True
+            for r in range(world):
+                cr = device_case(cfg, 1, device, seed=r)      # slice 0 of rank r, redrawn from its own seed
+                ref = run_step(swa, cr, impl, handoff, cfg["bwd"])
+                flat = torch.cat([t.reshape(-1).view(torch.int16 if t.element_size() == 2 else torch.int32).to(torch.int32)
+                                  for t in ref])
+                verified = verified and bool(torch.equal(flat, gathered[r]))
+
     # ---------------------------------------------------------------- e2e with host buffers
     e2e = None
     if not args.no_e2e:
@@ -500,24 +523,56 @@ def main():
                   "steps": v_steps}
         swa.check_status()
 
-    # ---------------------------------------------------------------- optional verification gather
-    # Sharded == unsharded, bitwise: every rank contributes the outputs of its FIRST (batch, head) slice; rank 0
-    # regenerates that slice from the rank's seed, runs it alone on its own GPU and compares bit for bit.
-    verified = None
-    if world > 1 and not args.no_verify:
-        outs = step()
-        mine = torch.cat([t[:, :1].reshape(-1).view(torch.int16 if t.element_size() == 2 else torch.int32).to(torch.int32)
-                          for t in outs])
-        gathered = [torch.empty_like(mine) for _ in range(world)]
-        dist.all_gather(gathered, mine)
+    # ---------------------------------------------------------------- row-sharded leg (spatial sharding)
+    # The per-GPU problem of the default workload (all its (batch, head) slices) with its grid ROWS split across the
+    # ranks: every rank holds its band of every slice, halo rows travel over NCCL send / receive into local buffers,
+    # the kernels run on the extended band.  Strong scaling; device-timed, max over ranks.  Rank 0 also compares its
+    # own rows of the first slice with an unsharded run of that slice (tile origins differ: tolerance, not bitwise).
+    spatial = None
+    if world > 1 and not args.no_spatial and rope is not None and args.layout == "bhnd":
+        from dl_templates_b200 import spatial as sp
+        G_ = cfg["grid"]
+        shard = sp.RowShard(G_, G_, half, rank, world)
+        cs_ = device_case(cfg, bh_local, device, seed=0)          # the same problem on every rank
+        own_g = shard.own_tokens_global()
+        loc = {x: cs_[x][:, :, own_g].contiguous() for x in ("q", "k", "v", "do")}
+        first = {x: cs_[x][:, :1].clone() for x in ("q", "k", "v", "do")} if rank == 0 else None
+        rope_s, sm_s = cs_["rope"], cs_["sm_scale"]
+        del cs_
+        torch.cuda.empty_cache()
+
+        def spatial_step():
+            o_, sv_ = sp.spatial_forward(shard, loc["q"], loc["k"], loc["v"], rope_s, 1, G_, half, half, sm_s)
+            return (o_,) + tuple(sp.spatial_backward(shard, sv_, loc["do"]))
+
+        for _ in range(2):
+            so = spatial_step()
+        barrier()
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n_sp = 5
+        p0.record(stream)
+        for _ in range(n_sp):
+            so = spatial_step()
+        p1.record(stream)
+        barrier()
+        tp_ = torch.tensor([p0.elapsed_time(p1)], device=device, dtype=torch.float64)
+        dist.all_reduce(tp_, op=dist.ReduceOp.MAX)
+        ms_sp = tp_.item() / n_sp
+        swa.check_status()
+        worst = None
         if rank == 0:
-            verified = True
-            for r in range(world):
-                cr = device_case(cfg, 1, device, seed=r)      # slice 0 of rank r, redrawn from its own seed
-                ref = run_step(swa, cr, impl, handoff, cfg["bwd"])
-                flat = torch.cat([t.reshape(-1).view(torch.int16 if t.element_size() == 2 else torch.int32).to(torch.int32)
-                                  for t in ref])
-                verified = verified and bool(torch.equal(flat, gathered[r]))
+            ref = run_step(swa, dict(first, rope=rope_s, win=(1, G_, G_, half, half), sm_scale=sm_s), impl, True)
+            worst = max((a[:, :1].float() - b[:, :, own_g].float()).abs().max().item() for a, b in zip(so, ref))
+        e = 2 if cfg["dtype"] != torch.float32 else 4
+        halo_rows = shard.rows_ext - shard.rows_own
+        spatial = {"what": f"{G_} grid rows of {bh_local} (batch, head) slices split over {world} ranks; halo rows of "
+                           "q, k, v (forward) and o, lse, dO (backward) by NCCL send / receive into local buffers",
+                   "scaling": "strong", "ms_per_step": ms_sp, "value": step_flops / (ms_sp * 1e-3) / 1e12,
+                   "unit": "TFLOP/s", "steps": n_sp, "rows_per_rank": shard.rows_own, "halo_rows_rank0": halo_rows,
+                   "recv_bytes_per_step_rank0": halo_rows * G_ * bh_local * (e * (2 * cfg["d_qk"] + 3 * cfg["d_v"]) + 4),
+                   "max_abs_vs_unsharded_first_slice": worst}
+        del loc, so
+        torch.cuda.empty_cache()
 
     # ---------------------------------------------------------------- strong scaling of the largest configuration
     # 256 (batch, head) slices of the 256 x 256 / d = 128 / 31 x 31 problem split over the GPUs of the job (the split
@@ -611,6 +666,8 @@ def main():
         line["strong_scaling_cfg5"] = strong
     if verified is not None:
         line["verified_sharded_equals_unsharded_bitwise"] = verified
+    if spatial is not None:
+        line["spatial_sharding"] = spatial
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
