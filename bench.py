@@ -535,15 +535,17 @@ def main():
         shard = sp.RowShard(G_, G_, half, rank, world)
         cs_ = device_case(cfg, bh_local, device, seed=0)          # the same problem on every rank
         own_g = shard.own_tokens_global()
-        loc = {x: cs_[x][:, :, own_g].contiguous() for x in ("q", "k", "v", "do")}
+        # the inputs live inside tensors of the extended band from the start: no band-sized copy per step
+        loc = {x: sp.embed_rows(shard, cs_[x][:, :, own_g]) for x in ("q", "k", "v", "do")}
         first = {x: cs_[x][:, :1].clone() for x in ("q", "k", "v", "do")} if rank == 0 else None
         rope_s, sm_s = cs_["rope"], cs_["sm_scale"]
         del cs_
         torch.cuda.empty_cache()
 
         def spatial_step():
-            o_, sv_ = sp.spatial_forward(shard, loc["q"], loc["k"], loc["v"], rope_s, 1, G_, half, half, sm_s)
-            return (o_,) + tuple(sp.spatial_backward(shard, sv_, loc["do"]))
+            o_, sv_ = sp.spatial_forward(shard, loc["q"], loc["k"], loc["v"], rope_s, 1, G_, half, half, sm_s,
+                                         ext_inputs=True)
+            return (o_,) + tuple(sp.spatial_backward(shard, sv_, loc["do"], ext_inputs=True))
 
         for _ in range(2):
             so = spatial_step()

@@ -83,21 +83,27 @@ class RowShard:
         return slice(self.r0 * self.W, self.r1 * self.W)
 
 
-def exchange_halo(shard: RowShard, tensors: Sequence[torch.Tensor], group=None) -> List[torch.Tensor]:
-    """``tensors``: this rank's own rows, each ``[B, H, rows_own * W, ...]``.  Returns tensors of the extended band
-    ``[B, H, rows_ext * W, ...]``: own rows copied, halo rows received from their owners.  One batch of
-    point-to-point operations for all tensors; received rows land in local staging buffers first."""
+def embed_rows(shard: RowShard, own: torch.Tensor) -> torch.Tensor:
+    """A tensor of the extended band ``[B, H, rows_ext * W, ...]`` with ``own`` (``[B, H, rows_own * W, ...]``) copied into
+    its own rows; the halo rows are uninitialised.  Callers that build their inputs inside such a tensor in the
+    first place (``ext_inputs=True`` below) save this copy."""
+    ext = torch.empty(own.shape[:2] + (shard.rows_ext * shard.W,) + own.shape[3:], dtype=own.dtype, device=own.device)
+    ext[:, :, shard.own_tokens()] = own
+    return ext
+
+
+def exchange_halo(shard: RowShard, ext_tensors: Sequence[torch.Tensor], group=None) -> None:
+    """Fill the halo rows of tensors of the extended band (``[B, H, rows_ext * W, ...]``, own rows valid) IN PLACE with
+    their owners' rows, and serve the peers' halos from the own rows.  One batch of point-to-point operations for
+    all tensors; rows are packed into and received in local staging buffers (a row range of a ``[B, H, N, ...]``
+    tensor is not contiguous), so only halo-sized copies are made."""
     import torch.distributed as dist
 
     W = shard.W
-    outs, ops, landing = [], [], []
-    for t in tensors:
-        ext = torch.empty(t.shape[:2] + (shard.rows_ext * W,) + t.shape[3:], dtype=t.dtype, device=t.device)
-        ext[:, :, shard.own_tokens()] = t
-        outs.append(ext)
-    for ti, t in enumerate(tensors):
+    ops, landing = [], []
+    for ti, t in enumerate(ext_tensors):
         for peer, a, b in shard.sends:
-            buf = t[:, :, (a - shard.r0) * W:(b - shard.r0) * W].contiguous()
+            buf = t[:, :, (a - shard.e0) * W:(b - shard.e0) * W].contiguous()
             ops.append(dist.P2POp(dist.isend, buf, peer, group=group))
         for peer, a, b in shard.recvs:
             buf = torch.empty(t.shape[:2] + ((b - a) * W,) + t.shape[3:], dtype=t.dtype, device=t.device)
@@ -107,8 +113,7 @@ def exchange_halo(shard: RowShard, tensors: Sequence[torch.Tensor], group=None) 
         for w in dist.batch_isend_irecv(ops):
             w.wait()
     for ti, a, b, buf in landing:
-        outs[ti][:, :, (a - shard.e0) * W:(b - shard.e0) * W] = buf
-    return outs
+        ext_tensors[ti][:, :, (a - shard.e0) * W:(b - shard.e0) * W] = buf
 
 
 def _default_kernels():
@@ -129,34 +134,39 @@ def _default_kernels():
 
 
 def spatial_forward(shard: RowShard, q, k, v, rope, b_size: int, t_width: int, row_size: int, col_size: int,
-                    sm_scale: float, group=None, exchange: Optional[Callable] = None, kernels=None):
-    """Forward of this rank's band.  ``q, k, v``: own rows ``[B, H, rows_own * W, d]``; ``rope``: ``None`` or
-    ``(idx, row_cs, col_cs)`` with ``idx`` of the FULL grid.  Returns ``(o_own, saved)``; ``saved`` goes to
-    :func:`spatial_backward`."""
+                    sm_scale: float, group=None, exchange: Optional[Callable] = None, kernels=None,
+                    ext_inputs: bool = False):
+    """Forward of this rank's band.  ``q, k, v``: own rows ``[B, H, rows_own * W, d]``, or -- ``ext_inputs`` --
+    tensors of the extended band whose own rows are filled (their halo rows are then written in place, and no
+    band-sized copy is made).  ``rope``: ``None`` or ``(idx, row_cs, col_cs)`` with ``idx`` of the FULL grid.
+    ``exchange(list of extended tensors)`` fills halo rows in place (default: :func:`exchange_halo` over
+    ``group``).  Returns ``(o_own, saved)``; ``saved`` goes to :func:`spatial_backward`."""
     if shard.W != t_width * b_size or shard.row_size != row_size:
         raise ValueError("shard geometry does not match the call")
     exchange = exchange or (lambda ts_: exchange_halo(shard, ts_, group))
     fwd, _ = kernels or _default_kernels()
-    q_ext, k_ext, v_ext = exchange([q, k, v])
+    q_ext, k_ext, v_ext = (q, k, v) if ext_inputs else (embed_rows(shard, t) for t in (q, k, v))
+    exchange([q_ext, k_ext, v_ext])
     rope_ext = None if rope is None else (rope[0][shard.ext_tokens_global()].contiguous(), rope[1], rope[2])
     win = (b_size, shard.rows_ext, t_width, row_size, col_size)
     o_ext, lse_ext, q_in, k_in = fwd(q_ext, k_ext, v_ext, rope_ext, win, sm_scale)
-    own = shard.own_tokens()
-    o_own, lse_own = o_ext[:, :, own], lse_ext[:, :, own]
-    saved = dict(q_in=q_in, k_in=k_in, v_ext=v_ext, o_own=o_own, lse_own=lse_own, rope_ext=rope_ext, win=win,
+    saved = dict(q_in=q_in, k_in=k_in, v_ext=v_ext, o_ext=o_ext, lse_ext=lse_ext, rope_ext=rope_ext, win=win,
                  sm_scale=sm_scale)
-    return o_own, saved
+    return o_ext[:, :, shard.own_tokens()], saved
 
 
 def spatial_backward(shard: RowShard, saved: dict, do, group=None, exchange: Optional[Callable] = None,
-                     kernels=None):
-    """Backward of this rank's band: ``do`` = own rows of dO.  Returns ``dq, dk, dv`` of the own rows."""
+                     kernels=None, ext_inputs: bool = False):
+    """Backward of this rank's band: ``do`` = own rows of dO (or, ``ext_inputs``, a tensor of the extended band with
+    its own rows filled).  Returns ``dq, dk, dv`` of the own rows (views of band-sized tensors).  The halo rows of
+    the saved O and softmax statistic are overwritten in place with their owners' values."""
     exchange = exchange or (lambda ts_: exchange_halo(shard, ts_, group))
     _, bwd = kernels or _default_kernels()
+    do_ext = do if ext_inputs else embed_rows(shard, do)
     # halo rows of O and of the softmax statistic come from their owners (locally their windows were cut)
-    o_ext, lse_ext, do_ext = exchange([saved["o_own"].contiguous(), saved["lse_own"].contiguous(), do.contiguous()])
-    dq, dk, dv = bwd(saved["q_in"], saved["k_in"], saved["v_ext"], o_ext, lse_ext, do_ext, saved["rope_ext"],
-                     saved["win"], saved["sm_scale"])
+    exchange([saved["o_ext"], saved["lse_ext"], do_ext])
+    dq, dk, dv = bwd(saved["q_in"], saved["k_in"], saved["v_ext"], saved["o_ext"], saved["lse_ext"], do_ext,
+                     saved["rope_ext"], saved["win"], saved["sm_scale"])
     own = shard.own_tokens()
     return dq[:, :, own], dk[:, :, own], dv[:, :, own]
 

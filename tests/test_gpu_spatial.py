@@ -38,15 +38,19 @@ def test_row_sharded_bands_match_oracle_and_unsharded(th, tw, b, rs, cs, world, 
     outs, saved = [], []
     for s in shards:
         own = s.own_tokens_global()
-        take = lambda ts_, s=s: [g[:, :, s.ext_tokens_global()].contiguous() for g in (Q, K, V)]
+        def take(ts_, s=s):                      # stands in for the exchange: fills the extended tensors in place
+            for t, g in zip(ts_, (Q, K, V)):
+                t.copy_(g[:, :, s.ext_tokens_global()])
         o, sv = sp.spatial_forward(s, Q[:, :, own], K[:, :, own], V[:, :, own], rope, b, tw, rs, cs, sm, exchange=take)
         outs.append(o)
         saved.append(sv)
     O = torch.cat(outs, dim=2)
-    LSE = torch.cat([sv["lse_own"] for sv in saved], dim=2)
+    LSE = torch.cat([sv["lse_ext"][:, :, s.own_tokens()] for s, sv in zip(shards, saved)], dim=2)
     grads = []
     for s, sv in zip(shards, saved):
-        take = lambda ts_, s=s: [g[:, :, s.ext_tokens_global()].contiguous() for g in (O, LSE, DO)]
+        def take(ts_, s=s):
+            for t, g in zip(ts_, (O, LSE, DO)):
+                t.copy_(g[:, :, s.ext_tokens_global()])
         grads.append(sp.spatial_backward(s, sv, DO[:, :, s.own_tokens_global()], exchange=take))
     swa.check_status()
     got = [O] + [torch.cat([g[i] for g in grads], dim=2) for i in range(3)]
