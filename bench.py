@@ -273,7 +273,8 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="target")
+    ap.add_argument("--workload", default="target", help="target, cfg1 .. cfg5, or refharness / refharness2 (the shape "
+                    "of the reference's own benchmark harness: b_size 16, d = 32, fp16; one / two tiles of reach)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--bh-per-gpu", type=int, default=0, help="(batch*head) slices per GPU; 0 = the workload's B*H")
     ap.add_argument("--kernels", default="auto", choices=["auto", "simt", "tc"], help="kernel family to force")
@@ -302,6 +303,8 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.workload in ("refharness", "refharness2"):
+        return bench_refharness(args)
     cfg = workload_dims(args.workload)
     if args.rope_dims >= 0:
         cfg["rope_dims"] = args.rope_dims
@@ -673,6 +676,66 @@ def main():
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+    return 0
+
+
+def bench_refharness(args):
+    """The shape of the reference's own benchmark harness (src/tiled_swa.py:736-757): B = 4, H = 8, 16 x 16 tiles of
+    4 x 4 pixels (b_size = 16), d_qk = d_v = 32, one tile of reach (two with ``refharness2``: the harness's second
+    comparison is against a 19-pixel neighbourhood), fp16, no RoPE, sm_scale 0.25, forward + backward
+    through ``TiledSwa`` (the public autograd surface).  One GPU; prints one JSON line in windowed TFLOP/s (the
+    reference's harness divides a dense FLOP count by milliseconds; the windowed convention is used here as for
+    every other workload).  Head dim 32 reaches the tensor-core kernels zero-padded to 64."""
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (sm_100a); there is no CPU fallback")
+    import dl_templates_b200 as swa
+    from dl_templates_b200 import _lib
+    device = torch.device("cuda", 0)
+    B, H, d, b_size, th, tw, sm = 4, 8, 32, 16, 16, 16, 0.25
+    rs = cs = 2 if args.workload == "refharness2" else 1      # the harness compares with natten kernels 11 and 19
+    N = b_size * th * tw
+    g = torch.Generator(device=device).manual_seed(0)
+    q, k, v, do = (torch.randn((B, H, N, d), generator=g, device=device).to(torch.float16) for _ in range(4))
+    q, k, v = (t.requires_grad_(True) for t in (q, k, v))
+
+    def step():
+        o = swa.TiledSwa.apply(q, k, v, b_size, th, tw, rs, cs, sm)
+        o.backward(do)
+        return o
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    swa.check_status()
+    stream = torch.cuda.current_stream(device)
+    sampler = ClockSampler(0)
+    sampler.start()
+    launches0 = _lib.launch_count()
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    torch.cuda.synchronize(device)
+    launches = _lib.launch_count() - launches0
+    clocks = sampler.stop()
+    swa.check_status()
+    ms = e0.elapsed_time(e1) / args.steps
+    fwd_f, bwd_f = workloads_module().windowed_flops(B * H, N, b_size, rs, cs, d, d)
+    value = (fwd_f + bwd_f) / (ms * 1e-3) / 1e12
+    fam = swa.selected_impl(torch.empty((B, H, N, 64), dtype=torch.float16, device=device),
+                            torch.empty((B, H, N, 64), dtype=torch.float16, device=device), None, b_size, th, tw, rs, cs, sm)
+    print(json.dumps({
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "refharness: the reference's own harness shape (src/tiled_swa.py:736-757): B=4 H=8, 16x16 "
+                               f"tiles of 16 tokens, d=32, {rs} tile(s) of reach ({(2 * rs + 1) ** 2 * 16} keys per query), fp16, no RoPE, fwd+bwd "
+                               "through TiledSwa.apply", "bh_per_gpu": B * H, "tokens_per_head": N,
+                   "l2": "inputs smaller than L2 (warm)", "head_dim_padding": "32 -> 64 by the Python layer",
+                   "kernel_family_after_padding": fam},
+        "gpu_launches": launches, "clocks": clocks,
+    }))
     return 0
 
 
