@@ -422,8 +422,7 @@ struct RopeTabs {
 };
 __host__ __device__ __forceinline__ uint32_t rope_tab_stride(int n_rdim) { return (uint32_t)n_rdim * 8u + 16u; }
 
-// `mul`: every staged value is multiplied by it (the backward epilogues fold the softmax scale into the rotation).
-__device__ __forceinline__ void stage_rope_tables(uint8_t* dst, const RopeDev& rp, int tid, int nthreads, float mul = 1.f) {
+__device__ __forceinline__ void stage_rope_tables(uint8_t* dst, const RopeDev& rp, int tid, int nthreads) {
   const int per_row = rp.R / 2;                                         // float4 = two (cos, sin) pairs
   const uint32_t stride = rope_tab_stride(rp.R);
   const float4* src_r = reinterpret_cast<const float4*>(rp.row_cs);
@@ -432,16 +431,12 @@ __device__ __forceinline__ void stage_rope_tables(uint8_t* dst, const RopeDev& r
 #pragma unroll 1
   for (int i = tid; i < rp.max_h * per_row; i += nthreads) {
     const int r = i / per_row, c = i - r * per_row;
-    float4 v = __ldg(src_r + i);
-    v.x *= mul; v.y *= mul; v.z *= mul; v.w *= mul;
-    *reinterpret_cast<float4*>(dst + (size_t)r * stride + c * 16) = v;
+    *reinterpret_cast<float4*>(dst + (size_t)r * stride + c * 16) = __ldg(src_r + i);
   }
 #pragma unroll 1
   for (int i = tid; i < rp.max_w * per_row; i += nthreads) {
     const int r = i / per_row, c = i - r * per_row;
-    float4 v = __ldg(src_c + i);
-    v.x *= mul; v.y *= mul; v.z *= mul; v.w *= mul;
-    *reinterpret_cast<float4*>(dst_c + (size_t)r * stride + c * 16) = v;
+    *reinterpret_cast<float4*>(dst_c + (size_t)r * stride + c * 16) = __ldg(src_c + i);
   }
 }
 
