@@ -240,10 +240,13 @@ static bool make_plan_tab(const swa_geom_t* g, const swa_rope_t* rope, int which
   const int th = kn.th[which] ? kn.th[which] : kn.th_all;
   if (th == 8) return make_plan_shape(g, which, 8, 16, tab, out, cost, v2);
   if (th == 16) return make_plan_shape(g, which, 16, 8, tab, out, cost, v2);
-  if (which == 2) {
+  if (which == 2 || (which == 0 && v2)) {
     // dK/dV (K tile resident, Q blocks streamed; its accumulators leave the narrowest blocks): the shape whose
     // blocks cost less by the planner's own measure -- 16 x 8 at the 13 x 13 window with d = 64, 8 x 16 once
-    // d_v = 128 or the window grows (measured: 10 % and 13 % faster at 15 x 15 / d_v = 128 and 31 x 31 / d = 128)
+    // d_v = 128 or the window grows (measured: 10 % and 13 % faster at 15 x 15 / d_v = 128 and 31 x 31 / d = 128).
+    // The forward kernel without streamed rotation: the same rule -- 8 x 16 at the 13 x 13 and 15 x 15 windows (five
+    // or six blocks instead of seven or eight), 16 x 8 at the 31 x 31 window with d = 128, where it halves the
+    // number of blocks (23 of 80 tokens instead of 38 of 48; measured 3.11 against 3.60 ms at 32 slices)
     Plan a, b;
     long ca = 0, cb = 0;
     const bool oa = make_plan_shape(g, which, 16, 8, tab, &a, &ca, v2), ob = make_plan_shape(g, which, 8, 16, tab, &b, &cb, v2);
