@@ -146,7 +146,7 @@ bool make_plan_shape(const swa_geom_t* g, int which, int TH, int TW, uint32_t ta
   const int hw = halo_width(g, pl.TW);
   if (!v2 && hw > kPenCols) return false;     // the kernels with streamed rotation keep a whole halo row per block row
   const int halo_rows = pl.TH + 2 * g->row_size;
-  const int qch = g->d_qk / 64, vch = g->d_v / 64;
+  const int qch = (g->d_qk + 63) / 64, vch = (g->d_v + 63) / 64;
   const uint32_t x_bytes = (which == 0 ? qch : qch + vch) * 16384u;
   const uint32_t row_bytes = (qch + vch) * 128u + kXRowBytes;
   const uint32_t stage_extra = which == 0 ? 0u : 1024u;       // lse / delta slots of a streamed block
@@ -365,8 +365,10 @@ KParams make_params(const swa_geom_t* g, const swa_rope_t* rope, const Plan& pl,
   p.wr = g->row_size;
   p.wc = g->col_size;
   p.H = g->H;
-  p.qch = g->d_qk / 64;
-  p.vch = g->d_v / 64;
+  p.qch = (g->d_qk + 63) / 64;
+  p.vch = (g->d_v + 63) / 64;
+  p.dqk = g->d_qk;
+  p.dv = g->d_v;
   p.sm_scale = g->sm_scale;
   p.scale_log2 = g->sm_scale * kLog2e;
   mask_constants(g->sm_scale, &p.mask_a, &p.mask_b);
@@ -403,7 +405,16 @@ const char* unsupported_reason(const swa_geom_t* g, const swa_rope_t* rope, cons
                                int n_tensors, int which, bool prerotated) {
   if (knobs().disable) return "disabled by SWA_TC_DISABLE";
   if (g->dtype != SWA_F16 && g->dtype != SWA_BF16) return "fp32 runs on the SIMT kernels";
-  if ((g->d_qk != 64 && g->d_qk != 128) || (g->d_v != 64 && g->d_v != 128)) return "head dims must be 64 or 128";
+  // The kernels work on 64-element chunks of a row.  Those without streamed rotation also take head dims of 32 and
+  // 96: the tensor map's innermost extent is the real head dim, so TMA zero-fills the missing half of the last chunk
+  // (zero columns of q, k leave every score unchanged, zero columns of v and dO give zero columns of O, dV that are
+  // never stored), which costs MMA work on zeros but no HBM traffic and no padded copies.
+  {
+    const bool v2_dims = prerotated || !(rope && rope->idx);
+    auto dim_ok = [&](int d) { return v2_dims ? (d >= 32 && d <= 128 && d % 32 == 0) : (d == 64 || d == 128); };
+    if (!dim_ok(g->d_qk) || !dim_ok(g->d_v))
+      return v2_dims ? "head dims must be 32, 64, 96 or 128" : "head dims must be 64 or 128 for the kernels that rotate streamed rows";
+  }
   if (!(g->sm_scale > 0.f)) return "sm_scale must be positive";
   float ma, mb;
   if (!mask_constants(g->sm_scale, &ma, &mb)) return "sm_scale too small for the MMA-side window mask";
@@ -428,7 +439,7 @@ bool describe_plan(const swa_geom_t* g, const swa_rope_t* rope, int which, int32
   const bool v2 = prerot || !(rope && rope->idx);
   Plan pl;
   if (!(v2 ? make_plan_prerot(g, kind == 0 ? nullptr : rope, kind, &pl) : make_plan(g, rope, kind, &pl))) return false;
-  const uint32_t qch = g->d_qk / 64, vch = g->d_v / 64, N = pl.N;
+  const uint32_t qch = (g->d_qk + 63) / 64, vch = (g->d_v + 63) / 64, N = pl.N;
   const uint32_t pen = v2 ? (uint32_t)(pl.pen_rows + pl.pen_cols) * 32u : 0u;   // v1: inside the kernels' shared block
   uint32_t used = 1023, tmem = 0;   // worst-case pad to the 1024-byte alignment of the swizzled tiles
   if (kind == 0) {

@@ -446,7 +446,7 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
       int irow = -1, icol = -1;
       if (rope_on && t_in) decode_idx(pend_packed, p.rope.max_h, p.rope.max_w, irow, icol);
       T* qk_row = (T*)out_qk.ptr + bi * out_qk.s0 + hi * out_qk.s1 + tok * out_qk.s2;
-      const int dqk = 64 * p.qch;
+      const int dqk = p.dqk;                       // the real head dims: columns beyond them hold zeros and are not stored
       // rotated dims [0, 4R): row-angle pairs (i, i + R) in [0, 2R), column-angle pairs in [2R, 4R).  One rotated step =
       // NP pairs: columns [c0, c0 + NP) with their partners [c0 + R, c0 + R + NP).
       constexpr int NP = (R >= 16 && TABS) ? 16 : 8;   // tables in global memory: 8, the prefetched (cos, sin) values take registers
@@ -474,7 +474,7 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tm_xqk, const __grid_constant__ 
         tc_fence_after();
         [[maybe_unused]] T* v_row = qk_row;
         if constexpr (DKDV) v_row = (T*)out_v.ptr + bi * out_v.s0 + hi * out_v.s1 + tok * out_v.s2;
-        const int dv = DKDV ? 64 * p.vch : 0;
+        const int dv = DKDV ? p.dv : 0;
         const uint32_t aqk = lane_base + acc_qk;
         const int v_per_step = nrot > 0 ? (dv / 16 + nrot - 1) / nrot : 0;   // dV chunks stored after every rotated step
         // ONE loop whose body holds the rotated step and the plain 16-column chunk once each: this code runs once per

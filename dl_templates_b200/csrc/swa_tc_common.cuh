@@ -40,7 +40,9 @@ struct Plan {
 
 struct KParams {
   int t_h, Wtok, b, wr, wc, H;
-  int qch, vch;        // d_qk/64, d_v/64
+  int qch, vch;        // 64-element chunks of a q/k row and of a v row: ceil(d_qk / 64), ceil(d_v / 64)
+  int dqk, dv;         // the head dims themselves (multiples of 32): a last chunk that is only half there is zero-filled
+                       // by TMA on the way in, and the epilogues store the real columns only
   float scale_log2, sm_scale;
   float mask_a, mask_b;  // window mask through the MMA: indicator value and penalty magnitude (powers of two)
   Plan pl;

@@ -443,12 +443,12 @@ fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       if (ok) {
         tc_fence_after();
 #pragma unroll 1
-        for (int c0 = 0; c0 < (int)o_cols; c0 += 32) {
+        for (int c0 = 0; c0 < p.dv; c0 += 32) {          // the real columns of O only
           uint32_t a[32], b[32];
           if (cnt_e > 0) tmem_ld32(o_even + c0, a);
           if (cnt_d > 0) tmem_ld32(o_odd + c0, b);
           tmem_wait_ld();
-          if (c0 + 32 >= (int)o_cols) {                // everything has been read: the next item may accumulate
+          if (c0 + 32 >= p.dv) {                       // everything has been read: the next item may accumulate
             tc_fence_before();
             mbar_arrive(&sh->o_free);
             trace_ev(p, 5, tn, t == 0 && it >= p.trace_it, 2 * 16 + (it & 15));

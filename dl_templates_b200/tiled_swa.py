@@ -121,8 +121,13 @@ def padded_head_dims(q, v, rope, b_size, t_height, t_width, row_size, col_size, 
     if p_qk is None or p_v is None or (p_qk == d_qk and p_v == d_v):
         return None
     B, H, _, _ = q.shape
-    g = _lib.make_geom(q.dtype, B, H, b_size, t_height, t_width, row_size, col_size, p_qk, p_v, sm_scale, "auto")
     r = _lib.make_rope(*rope) if rope is not None else None
+    # head dims of 32 and 96 run on the tensor-core kernels as they are when no streamed row has to be rotated
+    # (TMA zero-fills the missing half of the last 64-element chunk): nothing to pad then
+    g0 = _lib.make_geom(q.dtype, B, H, b_size, t_height, t_width, row_size, col_size, d_qk, d_v, sm_scale, "auto")
+    if all(_lib.lib.swa_select_impl(C.byref(g0), _ref(r), which) == _lib.IMPL_TC for which in (0, 1, 2)):
+        return None
+    g = _lib.make_geom(q.dtype, B, H, b_size, t_height, t_width, row_size, col_size, p_qk, p_v, sm_scale, "auto")
     for which in (0, 1, 2):
         if _lib.lib.swa_select_impl(C.byref(g), _ref(r), which) != _lib.IMPL_TC:
             return None

@@ -52,7 +52,9 @@ typedef struct {
   int32_t b_size;     /* tokens per grid cell ("tile")                       */
   int32_t t_height, t_width;
   int32_t row_size, col_size; /* window half-extent in tiles; truncated at the border */
-  int32_t d_qk, d_v;
+  int32_t d_qk, d_v;  /* any size on the SIMT kernels; the tensor-core kernels take 32, 64, 96, 128
+                         (64, 128 where an entry rotates the rows it streams: swa_fwd, swa_bwd_dq,
+                         swa_bwd_dkdv with rope != NULL) */
   float   sm_scale;
   int32_t impl;       /* swa_impl_t */
 } swa_geom_t;

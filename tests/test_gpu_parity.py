@@ -492,16 +492,20 @@ def test_packed_qkv_entry(with_rope):
 
 def test_reference_selftest_shape_runs_on_tensor_cores():
     """The shape of the reference's own self-test (src/tiled_swa.py:736-746: fp16, d = 32, 4x4-pixel tiles so
-    b_size = 16, 16 x 16 tiles, one tile of reach) reaches the tensor-core kernels through zero-padded head dims;
-    results against the oracle and against the SIMT kernels on the unpadded tensors."""
+    b_size = 16, 16 x 16 tiles, one tile of reach) through the public autograd surface: the tensor-core kernels take
+    d = 32 as it is (no padding by the Python layer); results against the oracle and against the SIMT kernels.  With
+    RoPE on the kernels that rotate streamed rows the Python layer still pads to 64."""
     torch.manual_seed(0)
     B, H, d, bs, TH, TW = 1, 2, 32, 16, 16, 16
     N = bs * TH * TW
     q, k, v, do = (torch.randn(B, H, N, d).to(torch.float16) for _ in range(4))
     win = (bs, TH, TW, 1, 1)
     qd, kd, vd = (t.to(DEV).requires_grad_(True) for t in (q, k, v))
-    assert swa.padded_head_dims(qd, vd, None, *win, 1.0) == (64, 64)
-    assert swa.selected_impl(qd, vd, None, *win) == "simt"          # the unpadded problem itself is not eligible
+    assert swa.padded_head_dims(qd, vd, None, *win, 1.0) is None     # nothing to pad: the problem itself is eligible
+    assert swa.selected_impl(qd, vd, None, *win) == "tc"
+    idx = orc.encode_idx(TH, TW * bs).to(DEV)
+    tab = orc.make_cs_table(8, TH * bs).to(DEV)
+    assert swa.padded_head_dims(qd, vd, (idx, tab, tab), *win, 1.0) == (64, 64)
     o = swa.TiledSwa.apply(qd, kd, vd, *win, 1.0)
     o.backward(do.to(DEV))
     swa.check_status()
@@ -621,3 +625,37 @@ def test_unaddressable_inputs_are_copied_not_demoted():
     assert torch.equal(o1, o2) and torch.equal(l1, l2)
     for a, b in zip(g1, g2):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("d_qk,d_v,rope_dims,b,th,tw,rs,cs,dtype", [
+    (32, 32, 0, 16, 16, 16, 1, 1, torch.float16),      # the reference's own self-test shape (src/tiled_swa.py:736-746)
+    (32, 32, 32, 1, 24, 20, 3, 2, torch.bfloat16),     # RoPE on all 32 dims, rotate-once path
+    (32, 96, 32, 1, 21, 19, 2, 3, torch.float16),      # different q/k and v dims, ragged grid
+    (96, 64, 64, 2, 10, 9, 1, 2, torch.bfloat16),      # 96 = one and a half chunks, partial RoPE, tiles of two tokens
+])
+def test_head_dims_32_and_96_run_on_tensor_cores_as_they_are(monkeypatch, d_qk, d_v, rope_dims, b, th, tw, rs, cs, dtype):
+    """Head dims of 32 and 96 through the C ABI itself, with the Python layer's zero-padding switched off: the
+    tensor-core kernels without streamed rotation take them (TMA zero-fills the missing half of the last 64-element
+    chunk, the epilogues store the real columns only)."""
+    monkeypatch.setenv("SWA_NO_HEAD_PAD", "1")
+    B, H, N, W = 1, 3, th * tw * b, tw * b
+    q, k, v, do = orc.seeded_inputs(B, H, N, d_qk, d_v, dtype, seed=21)
+    rope = None
+    if rope_dims:
+        idx = orc.encode_idx(th, W)
+        idx[torch.arange(0, N, 5)] = -1
+        rope = (idx, orc.make_cs_table(rope_dims // 4, th), orc.make_cs_table(rope_dims // 4, W))
+    win, sm = (b, th, tw, rs, cs), d_qk ** -0.5
+    g = swa._lib.make_geom(dtype, B, H, *win, d_qk, d_v, sm)
+    r = swa._lib.make_rope(*(t.to(DEV) for t in rope)) if rope else None
+    for which in ((3, 4, 5) if rope else (0, 1, 2)):
+        out = (C.c_int32 * 12)()
+        assert swa._lib.lib.swa_describe_plan(C.byref(g), C.byref(r) if r else None, which, out) == 0, "not a tensor-core shape"
+    got, _ = run_gpu(q, k, v, do, rope, win, sm, path="handoff")
+    f = lambda t: t.float()
+    if rope:
+        want = orc.fused_ref(f(q), f(k), f(v), f(do), *rope, *win, sm)
+    else:
+        want = list(orc.tiled_swa_bwd_ref(f(q), f(k), f(v), f(do), *win, sm))
+    assert [t.shape[-1] for t in got] == [d_v, d_qk, d_qk, d_v]
+    assert_close(got, want, dtype, what=f"d_qk={d_qk} d_v={d_v}")
