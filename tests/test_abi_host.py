@@ -117,7 +117,7 @@ def test_every_tile_plan_fits_shared_and_tensor_memory():
     512 columns, blocks are multiples of 16 tokens of at most 128, and the ring has at least two stages."""
     idx = torch.zeros(16, dtype=torch.int32)
     n_plans = 0
-    for d_qk, d_v in ((64, 64), (128, 64), (64, 128), (128, 128)):
+    for d_qk, d_v in ((64, 64), (128, 64), (64, 128), (128, 128), (32, 32), (32, 96), (96, 64)):
         for n_rdim, max_hw in ((0, 0), (8, 16), (16, 128), (32, 128), (32, 1024)):
             if 4 * n_rdim > d_qk:
                 continue
@@ -147,6 +147,22 @@ def test_every_tile_plan_fits_shared_and_tensor_memory():
                             assert (tab_b > 0) <= (n_rdim > 0), what
                             n_plans += 1
     assert n_plans > 500
+
+
+def test_head_dims_the_tensor_core_kernels_take():
+    """32, 64, 96, 128 where no streamed row is rotated (no RoPE, or the entries that take rotated copies); 64 and
+    128 only for the kernels that rotate what they stream; anything else runs on the SIMT kernels."""
+    idx = torch.zeros(16, dtype=torch.int32)
+    tab = torch.zeros(64, 8, 2)
+    r = _lib.make_rope(idx, tab, tab)
+    out = (C.c_int32 * 12)()
+    for d, plain, streamed in ((32, True, False), (64, True, True), (96, True, False), (128, True, True), (48, False, False),
+                               (16, False, False), (160, False, False)):
+        g = _geom(d_qk=d, d_v=d)
+        assert (_lib.lib.swa_select_impl(C.byref(g), None, 0) == _lib.IMPL_TC) == plain, d
+        if 32 <= d:
+            assert (_lib.lib.swa_select_impl(C.byref(g), C.byref(r), 0) == _lib.IMPL_TC) == streamed, d
+            assert (_lib.lib.swa_describe_plan(C.byref(g), C.byref(r), 3, out) == 0) == plain, d
 
 
 def test_describe_plan_rejects_bad_arguments():
