@@ -420,7 +420,8 @@ def test_outputs_stay_inside_their_rows():
     columns after every row; ragged grids (partly empty tiles at the right and bottom edges) on both paths.  After
     forward and backward the outputs match the oracle and every guard element still holds the poison."""
     POISON = -1234.0
-    for (th, tw, w, dqk, dv, R) in ((21, 19, 7, 64, 64, 16), (9, 50, 9, 64, 128, 8), (37, 11, 5, 128, 64, 32)):
+    for (th, tw, w, dqk, dv, R) in ((21, 19, 7, 64, 64, 16), (9, 50, 9, 64, 128, 8), (37, 11, 5, 128, 64, 32),
+                                    (19, 21, 5, 32, 64, 8), (13, 18, 7, 96, 32, 16)):    # half-filled last chunks
         N = th * tw
         q, k, v, do = orc.seeded_inputs(1, 2, N, dqk, dv, torch.bfloat16, 5)
         idx = orc.encode_idx(th, tw)
@@ -436,6 +437,8 @@ def test_outputs_stay_inside_their_rows():
             return buf, buf[:, :, 8:N + 8, :d]
 
         for path in PATHS:
+            if path != "handoff" and (dqk % 64 or dv % 64):
+                continue                 # the kernels that rotate streamed rows take head dims 64 and 128 only
             (bo, o), (bq, dq), (bk, dk), (bv, dv_) = guarded(dv), guarded(dqk), guarded(dqk), guarded(dv)
             if path == "handoff":
                 _, lse, qr, kr = swa.swa_forward_rot(qd, kd, vd, rope, *win, sc, impl="tc", out=o)
