@@ -177,6 +177,8 @@ class SpatialTiledSwaRope2D(torch.autograd.Function):
     this rank's rows of the grid (``row_range(t_height, rank, world)``), ``t_height`` and ``idx`` are those of the
     full grid.  ``idx`` may be ``None`` (no RoPE)."""
 
+    kernels = None      # (forward, backward) callables standing in for the CUDA entries; the CPU tests set it
+
     @staticmethod
     def forward(ctx, q, k, v, idx, row_cs, col_cs, b_size, t_height, t_width, row_size, col_size, sm_scale,
                 group=None):
@@ -184,11 +186,17 @@ class SpatialTiledSwaRope2D(torch.autograd.Function):
 
         shard = RowShard(t_height, t_width * b_size, row_size, dist.get_rank(group), dist.get_world_size(group))
         rope = None if idx is None else (idx, row_cs, col_cs)
-        o, saved = spatial_forward(shard, q, k, v, rope, b_size, t_width, row_size, col_size, sm_scale, group)
-        ctx.shard, ctx.saved, ctx.group = shard, saved, group
+        o, saved = spatial_forward(shard, q, k, v, rope, b_size, t_width, row_size, col_size, sm_scale, group,
+                                   kernels=SpatialTiledSwaRope2D.kernels)
+        rope_ext = saved["rope_ext"] or ()
+        ctx.save_for_backward(saved["q_in"], saved["k_in"], saved["v_ext"], saved["o_ext"], saved["lse_ext"], *rope_ext)
+        ctx.shard, ctx.group, ctx.win, ctx.sm_scale = shard, group, saved["win"], saved["sm_scale"]
         return o.contiguous()
 
     @staticmethod
     def backward(ctx, do):
-        dq, dk, dv = spatial_backward(ctx.shard, ctx.saved, do, ctx.group)
+        q_in, k_in, v_ext, o_ext, lse_ext, *rope_ext = ctx.saved_tensors
+        saved = dict(q_in=q_in, k_in=k_in, v_ext=v_ext, o_ext=o_ext, lse_ext=lse_ext,
+                     rope_ext=tuple(rope_ext) if rope_ext else None, win=ctx.win, sm_scale=ctx.sm_scale)
+        dq, dk, dv = spatial_backward(ctx.shard, saved, do, ctx.group, kernels=SpatialTiledSwaRope2D.kernels)
         return (dq.contiguous(), dk.contiguous(), dv.contiguous()) + (None,) * 10

@@ -78,6 +78,13 @@ def _worker(rank, world, port, case, ret):
                                       kernels=cpu_kernels())
         dq, dk, dv = sp.spatial_backward(shard, saved, do[:, :, own], kernels=cpu_kernels())
         err = max((g - w[:, :, own]).abs().max().item() for g, w in zip((o, dq, dk, dv), want))
+        # the same through the autograd surface
+        sp.SpatialTiledSwaRope2D.kernels = cpu_kernels()
+        ql, kl, vl = (t[:, :, own].clone().requires_grad_(True) for t in (q, k, v))
+        ropes = rope if rope is not None else (None, None, None)
+        o2 = sp.SpatialTiledSwaRope2D.apply(ql, kl, vl, *ropes, b, th, tw, rs, cs, 0.3, None)
+        o2.backward(do[:, :, own])
+        err = max([err] + [(g - w[:, :, own]).abs().max().item() for g, w in zip((o2.detach(), ql.grad, kl.grad, vl.grad), want)])
         flag = torch.tensor([err])
         dist.all_reduce(flag, op=dist.ReduceOp.MAX)
         if rank == 0:
