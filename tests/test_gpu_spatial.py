@@ -75,3 +75,57 @@ def test_row_sharded_bands_match_oracle_and_unsharded(th, tw, b, rs, cs, world, 
     assert (LSE - l1).abs().max().item() < 1e-3
     for g, w, n in zip(got, ref, ("o", "dq", "dk", "dv")):
         assert orc.mean_rel(g.float().cpu(), w.float().cpu()) < mr, n
+
+
+def _nccl_worker(rank, world, port, ret):
+    import os
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        th, tw, b, rs, cs, d = 48, 40, 1, 4, 3, 64
+        q, k, v, do = orc.seeded_inputs(1, 3, th * tw, d, d, torch.bfloat16, seed=13)
+        idx = orc.encode_idx(th, tw)
+        rope = tuple(t.to(dev) for t in (idx, orc.make_cs_table(16, th), orc.make_cs_table(16, tw)))
+        Q, K, V, DO = (t.to(dev) for t in (q, k, v, do))
+        own = sp.RowShard(th, tw, rs, rank, world).own_tokens_global()
+        ql, kl, vl = (t[:, :, own].clone().requires_grad_(True) for t in (Q, K, V))
+        o = sp.SpatialTiledSwaRope2D.apply(ql, kl, vl, *rope, b, th, tw, rs, cs, d ** -0.5, None)
+        o.backward(DO[:, :, own])
+        swa.check_status()
+        o1, l1, qr, kr = swa.swa_forward_rot(Q, K, V, rope, b, th, tw, rs, cs, d ** -0.5)
+        ref = [o1] + list(swa.swa_backward_rot(qr, kr, V, o1, l1, DO, rope, b, th, tw, rs, cs, d ** -0.5))
+        err = max(orc.mean_rel(g.float().cpu(), w[:, :, own].float().cpu())
+                  for g, w in zip((o.detach(), ql.grad, kl.grad, vl.grad), ref))
+        t = torch.tensor([err], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        if rank == 0:
+            ret.put(float(t.item()))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_ranks_exchange_halos_over_nccl():
+    """The autograd surface on two GPUs with the real exchange (NCCL send / receive into local buffers): every
+    rank's rows of O, dQ, dK, dV against the unsharded run of the same kernels."""
+    import socket
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    procs = [ctx.Process(target=_nccl_worker, args=(r, 2, port, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(240)
+    alive = [p for p in procs if p.is_alive()]
+    for p in alive:                       # a rank that never came back must not outlive the test
+        p.terminate()
+        p.join(10)
+    assert not alive and all(p.exitcode == 0 for p in procs)
+    assert ret.get(timeout=5) < tolerances(torch.bfloat16)[1]
